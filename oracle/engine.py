@@ -1,0 +1,131 @@
+"""Request-at-a-time CPU restatement of generation with affix-KV reuse.
+
+Restates, for one request, what the reference engine does for every request of a
+batch (requests only share the read-only affix K/V, so batching does not change
+a request's tokens): reference nano-vdllm/model_runner.py:492-541 (affix forward
+alone at positions 0..A-1, K cached post-RoPE), :640-845 (anchor-selection probe
+and top-k), :2032-2277 (refresh at every new block, block decoding until no mask
+is left), :56-66,2091-2118 (Dream's shifted logits and seed token); same
+algorithm as the HF batch-1 path, reference llada/generate_ACache.py:311-629.
+"""
+import math
+
+import torch
+
+from .importance import relocate_keys
+from .models import KVState, OracleModel
+from .rope import rope_table
+from .sampling import get_transfer_index
+from .topk import anchor_topk
+
+
+def compute_affix_kv(model: OracleModel, affix_tokens):
+    """K/V of the affix run alone (reference: model_runner.py:492-541)."""
+    A = len(affix_tokens)
+    kv = KVState(model.spec, A, model.dtype)
+    t = torch.tensor(affix_tokens, dtype=torch.long)
+    pos = torch.arange(A)
+    model.forward_rows(t, pos, kv, pos)
+    return kv
+
+
+def _relocation_tables(model: OracleModel, length):
+    # LLaDA keeps fp32 tables, Dream casts them to the cache dtype
+    # (reference: model_runner.py:258-271)
+    dt = torch.float32 if model.spec.kind == "llada" else model.dtype
+    return rope_table(length, model.spec.head_dim, model.spec.rope_theta, dt)
+
+
+def _request_kv(model, affix_kv, total_len, affix_start):
+    """Dense logical cache of a request with the shared affix relocated into
+    [affix_start, affix_start + A) (key-side relocation semantics)."""
+    A = affix_kv.k.shape[1]
+    kv = KVState(model.spec, total_len, model.dtype)
+    cos, sin = _relocation_tables(model, max(total_len, affix_start + 1))
+    for l in range(model.spec.n_layers):
+        k = affix_kv.k[l]
+        if affix_start != 0:
+            k = relocate_keys(k, cos, sin, affix_start)
+        kv.k[l, affix_start : affix_start + A] = k
+        kv.v[l, affix_start : affix_start + A] = affix_kv.v[l]
+    return kv
+
+
+def select_anchors(model, affix_kv, tokens, affix_start, affix_end, anchor_ratio, selection_mode="top", exact=False):
+    """Returns (anchor logical positions, fp32 scores [A])."""
+    A = affix_end - affix_start
+    k = min(math.ceil(anchor_ratio * A), A)
+    n = len(tokens)
+    outside = torch.tensor([*range(affix_start), *range(affix_end, n)], dtype=torch.long)
+    tok = torch.tensor(tokens, dtype=torch.long)
+    kv = _request_kv(model, affix_kv, n, affix_start)
+    acc = torch.zeros(A, dtype=torch.float32)
+    probe = {"mask_rows": tok[outside] == model.spec.mask_id, "affix": slice(affix_start, affix_end), "acc": acc,
+             "exact": exact}
+    if k > 0:
+        model.forward_rows(tok[outside], outside, kv, outside, probe=probe)
+    idx = anchor_topk(acc[None], k, largest=(selection_mode != "bottom"))[0]
+    return (idx + affix_start).tolist(), acc
+
+
+def generate_request(model, affix_kv, tokens, affix_start, affix_end, generation_start, gen_length, block_length,
+                     anchors, threshold=0.9, trace=None):
+    """Denoise one request.  ``tokens`` already contains the mask span.
+    Returns (tokens list, nfe)."""
+    spec = model.spec
+    n = len(tokens)
+    x = torch.tensor(tokens, dtype=torch.long)
+    kv = _request_kv(model, affix_kv, n, affix_start)
+    anchors = sorted(anchors)
+    rows = torch.tensor(sorted(set(anchors) | set(range(affix_start)) | set(range(affix_end, n))), dtype=torch.long)
+    row_of = {int(p): i for i, p in enumerate(rows.tolist())}
+    nfe = 0
+    for b in range(-(-gen_length // block_length)):
+        s = generation_start + b * block_length
+        e = s + block_length
+        first = row_of[s]
+        keep = torch.arange(first, first + block_length)
+        if spec.kind == "dream":
+            keep = torch.clamp(keep, min=1) - 1  # logits of the preceding row (reference: model_runner.py:63-66)
+        logits = model.forward_rows(x[rows], rows, kv, rows, logits_rows=keep)
+        nfe += 1
+        if trace is not None:
+            trace.append(("refresh", b, logits.clone()))
+        blk = x[s:e].clone()
+        if spec.kind == "dream":
+            blk[0] = torch.argmax(logits[0])
+        else:
+            x0, ti = get_transfer_index(logits[None], (blk == spec.mask_id)[None], blk[None], threshold)
+            blk = torch.where(ti[0], x0[0], blk)
+        x[s:e] = blk
+        pos = torch.arange(s, e)
+        while bool((x[s:e] == spec.mask_id).any()):
+            logits = model.forward_rows(x[s:e], pos, kv, pos, logits_rows=torch.arange(block_length))
+            nfe += 1
+            if spec.kind == "dream":
+                logits = torch.cat([logits[:1], logits[:-1]], dim=0)
+            if trace is not None:
+                trace.append(("decode", b, logits.clone()))
+            blk = x[s:e].clone()
+            x0, ti = get_transfer_index(logits[None], (blk == spec.mask_id)[None], blk[None], threshold)
+            x[s:e] = torch.where(ti[0], x0[0], blk)
+    return x.tolist(), nfe
+
+
+def generate_with_acache(model, requests, anchor_ratio, selection_mode="top", threshold=0.9, block_length=32):
+    """requests: list of dicts {tokens (with masks), affix_start, affix_end,
+    generation_start, gen_length}.  All share the same affix tokens.
+    Returns (list of generated spans, total nfe, list of anchor lists)."""
+    r0 = requests[0]
+    affix_tokens = r0["tokens"][r0["affix_start"] : r0["affix_end"]]
+    affix_kv = compute_affix_kv(model, affix_tokens)
+    outs, anchors_all, nfe = [], [], 0
+    for r in requests:
+        anchors, _ = select_anchors(model, affix_kv, r["tokens"], r["affix_start"], r["affix_end"], anchor_ratio,
+                                    selection_mode)
+        toks, n = generate_request(model, affix_kv, r["tokens"], r["affix_start"], r["affix_end"],
+                                   r["generation_start"], r["gen_length"], block_length, anchors, threshold)
+        outs.append(toks[r["generation_start"] : r["generation_start"] + r["gen_length"]])
+        anchors_all.append(anchors)
+        nfe += n
+    return outs, nfe, anchors_all
