@@ -1,0 +1,89 @@
+// Shared helpers of the acache_b200 kernels (sm_100a only).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/acache_b200.h"
+
+namespace acache {
+
+constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs
+
+void set_last_cuda_error(cudaError_t e);
+
+#define ACACHE_CUDA_CHECK(expr)                      \
+  do {                                               \
+    cudaError_t _e = (expr);                         \
+    if (_e != cudaSuccess) {                         \
+      ::acache::set_last_cuda_error(_e);             \
+      return ACACHE_ECUDA;                           \
+    }                                                \
+  } while (0)
+
+#define ACACHE_LAUNCH_CHECK() ACACHE_CUDA_CHECK(cudaGetLastError())
+
+inline int dtype_bytes(int dtype) { return dtype == ACACHE_F32 ? 4 : 2; }
+inline bool dtype_ok(int dtype) { return dtype == ACACHE_F32 || dtype == ACACHE_F16 || dtype == ACACHE_BF16; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// ---- element conversion ---------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f32(T x);
+template <> __device__ __forceinline__ float to_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_f32<__half>(__half x) { return __half2float(x); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float x);
+template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+// round-trip through T: the rounding an eager op producing dtype T applies
+template <typename T> __device__ __forceinline__ float round_to(float x) { return to_f32<T>(from_f32<T>(x)); }
+
+// 16-byte vector of elements
+template <typename T> struct Vec16 {
+  static constexpr int N = 16 / sizeof(T);
+  union { uint4 u; T e[N]; };
+};
+
+__device__ __forceinline__ uint4 ld_global_nc(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+  return r;
+}
+__device__ __forceinline__ void st_global_cs(void* p, uint4 v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Arithmetic dtype of a rotation: promote(element dtype, table dtype).  When it is
+// fp32 the three operations (mul, mul, add) each round once in fp32 and the result is
+// cast once; when it is a 16-bit type every operation result is rounded to it, which
+// is what an eager framework op chain in that dtype produces.
+template <typename TC>
+__device__ __forceinline__ float rot_lo(float x1, float x2, float c, float s) {
+  // out = x1*c + (-x2)*s
+  float a = round_to<TC>(__fmul_rn(x1, c));
+  float b = round_to<TC>(__fmul_rn(-x2, s));
+  return round_to<TC>(__fadd_rn(a, b));
+}
+template <typename TC>
+__device__ __forceinline__ float rot_hi(float x1, float x2, float c, float s) {
+  // out = x2*c + x1*s
+  float a = round_to<TC>(__fmul_rn(x2, c));
+  float b = round_to<TC>(__fmul_rn(x1, s));
+  return round_to<TC>(__fadd_rn(a, b));
+}
+
+// dispatch helpers ---------------------------------------------------------------
+#define ACACHE_DISPATCH_DTYPE(dtype, T, ...)                    \
+  switch (dtype) {                                              \
+    case ACACHE_F32: { using T = float; __VA_ARGS__; break; }   \
+    case ACACHE_F16: { using T = __half; __VA_ARGS__; break; }  \
+    case ACACHE_BF16: { using T = __nv_bfloat16; __VA_ARGS__; break; } \
+    default: return ACACHE_EINVAL;                              \
+  }
+
+}  // namespace acache

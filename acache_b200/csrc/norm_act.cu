@@ -1,0 +1,167 @@
+// RMSNorm and gated activation of the transformer block: single-pass, HBM-bound.
+#include "common.cuh"
+
+namespace acache {
+
+// one CTA per row; the row is kept in registers between the reduction and the write
+template <typename T, int VPT /*16-byte vectors per thread*/>
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const T* __restrict__ x, int64_t x_stride,
+                                                      const T* __restrict__ w, T* __restrict__ y, int64_t y_stride,
+                                                      int n_cols, float eps) {
+  constexpr int E = 16 / sizeof(T);
+  const int row = blockIdx.x;
+  const T* xr = x + (int64_t)row * x_stride;
+  T* yr = y + (int64_t)row * y_stride;
+  const int nvec = n_cols / E;
+  Vec16<T> v[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * 256;
+    if (c < nvec) {
+      v[i].u = *reinterpret_cast<const uint4*>(xr + (int64_t)c * E);
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const float f = to_f32<T>(v[i].e[e]);
+        ss = fmaf(f, f, ss);
+      }
+    }
+  }
+  __shared__ float red[8];
+  __shared__ float s_scale;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < 8; ++i) t += red[i];
+    s_scale = rsqrtf(t / (float)n_cols + eps);
+  }
+  __syncthreads();
+  const float sc = s_scale;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * 256;
+    if (c < nvec) {
+      Vec16<T> wv, o;
+      wv.u = *reinterpret_cast<const uint4*>(w + (int64_t)c * E);
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const float n = round_to<T>(to_f32<T>(v[i].e[e]) * sc);      // normalised value cast back to T
+        o.e[e] = from_f32<T>(to_f32<T>(wv.e[e]) * n);                 // weight * x in T
+      }
+      *reinterpret_cast<uint4*>(yr + (int64_t)c * E) = o.u;
+    }
+  }
+}
+
+// generic row kernel for widths the register kernel does not cover
+template <typename T>
+__global__ void __launch_bounds__(256) rmsnorm_generic_kernel(const T* __restrict__ x, int64_t x_stride,
+                                                              const T* __restrict__ w, T* __restrict__ y,
+                                                              int64_t y_stride, int n_cols, float eps) {
+  const int row = blockIdx.x;
+  const T* xr = x + (int64_t)row * x_stride;
+  T* yr = y + (int64_t)row * y_stride;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < n_cols; c += 256) {
+    const float f = to_f32<T>(xr[c]);
+    ss = fmaf(f, f, ss);
+  }
+  __shared__ float red[8];
+  __shared__ float s_scale;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < 8; ++i) t += red[i];
+    s_scale = rsqrtf(t / (float)n_cols + eps);
+  }
+  __syncthreads();
+  const float sc = s_scale;
+  for (int c = threadIdx.x; c < n_cols; c += 256) {
+    const float n = round_to<T>(to_f32<T>(xr[c]) * sc);
+    yr[c] = from_f32<T>(to_f32<T>(w[c]) * n);
+  }
+}
+
+__device__ __forceinline__ float act_fn(float x, int act) {
+  if (act == 0) return x / (1.f + expf(-x));
+  if (act == 1) return fmaxf(x, 0.f);
+  return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) act_mul_kernel(const T* __restrict__ gate, const T* __restrict__ up,
+                                                      T* __restrict__ y, int64_t n_vec, int64_t n, int act) {
+  constexpr int E = 16 / sizeof(T);
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_vec; i += (int64_t)gridDim.x * blockDim.x) {
+    Vec16<T> g, u, o;
+    g.u = ld_global_nc(gate + i * E);
+    u.u = ld_global_nc(up + i * E);
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      const float a = round_to<T>(act_fn(to_f32<T>(g.e[e]), act));
+      o.e[e] = from_f32<T>(a * to_f32<T>(u.e[e]));
+    }
+    *reinterpret_cast<uint4*>(y + i * E) = o.u;
+  }
+  // tail (n not a multiple of the vector width)
+  if (blockIdx.x == 0) {
+    for (int64_t i = n_vec * E + threadIdx.x; i < n; i += blockDim.x) {
+      const float a = round_to<T>(act_fn(to_f32<T>(gate[i]), act));
+      y[i] = from_f32<T>(a * to_f32<T>(up[i]));
+    }
+  }
+}
+
+}  // namespace acache
+
+using namespace acache;
+
+extern "C" int acache_rmsnorm(const void* x, int64_t x_stride, const void* weight, void* y, int64_t y_stride,
+                              int n_rows, int n_cols, float eps, int dtype, void* stream) {
+  if (!dtype_ok(dtype) || n_rows < 0 || n_cols <= 0) return ACACHE_EINVAL;
+  if (n_rows == 0) return ACACHE_OK;
+  if (!x || !weight || !y) return ACACHE_EINVAL;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int E = 16 / dtype_bytes(dtype);
+  const bool vec = n_cols % E == 0 && x_stride % E == 0 && y_stride % E == 0 && aligned16(x) && aligned16(y) &&
+                   aligned16(weight);
+  const int nvec = n_cols / E;
+  ACACHE_DISPATCH_DTYPE(dtype, T, {
+    if (vec && nvec <= 256) {
+      rmsnorm_kernel<T, 1><<<n_rows, 256, 0, st>>>((const T*)x, x_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps);
+    } else if (vec && nvec <= 512) {
+      rmsnorm_kernel<T, 2><<<n_rows, 256, 0, st>>>((const T*)x, x_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps);
+    } else if (vec && nvec <= 1024) {
+      rmsnorm_kernel<T, 4><<<n_rows, 256, 0, st>>>((const T*)x, x_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps);
+    } else {
+      rmsnorm_generic_kernel<T><<<n_rows, 256, 0, st>>>((const T*)x, x_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps);
+    }
+  });
+  ACACHE_LAUNCH_CHECK();
+  return ACACHE_OK;
+}
+
+extern "C" int acache_act_mul(const void* gate, const void* up, void* y, int64_t n, int act, int dtype,
+                              void* stream) {
+  if (!dtype_ok(dtype) || n < 0 || act < 0 || act > 2) return ACACHE_EINVAL;
+  if (n == 0) return ACACHE_OK;
+  if (!gate || !up || !y) return ACACHE_EINVAL;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int E = 16 / dtype_bytes(dtype);
+  const bool vec = aligned16(gate) && aligned16(up) && aligned16(y);
+  const int64_t n_vec = vec ? n / E : 0;
+  int64_t blocks = (n_vec + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > kNumSMs * 8) blocks = kNumSMs * 8;
+  ACACHE_DISPATCH_DTYPE(dtype, T, {
+    act_mul_kernel<T><<<(int)blocks, 256, 0, st>>>((const T*)gate, (const T*)up, (T*)y, n_vec, n, act);
+  });
+  ACACHE_LAUNCH_CHECK();
+  return ACACHE_OK;
+}

@@ -1,0 +1,172 @@
+"""LLaDA-8B architecture for paged serving.
+
+Llama-style pre-norm block with separate q/k/v projections, RoPE computed in fp32,
+SiLU-gated FFN and an untied output head; ragged ``[n]`` and batched ``[B, T]`` inputs
+(reference: nano-vdllm/model/modeling_llada.py:593-767 block, :889-982 model,
+:999-1064 wrapper).  Parameter names equal the reference's, so its checkpoints load
+with ``load_state_dict``.  The GEMMs are library calls; normalisation, RoPE + K/V
+scatter, attention and the gated activation are this package's kernels.
+"""
+from __future__ import annotations
+
+from types import SimpleNamespace
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from .. import ops
+from ..utils import get_context
+from .attention import Attention
+from .configuration import LLaDAConfig
+from .modeling_common import RMSNorm, RopeCache
+
+
+class LLaDALlamaBlock(nn.Module):
+    def __init__(self, layer_id: int, config: LLaDAConfig, rope: RopeCache, device=None, dtype=None):
+        super().__init__()
+        self.layer_id = layer_id
+        self.config = config
+        d, kvd, ffn = config.d_model, config.effective_n_kv_heads * (config.d_model // config.n_heads), config.ffn_size
+        kw = dict(device=device, dtype=dtype)
+        qkv_bias = config.include_bias or config.include_qkv_bias
+        self.attn_norm = RMSNorm(d, config.rms_norm_eps, **kw)
+        self.ff_norm = RMSNorm(d, config.rms_norm_eps, **kw)
+        self.q_proj = nn.Linear(d, d, bias=qkv_bias, **kw)
+        self.k_proj = nn.Linear(d, kvd, bias=qkv_bias, **kw)
+        self.v_proj = nn.Linear(d, kvd, bias=qkv_bias, **kw)
+        self.attn_out = nn.Linear(d, d, bias=config.include_bias, **kw)
+        self.ff_proj = nn.Linear(d, ffn, bias=config.include_bias, **kw)
+        self.up_proj = nn.Linear(d, ffn, bias=config.include_bias, **kw)
+        self.ff_out = nn.Linear(ffn, d, bias=config.include_bias, **kw)
+        self.rotary_emb = rope
+        self.attn = Attention(num_heads=config.n_heads, head_dim=d // config.n_heads,
+                              num_kv_heads=config.effective_n_kv_heads)
+        self._qkv_w = self._qkv_b = None
+
+    def fuse_qkv(self):
+        """One projection GEMM for q, k and v: the three weights become views of one
+        buffer (state-dict names and values are unchanged)."""
+        w = torch.cat([self.q_proj.weight.data, self.k_proj.weight.data, self.v_proj.weight.data], dim=0)
+        d, kvd = self.q_proj.out_features, self.k_proj.out_features
+        self.q_proj.weight.data, self.k_proj.weight.data, self.v_proj.weight.data = w[:d], w[d:d + kvd], w[d + kvd:]
+        self._qkv_w = w
+        if self.q_proj.bias is not None:
+            b = torch.cat([self.q_proj.bias.data, self.k_proj.bias.data, self.v_proj.bias.data])
+            self.q_proj.bias.data, self.k_proj.bias.data, self.v_proj.bias.data = b[:d], b[d:d + kvd], b[d + kvd:]
+            self._qkv_b = b
+
+    def forward(self, x: torch.Tensor, position_ids: torch.Tensor, max_pos: int) -> torch.Tensor:
+        """``x [n, d]`` rows of the ragged batch, ``position_ids [n]`` int64."""
+        cfg = self.config
+        n = x.shape[0]
+        nh, hkv, D = cfg.n_heads, cfg.effective_n_kv_heads, cfg.d_model // cfg.n_heads
+        h = self.attn_norm(x)
+        if self._qkv_w is not None:
+            qkv = F.linear(h, self._qkv_w, self._qkv_b)
+            q, k, v = qkv[:, : nh * D], qkv[:, nh * D: (nh + hkv) * D], qkv[:, (nh + hkv) * D:]
+        else:
+            q, k, v = self.q_proj(h), self.k_proj(h), self.v_proj(h)
+        q, k, v = q.view(n, nh, D), k.view(n, hkv, D), v.view(n, hkv, D)
+        cos, sin = self.rotary_emb.get(max_pos, x.device)
+        ctx = get_context()
+        attn = self.attn
+        if attn.k_cache.numel() and ctx.slot_mapping is not None:
+            # RoPE of q/k and the scatter of k/v into the paged cache in one pass
+            ops.rope_store(q, k, v, position_ids, cos, sin, attn.k_cache, attn.v_cache, ctx.slot_mapping)
+            attn.kv_already_stored = True
+        else:
+            ops.rope_store(q, k, None, position_ids, cos, sin)
+            attn.kv_already_stored = False
+        att = attn(q, k, v).reshape(n, nh * D)
+        attn.kv_already_stored = False
+        x = x + self.attn_out(att)
+        h = self.ff_norm(x)
+        x = x + self.ff_out(ops.act_mul(self.ff_proj(h), self.up_proj(h), cfg.activation_type))
+        return x
+
+
+class LLaDAModel(nn.Module):
+    def __init__(self, config: LLaDAConfig, device=None, dtype=None):
+        super().__init__()
+        self.config = config
+        kw = dict(device=device, dtype=dtype)
+        D = config.d_model // config.n_heads
+        self.rope = RopeCache(D, config.rope_theta, torch.float32)
+        self.transformer = nn.ModuleDict(dict(
+            wte=nn.Embedding(config.embedding_size or config.vocab_size, config.d_model, **kw),
+            ln_f=RMSNorm(config.d_model, config.rms_norm_eps, **kw),
+        ))
+        self.transformer.update({"blocks": nn.ModuleList(
+            [LLaDALlamaBlock(i, config, self.rope, **kw) for i in range(config.n_layers)])})
+        if not config.weight_tying:
+            self.transformer.update({"ff_out": nn.Linear(config.d_model, config.embedding_size or config.vocab_size,
+                                                         bias=config.include_bias, **kw)})
+
+    def forward(self, input_ids, position_ids=None, output_hidden_states=None, compute_logits=True,
+                logits_keep_indices=None, max_pos: int | None = None):
+        shape = input_ids.shape
+        ids = input_ids.reshape(-1)
+        if position_ids is None:
+            position_ids = torch.arange(ids.numel(), device=ids.device)
+        pos = position_ids.reshape(-1)
+        if max_pos is None:
+            max_pos = int(pos.max().item()) + 1
+        x = self.transformer["wte"](ids)
+        if self.config.input_emb_norm:
+            x = x * (self.config.d_model ** 0.5)
+        for block in self.transformer["blocks"]:
+            x = block(x, pos, max_pos)
+        logits = None
+        if compute_logits:
+            if logits_keep_indices is not None:
+                x = x.index_select(0, logits_keep_indices)
+            x = self.transformer["ln_f"](x)
+            if self.config.weight_tying:
+                logits = F.linear(x, self.transformer["wte"].weight)
+            else:
+                logits = self.transformer["ff_out"](x)
+            if self.config.scale_logits:
+                logits = logits * (self.config.d_model ** -0.5)
+            if logits_keep_indices is None:
+                logits = logits.view(*shape, -1)
+        return SimpleNamespace(logits=logits, hidden_states=None)
+
+
+class LLaDAModelLM(nn.Module):
+    """Wrapper with the reference's attribute layout: ``.model`` is the transformer,
+    ``.config`` the architecture (reference: modeling_llada.py:999-1064)."""
+
+    def __init__(self, config: LLaDAConfig, device=None, dtype=None, init_params: bool = True, seed: int | None = None):
+        super().__init__()
+        self.config = config
+        self.model = LLaDAModel(config, device=device, dtype=dtype)
+        if init_params:
+            self.reset_parameters(seed)
+
+    @property
+    def device(self):
+        return next(self.parameters()).device
+
+    @torch.no_grad()
+    def reset_parameters(self, seed: int | None = None):
+        gen = None
+        if seed is not None:
+            gen = torch.Generator(device=self.device).manual_seed(seed)
+        for name, p in self.named_parameters():
+            if name.endswith("norm.weight") or name.endswith("ln_f.weight"):
+                p.fill_(1.0)
+            elif name.endswith(".bias"):
+                p.zero_()
+            else:
+                p.normal_(0.0, self.config.init_std, generator=gen)
+
+    def fuse_projections(self):
+        for block in self.model.transformer["blocks"]:
+            block.fuse_qkv()
+        return self
+
+    def forward(self, input_ids=None, output_hidden_states=None, position_ids=None, logits_keep_indices=None,
+                compute_logits=True, max_pos=None):
+        return self.model(input_ids, position_ids=position_ids, compute_logits=compute_logits,
+                          logits_keep_indices=logits_keep_indices, max_pos=max_pos)

@@ -1,0 +1,121 @@
+"""Operators that replace eager PyTorch sequences of the reference engine:
+anchor scoring and top-k, RoPE + K/V scatter, RMSNorm, gated activation and
+threshold unmasking.  Thin wrappers over the C ABI."""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import check, dtype_code, ptr, stream_ptr
+
+_ACT = {"silu": 0, "relu": 1, "gelu": 2}
+
+
+def anchor_topk(scores: torch.Tensor, k: int, largest: bool = True, offsets: torch.Tensor | None = None):
+    """``scores`` fp32 ``[B, A]`` -> int64 ``[B, k]`` ascending indices (+ ``offsets[b]``).
+    Replaces topk + sort + add (reference: nano-vdllm/model_runner.py:833-843); among
+    equal scores the lowest index is selected."""
+    assert scores.is_cuda and scores.dtype == torch.float32 and scores.dim() == 2 and scores.stride(1) == 1
+    B, A = scores.shape
+    k = min(int(k), A)
+    out = torch.empty(B, k, dtype=torch.int64, device=scores.device)
+    if offsets is not None:
+        assert offsets.dtype == torch.int32 and offsets.numel() == B and offsets.is_cuda
+    check(_lib.load().acache_anchor_topk(ptr(scores), B, A, scores.stride(0), k, int(bool(largest)), ptr(offsets),
+                                         ptr(out), stream_ptr()), "anchor_topk")
+    return out
+
+
+_scratch: dict[int, torch.Tensor] = {}
+
+
+def _scratch_for(device, nbytes: int) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _scratch.get(idx)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _scratch[idx] = buf
+    return buf
+
+
+def anchor_importance(q, q_rows, affix_k, affix_shift: int, rope_cos, rope_sin, scale: float, importance):
+    """Accumulates one layer's influence score of every affix token into
+    ``importance`` fp32 ``[A]`` (reference: nano-vdllm/model_runner.py:730-773).
+    ``q`` ``[n, nh, D]`` post-RoPE; ``q_rows`` int32 indices of the mask-token rows;
+    ``affix_k`` ``[A, Hkv, D]`` = the layer's cached affix keys (slots ``0..A-1``)."""
+    assert q.is_cuda and q.dim() == 3 and q.stride(2) == 1 and q.stride(1) == q.shape[2]
+    assert q_rows.dtype == torch.int32 and q_rows.is_cuda
+    assert affix_k.dim() == 3 and affix_k.stride(2) == 1 and affix_k.stride(1) == affix_k.shape[2]
+    assert importance.dtype == torch.float32 and importance.is_contiguous()
+    n_q, (nh, D) = q_rows.numel(), q.shape[1:]
+    A, hkv = affix_k.shape[:2]
+    if n_q == 0 or A == 0:
+        return
+    lib = _lib.load()
+    nbytes = lib.acache_anchor_importance_scratch_bytes(n_q, nh, A)
+    scratch = _scratch_for(q.device, nbytes)
+    if affix_shift != 0:
+        rc, rs, rstride, rrows, rdt = ptr(rope_cos), ptr(rope_sin), rope_cos.stride(0), rope_cos.shape[0], dtype_code(rope_cos.dtype)
+    else:
+        rc, rs, rstride, rrows, rdt = None, None, 0, 0, _lib.F32
+    check(lib.acache_anchor_importance(
+        ptr(q), q.stride(0), ptr(q_rows), n_q, nh, hkv, D, dtype_code(q.dtype), ptr(affix_k), affix_k.stride(0), A,
+        int(affix_shift), rc, rs, rstride, rrows, rdt, float(scale), ptr(importance), ptr(scratch), scratch.numel(),
+        stream_ptr()), "anchor_importance")
+
+
+def rope_store(q, k, v, positions, rope_cos, rope_sin, k_cache=None, v_cache=None, slot_mapping=None):
+    """Rotates ``q [n, nh, D]`` and ``k [n, Hkv, D]`` in place by table rows
+    ``positions`` and scatters the rotated ``k`` and ``v`` to ``slot_mapping``
+    (reference: nano-vdllm/model/modeling_llada.py:412-453 + model/attention.py:34-41)."""
+    n, nh, D = q.shape
+    hkv = k.shape[1]
+    assert q.stride(2) == 1 and q.stride(1) == D and k.stride(2) == 1 and k.stride(1) == D
+    assert positions.dtype == torch.int64 and positions.numel() == n
+    num_slots = 0
+    if slot_mapping is not None:
+        assert v is not None and v.stride(2) == 1 and v.stride(1) == D
+        assert slot_mapping.dtype == torch.int32 and slot_mapping.numel() == n
+        num_slots = k_cache.numel() // (hkv * D)
+    flag = _lib.err_flag(q.device)
+    check(_lib.load().acache_rope_store(
+        ptr(q), q.stride(0), ptr(k), k.stride(0), ptr(v), v.stride(0) if v is not None else 0, n, nh, hkv, D,
+        dtype_code(q.dtype), ptr(positions), ptr(rope_cos), ptr(rope_sin), rope_cos.stride(0), rope_cos.shape[0],
+        dtype_code(rope_cos.dtype), ptr(k_cache), ptr(v_cache), ptr(slot_mapping), num_slots, ptr(flag),
+        stream_ptr()), "rope_store")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """``weight * cast(x * rsqrt(mean(x^2) + eps))`` with the mean in fp32
+    (reference: nano-vdllm/model/modeling_llada.py:308-323)."""
+    shape = x.shape
+    x2 = x.reshape(-1, shape[-1])
+    assert x2.stride(1) == 1
+    y = torch.empty_like(x2)
+    check(_lib.load().acache_rmsnorm(ptr(x2), x2.stride(0), ptr(weight), ptr(y), y.stride(0), x2.shape[0], x2.shape[1],
+                                     float(eps), dtype_code(x.dtype), stream_ptr()), "rmsnorm")
+    return y.view(shape)
+
+
+def act_mul(gate: torch.Tensor, up: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """``act(gate) * up`` (reference: nano-vdllm/model/modeling_llada.py:757-763)."""
+    assert gate.shape == up.shape and gate.is_contiguous() and up.is_contiguous()
+    y = torch.empty_like(gate)
+    check(_lib.load().acache_act_mul(ptr(gate), ptr(up), ptr(y), gate.numel(), _ACT[act], dtype_code(gate.dtype),
+                                     stream_ptr()), "act_mul")
+    return y
+
+
+def transfer_tokens(logits: torch.Tensor, blocks: torch.Tensor, mask_id: int, threshold: float):
+    """Threshold unmasking at temperature 0 applied in place to ``blocks`` int64
+    ``[R, T]`` from ``logits [R*T, V]`` (reference: nano-vdllm/model_runner.py:2279-2314).
+    Returns ``(x0, confidence)`` of every position."""
+    R, T = blocks.shape
+    logits = logits.reshape(R * T, -1)
+    assert logits.stride(1) == 1 and blocks.is_contiguous() and blocks.dtype == torch.int64
+    x0 = torch.empty(R, T, dtype=torch.int64, device=blocks.device)
+    conf = torch.empty(R, T, dtype=torch.float32, device=blocks.device)
+    check(_lib.load().acache_transfer_tokens(ptr(logits), logits.stride(0), logits.shape[1], dtype_code(logits.dtype),
+                                             ptr(blocks), R, T, int(mask_id), float(threshold), ptr(x0), ptr(conf),
+                                             stream_ptr()), "transfer_tokens")
+    return x0, conf

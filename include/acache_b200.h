@@ -1,0 +1,183 @@
+/*
+ * acache_b200 - C ABI of the B200 (sm_100a) affix-KV-reuse kernels.
+ *
+ * The reference engine has no FFI: its operator boundary is a set of Python
+ * callables backed by Triton kernels and eager PyTorch ops.  Each entry point
+ * below replaces one of them and cites it (paths are relative to the reference
+ * repository).  All pointers are device pointers unless stated otherwise, all
+ * tensors are borrowed for the duration of the call, nothing is retained, and no
+ * entry point allocates device memory unless its comment says so.  `stream` is a
+ * cudaStream_t passed as void* (NULL = default stream); work is enqueued, not
+ * synchronised.  Return value: 0 on success, a negative ACACHE_E* code otherwise
+ * (acache_status_string gives the text).  No entry point has a CPU fallback.
+ */
+#ifndef ACACHE_B200_H
+#define ACACHE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define ACACHE_API __attribute__((visibility("default")))
+#else
+#define ACACHE_API
+#endif
+
+#define ACACHE_OK 0
+#define ACACHE_EINVAL (-1)      /* bad argument (shape, dtype, alignment)            */
+#define ACACHE_EUNSUPPORTED (-2)/* valid request this build has no kernel for        */
+#define ACACHE_ECUDA (-3)       /* a CUDA call failed; see acache_last_cuda_error()  */
+#define ACACHE_ELIMIT (-4)      /* size beyond a documented fixed limit              */
+#define ACACHE_ETIMEOUT (-5)    /* a bounded device-side wait gave up                */
+
+/* element types of K/V/Q tensors and RoPE tables */
+#define ACACHE_F32 0
+#define ACACHE_F16 1
+#define ACACHE_BF16 2
+
+ACACHE_API const char* acache_status_string(int status);
+/* text of the last CUDA error seen by this library on the calling thread */
+ACACHE_API const char* acache_last_cuda_error(void);
+/* ABI version, bumped on any signature change */
+ACACHE_API int acache_abi_version(void);
+
+/* ------------------------------------------------------------------ K/V scatter
+ * Replaces store_kvcache (nano-vdllm/model/attention.py:11-41).
+ * key/value: [n_tokens, row_elems] rows `key_stride`/`value_stride` elements apart
+ * (row_elems = n_kv_heads*head_dim, contiguous inside a row).  Caches are addressed
+ * flat: row `slot` starts at slot*row_elems.  slot == -1 skips the token; any other
+ * slot outside [0, num_slots) is an error that the kernel reports by skipping the
+ * row and raising the flag *err_flag (device int32, may be NULL). */
+ACACHE_API int acache_store_kvcache(const void* key, int64_t key_stride, const void* value, int64_t value_stride,
+                         void* k_cache, void* v_cache, const int32_t* slot_mapping, int n_tokens,
+                         int row_elems, int64_t num_slots, int dtype, int32_t* err_flag, void* stream);
+
+/* ------------------------------------------------------------------ affix relocation
+ * Replaces materialize_relocated_affix (nano-vdllm/model/acache_attention.py:7-128;
+ * caller nano-vdllm/model_runner.py:314-341): for every layer l, affix token t, kv head h
+ *   K[l, dst(t), h, :] = K[l, t, h, :]*cos[shift] + rotate_half(K[l, t, h, :])*sin[shift]
+ *   V[l, dst(t), h, :] = V[l, t, h, :]
+ * in ONE launch for all layers and all requests.  k_cache/v_cache: layer l starts at
+ * l*layer_stride elements, slot s at s*n_kv_heads*head_dim inside a layer; the source
+ * is slots 0..affix_len-1.  Arithmetic is in promote(dtype, rope_dtype) with one
+ * rounding per operation (no FMA contraction), result cast to `dtype`.
+ * Request r is relocated by shifts[r] (row of the RoPE tables) to
+ *   dst(t) = dst_block_tables ? dst_block_tables[r*table_stride + t/block_size]*block_size + t%block_size
+ *                             : dst_slots[r] + t.
+ * The single-request reference call is n_requests = 1, dst_block_tables = NULL.
+ * shifts, dst_slots, dst_block_tables are device int32 arrays.  Source and
+ * destination slots must not overlap. */
+ACACHE_API int acache_relocate_affix(void* k_cache, void* v_cache, int64_t layer_stride, int n_layers, int64_t num_slots,
+                          int n_kv_heads, int head_dim, int dtype, const void* rope_cos, const void* rope_sin,
+                          int64_t rope_row_stride, int rope_rows, int rope_dtype, int affix_len, int n_requests,
+                          const int32_t* shifts, const int32_t* dst_slots, const int32_t* dst_block_tables,
+                          int table_stride, int block_size, int32_t* err_flag, void* stream);
+
+/* ------------------------------------------------------------------ RoPE + K/V scatter
+ * Replaces RotaryEmbedding.forward (nano-vdllm/model/modeling_llada.py:412-453; Dream:
+ * nano-vdllm/model/modeling_dream.py:159-170,472-476) followed by store_kvcache
+ * (nano-vdllm/model/attention.py:34-41) for the rows of one forward:
+ *   q[i], k[i] rotated in place by table row positions[i]; rotated k[i] and v[i]
+ *   scattered to slot_mapping[i] (skipped if slot_mapping is NULL or the slot is -1).
+ * q: [n, n_heads, head_dim] rows q_stride elements apart; k/v: [n, n_kv_heads, head_dim]
+ * rows k_stride/v_stride apart.  Arithmetic as in acache_relocate_affix:
+ * rope_dtype == ACACHE_F32 gives the LLaDA flow (fp32 math, one cast), a table of the
+ * activation dtype gives the Dream flow (every product and sum rounded to it). */
+ACACHE_API int acache_rope_store(void* q, int64_t q_stride, void* k, int64_t k_stride, const void* v, int64_t v_stride,
+                      int n_tokens, int n_heads, int n_kv_heads, int head_dim, int dtype,
+                      const int64_t* positions, const void* rope_cos, const void* rope_sin,
+                      int64_t rope_row_stride, int rope_rows, int rope_dtype, void* k_cache, void* v_cache,
+                      const int32_t* slot_mapping, int64_t num_slots, int32_t* err_flag, void* stream);
+
+/* ------------------------------------------------------------------ anchor top-k
+ * Replaces torch.topk + sort + add in anchor selection (nano-vdllm/model_runner.py:833-843;
+ * llada/generate_ACache.py:225-262).  scores: fp32 [n_rows, row_stride] (first n_cols of
+ * a row are used).  Writes, per row, the k selected column indices in ascending order plus
+ * offsets[row] (offsets may be NULL) as int64 into out[row*k ...].  largest != 0 selects
+ * the k largest scores, else the k smallest; among equal scores the lowest index wins;
+ * NaN orders above +inf.  k is clamped to n_cols. */
+ACACHE_API int acache_anchor_topk(const float* scores, int n_rows, int n_cols, int64_t row_stride, int k, int largest,
+                       const int32_t* offsets, int64_t* out, void* stream);
+
+/* ------------------------------------------------------------------ anchor influence score
+ * Replaces the eager code patched into Attention.forward during the anchor-selection
+ * probe (nano-vdllm/model_runner.py:730-773; HF: llada/generate_ACache.py:139-183) for one
+ * layer and one request:
+ *   K' = rotate(affix K rows 0..affix_len-1 of the layer's cache, by table row affix_shift)
+ *   W  = softmax_over_affix( q[rows] K'^T * scale )      (GQA: head h reads kv head h/group)
+ *   importance[a] += sum_heads sum_rows W[h, row, a]      (fp32, accumulated in place)
+ * q: [*, n_heads, head_dim] post-RoPE, rows q_stride apart; q_rows: device int32[n_q_rows]
+ * row indices (the mask-token rows).  Deterministic: per-CTA partial sums go to `scratch`
+ * and are reduced in a fixed order.  scratch must hold acache_anchor_importance_scratch_bytes()
+ * bytes; contents on entry are irrelevant. */
+ACACHE_API int64_t acache_anchor_importance_scratch_bytes(int n_q_rows, int n_heads, int affix_len);
+ACACHE_API int acache_anchor_importance(const void* q, int64_t q_stride, const int32_t* q_rows, int n_q_rows, int n_heads,
+                             int n_kv_heads, int head_dim, int dtype, const void* affix_k, int64_t k_slot_stride,
+                             int affix_len, int affix_shift, const void* rope_cos, const void* rope_sin,
+                             int64_t rope_row_stride, int rope_rows, int rope_dtype, float scale,
+                             float* importance, void* scratch, int64_t scratch_bytes, void* stream);
+
+/* ------------------------------------------------------------------ varlen attention, slot map
+ * Replaces acache_attention (nano-vdllm/model/acache_attention.py:338-514,643-738):
+ * bidirectional attention of ragged queries q[total_q, n_heads, head_dim] (rows q_stride
+ * apart) over K/V rows gathered from the flat caches through read_slot_mapping
+ * (int32[sum kv_len], request b uses [cu_seqlens_k[b], cu_seqlens_k[b+1])).
+ * Relocation modes (all NULL / 0 = none):
+ *   key side:   shared_prefix_len > 0, affix_shifts != NULL, shared_kv_lens == NULL:
+ *               a key whose slot < shared_prefix_len is rotated by table row
+ *               |j - slot| (j = its index in the request), sine negated when j < slot;
+ *   query side: additionally shared_kv_lens != NULL: the first shared_kv_lens[b] keys of
+ *               request b are scored with q rotated by the inverse of table row
+ *               affix_shifts[b]; the remaining keys with q as given.
+ * Output rows have the layout of q (rows o_stride apart).  Requests with kv_len <= 0
+ * get zeros.  max_seqlen_q / max_seqlen_k are host-known upper bounds (no device
+ * synchronisation is done to find them). */
+ACACHE_API int acache_attention(const void* q, int64_t q_stride, void* out, int64_t o_stride, const void* k_cache,
+                     const void* v_cache, int64_t num_slots, int n_heads, int n_kv_heads, int head_dim, int dtype,
+                     const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int batch, int max_seqlen_q,
+                     int max_seqlen_k, const int32_t* read_slot_mapping, float softmax_scale,
+                     int shared_prefix_len, const int32_t* shared_kv_lens, const int32_t* affix_shifts,
+                     const void* rope_cos, const void* rope_sin, int64_t rope_row_stride, int rope_rows,
+                     int rope_dtype, int32_t* err_flag, void* stream);
+
+/* ------------------------------------------------------------------ varlen attention, block tables
+ * Replaces baseline_ragged_attention and baseline_decode_attention
+ * (nano-vdllm/model/acache_attention.py:132-334,525-640): key j of request b lives at
+ * slot block_tables[b*table_stride + j/block_size]*block_size + j%block_size.
+ * The decode form is cu_seqlens_q = {0, T, 2T, ...}. */
+ACACHE_API int acache_paged_attention(const void* q, int64_t q_stride, void* out, int64_t o_stride, const void* k_cache,
+                           const void* v_cache, int64_t num_slots, int n_heads, int n_kv_heads, int head_dim,
+                           int dtype, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int batch,
+                           int max_seqlen_q, int max_seqlen_k, const int32_t* block_tables, int table_stride,
+                           int block_size, float softmax_scale, int32_t* err_flag, void* stream);
+
+/* ------------------------------------------------------------------ small fused ops of the block
+ * RMSNorm as the served models compute it (nano-vdllm/model/modeling_llada.py:308-323,
+ * nano-vdllm/model/modeling_dream.py:76-81): y = weight * cast(x_f32 * rsqrt(mean(x_f32^2) + eps)). */
+ACACHE_API int acache_rmsnorm(const void* x, int64_t x_stride, const void* weight, void* y, int64_t y_stride, int n_rows,
+                   int n_cols, float eps, int dtype, void* stream);
+/* y = act(gate) * up, act: 0 = SiLU, 1 = ReLU, 2 = GELU(erf)
+ * (nano-vdllm/model/modeling_llada.py:757-763, nano-vdllm/model/modeling_dream.py:297-303). */
+ACACHE_API int acache_act_mul(const void* gate, const void* up, void* y, int64_t n, int act, int dtype, void* stream);
+
+/* ------------------------------------------------------------------ threshold unmasking
+ * Replaces get_transfer_index at temperature 0 with 'low_confidence' remasking
+ * (nano-vdllm/model_runner.py:2279-2314) and applies the result:
+ * logits [n_rows*block_len, vocab] (rows logits_stride apart, `dtype`); blocks int64
+ * [n_rows, block_len] updated in place: masked positions whose confidence
+ * exp(max_logit - logsumexp) >= threshold receive argmax(logits); a row that has masks
+ * but no position over the threshold commits its most confident masked position.
+ * Ties in argmax resolve to the lowest vocabulary index, ties in confidence to the lowest
+ * position.  x0_out (int64) and conf_out (fp32), each n_rows*block_len long, are required
+ * work space and receive the per-position argmax and confidence. */
+ACACHE_API int acache_transfer_tokens(const void* logits, int64_t logits_stride, int vocab, int dtype, int64_t* blocks,
+                           int n_rows, int block_len, int64_t mask_id, float threshold, int64_t* x0_out,
+                           float* conf_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ACACHE_B200_H */

@@ -1,0 +1,417 @@
+"""CUDA kernels (through the C ABI) against the CPU oracle and the reference-generated
+golden vectors.  Bit-exact for data movement, rotation and index selection; stated
+tolerances for the floating-point contractions."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import load_npz
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _ops():
+    from acache_b200 import _lib, ops
+    from acache_b200.model import acache_attention as aa
+    from acache_b200.model import attention as att
+
+    return _lib, ops, aa, att
+
+
+def _rope(length, D, theta=10000.0, dtype=torch.float32):
+    from oracle.rope import rope_table
+
+    c, s = rope_table(length, D, theta, dtype)
+    return c, s
+
+
+# ----------------------------------------------------------------------------- store
+def test_store_kvcache_golden(triton_ops):
+    _lib, ops, aa, att = _ops()
+    t = triton_ops
+    kc, vc = t["store_kc_in"].to(DEV), t["store_vc_in"].to(DEV)
+    att.store_kvcache(t["store_key"].to(DEV), t["store_val"].to(DEV), kc, vc, t["store_slots"].to(DEV))
+    assert torch.equal(kc.cpu(), t["store_kc_out"]) and torch.equal(vc.cpu(), t["store_vc_out"])
+    _lib.check_device_errors()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_store_kvcache_random(dtype):
+    from oracle import kv_ops
+
+    _lib, ops, aa, att = _ops()
+    g = torch.Generator().manual_seed(0)
+    N, H, D, nb, Bk = 300, 8, 128, 6, 256
+    key = torch.randn(N, H, D, generator=g).to(dtype)
+    val = torch.randn(N, H, D, generator=g).to(dtype)
+    kc = torch.randn(nb, Bk, H, D, generator=g).to(dtype)
+    vc = torch.randn(nb, Bk, H, D, generator=g).to(dtype)
+    slots = torch.randperm(nb * Bk, generator=g)[:N].to(torch.int32)
+    slots[::7] = -1
+    kc_d, vc_d = kc.to(DEV), vc.to(DEV)
+    # strided rows: key/value are slices of a fused projection output
+    fused = torch.zeros(N, 3, H, D, dtype=dtype, device=DEV)
+    fused[:, 1], fused[:, 2] = key.to(DEV), val.to(DEV)
+    att.store_kvcache(fused[:, 1], fused[:, 2], kc_d, vc_d, slots.to(DEV))
+    kv_ops.store_kvcache(key, val, kc, vc, slots)
+    assert torch.equal(kc_d.cpu(), kc) and torch.equal(vc_d.cpu(), vc)
+    _lib.check_device_errors()
+
+
+def test_store_kvcache_flags_bad_slot_without_faulting():
+    _lib, ops, aa, att = _ops()
+    key = torch.ones(2, 1, 16, device=DEV)
+    kc = torch.zeros(1, 4, 1, 16, device=DEV)
+    vc = torch.zeros_like(kc)
+    att.store_kvcache(key, key, kc, vc, torch.tensor([1, 99], dtype=torch.int32, device=DEV))
+    with pytest.raises(_lib.AcacheError):
+        _lib.check_device_errors()
+    assert kc[0, 1].eq(1).all() and kc[0, 0].eq(0).all()
+
+
+def test_empty_inputs_are_noops():
+    _lib, ops, aa, att = _ops()
+    kc = torch.zeros(1, 4, 1, 16, device=DEV)
+    att.store_kvcache(torch.zeros(0, 1, 16, device=DEV), torch.zeros(0, 1, 16, device=DEV), kc, kc.clone(),
+                      torch.zeros(0, dtype=torch.int32, device=DEV))
+    out = ops.anchor_topk(torch.zeros(0, 8, device=DEV), 3)
+    assert out.shape == (0, 3)
+    q = torch.zeros(0, 2, 16, device=DEV)
+    cu = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o = aa.acache_attention(q, kc.expand(1, 4, 1, 16).contiguous(), kc.clone(), cu, cu,
+                            torch.zeros(0, dtype=torch.int32, device=DEV), max_seqlen_q=0)
+    assert o.shape == q.shape
+
+
+# ----------------------------------------------------------------------------- relocation
+def test_materialize_golden_bit_exact(triton_ops):
+    _lib, ops, aa, att = _ops()
+    t = triton_ops
+    for tag in ("f32", "f16"):
+        A, shift, dst = (int(x) for x in t[f"mat_{tag}_meta"])
+        k, v = t[f"mat_{tag}_k_in"].to(DEV), t[f"mat_{tag}_v_in"].to(DEV)
+        aa.materialize_relocated_affix(k, v, t["mat_cos"].to(DEV), t["mat_sin"].to(DEV), dst, A, shift)
+        assert torch.equal(k.cpu(), t[f"mat_{tag}_k_out"]), tag
+        assert torch.equal(v.cpu(), t[f"mat_{tag}_v_out"]), tag
+    _lib.check_device_errors()
+
+
+@pytest.mark.parametrize("dtype,table_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.float32),
+                                                (torch.bfloat16, torch.bfloat16), (torch.float16, torch.float16)])
+def test_relocation_batched_block_tables_bit_exact(dtype, table_dtype):
+    """Micro-op configuration: 2 layers, 8 KV heads, head_dim 128, blocks of 256, a
+    512-token affix, 4 requests with shifts 0 / U[64,1024], RoPE theta 5e5."""
+    from oracle import kv_ops
+
+    _lib, ops, aa, att = _ops()
+    g = torch.Generator().manual_seed(1)
+    L, H, D, Bk, A, R = 2, 8, 128, 256, 512, 4
+    nb = 2 + 2 * R
+    k = torch.randn(L, nb * Bk, H, D, generator=g).to(dtype)
+    v = torch.randn(L, nb * Bk, H, D, generator=g).to(dtype)
+    cos, sin = _rope(1100, D, 500000.0, table_dtype)
+    shifts = [0] + torch.randint(64, 1025, (R - 1,), generator=g).tolist()
+    perm = (torch.randperm(nb - 2, generator=g) + 2).tolist()
+    tables = [perm[2 * r: 2 * r + 2] for r in range(R)]
+    kd, vd = k.to(DEV), v.to(DEV)
+    aa.relocate_affix_batched(kd, vd, cos.to(DEV), sin.to(DEV), A,
+                              torch.tensor(shifts, dtype=torch.int32, device=DEV),
+                              dst_block_tables=torch.tensor(tables, dtype=torch.int32, device=DEV), block_size=Bk)
+    kv_ops.relocate_affix_batched(k, v, cos, sin, tables, shifts, A, Bk)
+    assert torch.equal(kd.cpu(), k) and torch.equal(vd.cpu(), v)
+    _lib.check_device_errors()
+
+
+def test_relocation_ragged_affix_and_single_form():
+    from oracle import kv_ops
+
+    _lib, ops, aa, att = _ops()
+    g = torch.Generator().manual_seed(2)
+    L, S, H, D = 3, 64, 2, 64
+    k = torch.randn(L, S, H, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(L, S, H, D, generator=g).to(torch.bfloat16)
+    cos, sin = _rope(S, D)
+    kd, vd = k.to(DEV), v.to(DEV)
+    aa.materialize_relocated_affix(kd, vd, cos.to(DEV), sin.to(DEV), 12, 7, 5)
+    kv_ops.materialize_relocated_affix(k, v, cos, sin, 12, 7, 5)
+    assert torch.equal(kd.cpu(), k) and torch.equal(vd.cpu(), v)
+
+
+def test_relocation_roundtrip_property():
+    """Relocating by +s and then rotating back by -s recovers K within bf16 rounding;
+    V is copied exactly.  Size-independent check used at full cache sizes."""
+    _lib, ops, aa, att = _ops()
+    g = torch.Generator().manual_seed(3)
+    L, H, D, Bk, A = 4, 8, 128, 256, 1024
+    k = torch.randn(L, 3 * A, H, D, generator=g).to(torch.bfloat16).to(DEV)
+    v = torch.randn(L, 3 * A, H, D, generator=g).to(torch.bfloat16).to(DEV)
+    cos, sin = _rope(2048, D, 500000.0)
+    cos, sin = cos.to(DEV), sin.to(DEV)
+    src_k, src_v = k[:, :A].clone(), v[:, :A].clone()
+    aa.materialize_relocated_affix(k, v, cos, sin, A, A, 777)
+    assert torch.equal(v[:, A: 2 * A], src_v)
+    # norms are preserved by a rotation
+    n0 = src_k.float().norm(dim=-1)
+    n1 = k[:, A: 2 * A].float().norm(dim=-1)
+    assert torch.allclose(n0, n1, rtol=1e-2, atol=1e-2)
+    rot = k[:, A: 2 * A].float()
+    half = D // 2
+    back = rot * cos[777] - torch.cat((-rot[..., half:], rot[..., :half]), -1) * sin[777]
+    assert (back - src_k.float()).abs().max() < 0.05
+
+
+# ----------------------------------------------------------------------------- rope + store
+@pytest.mark.parametrize("kind", ["llada", "dream"])
+def test_rope_store_matches_oracle(kind):
+    from oracle import kv_ops
+    from oracle.rope import dream_rope_qk, llada_rope_qk
+
+    _lib, ops, aa, att = _ops()
+    g = torch.Generator().manual_seed(4)
+    n, nh, hkv, D, nb, Bk = 77, 8, 2, 128, 3, 64
+    dt = torch.bfloat16
+    q = torch.randn(n, nh, D, generator=g).to(dt)
+    k = torch.randn(n, hkv, D, generator=g).to(dt)
+    v = torch.randn(n, hkv, D, generator=g).to(dt)
+    pos = torch.randint(0, 500, (n,), generator=g)
+    kc = torch.zeros(nb, Bk, hkv, D, dtype=dt)
+    vc = torch.zeros_like(kc)
+    slots = torch.randperm(nb * Bk, generator=g)[:n].to(torch.int32)
+    slots[5] = -1
+    theta = 500000.0
+    if kind == "llada":
+        q_ref, k_ref = llada_rope_qk(q, k, pos, theta)
+        cos, sin = _rope(512, D, theta, torch.float32)
+    else:
+        q_ref, k_ref = dream_rope_qk(q, k, pos, theta)
+        cos, sin = _rope(512, D, theta, dt)
+    kv_ops.store_kvcache(k_ref, v, kc, vc, slots)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    kcd, vcd = torch.zeros_like(kc, device=DEV), torch.zeros_like(vc, device=DEV)
+    ops.rope_store(qd, kd, vd, pos.to(DEV), cos.to(DEV), sin.to(DEV), kcd, vcd, slots.to(DEV))
+    assert torch.equal(qd.cpu(), q_ref) and torch.equal(kd.cpu(), k_ref)
+    assert torch.equal(kcd.cpu(), kc) and torch.equal(vcd.cpu(), vc)
+    _lib.check_device_errors()
+
+
+# ----------------------------------------------------------------------------- top-k
+def test_topk_golden_and_ties():
+    from oracle import topk as otopk
+
+    _lib, ops, aa, att = _ops()
+    z = load_npz("topk.npz")
+    s = torch.from_numpy(z["scores"]).to(DEV)
+    assert np.array_equal(ops.anchor_topk(s, int(z["k"]), True).cpu().numpy(), z["top"])
+    assert np.array_equal(ops.anchor_topk(s, int(z["k"]), False).cpu().numpy(), z["bottom"])
+    t = torch.tensor([[1.0, 3.0, 3.0, 2.0, 3.0, 0.0, 3.0]], device=DEV)
+    assert ops.anchor_topk(t, 3, True).tolist() == [[1, 2, 4]]
+    assert ops.anchor_topk(t, 2, False).tolist() == [[0, 5]]
+    assert ops.anchor_topk(torch.zeros(2, 9, device=DEV), 4, True).tolist() == [[0, 1, 2, 3]] * 2
+    off = torch.tensor([10, 20], dtype=torch.int32, device=DEV)
+    assert ops.anchor_topk(torch.zeros(2, 9, device=DEV), 2, True, off).tolist() == [[10, 11], [20, 21]]
+    g = torch.Generator().manual_seed(5)
+    for A, k in ((1, 1), (33, 33), (800, 160), (1024, 7), (1025, 103), (8192, 820), (60000, 5000)):
+        for quant in (False, True):
+            sc = torch.randn(3, A, generator=g)
+            if quant:  # duplicate-heavy: many equal scores straddle the cut
+                sc = (sc * 2).round() / 2
+            sc[0, 0] = float("-inf")
+            for largest in (True, False):
+                got = ops.anchor_topk(sc.to(DEV), k, largest).cpu()
+                assert torch.equal(got, otopk.anchor_topk(sc, k, largest)), (A, k, quant, largest)
+
+
+# ----------------------------------------------------------------------------- importance
+@pytest.mark.parametrize("nh,hkv,D,A,nq,shift,dt", [
+    (4, 4, 64, 37, 9, 0, torch.bfloat16), (8, 2, 128, 300, 70, 13, torch.bfloat16),
+    (4, 2, 32, 64, 5, 3, torch.float32), (32, 32, 128, 800, 256, 0, torch.bfloat16)])
+def test_anchor_importance_vs_oracle(nh, hkv, D, A, nq, shift, dt):
+    from oracle.importance import layer_importance, relocate_keys
+
+    _lib, ops, aa, att = _ops()
+    g = torch.Generator().manual_seed(6)
+    n = nq + 11
+    q = torch.randn(n, nh, D, generator=g).to(dt)
+    kc = torch.randn(A + 20, hkv, D, generator=g).to(dt)
+    rows = torch.randperm(n, generator=g)[:nq].sort().values.to(torch.int32)
+    cos, sin = _rope(64, D)
+    kk = relocate_keys(kc[:A], cos, sin, shift) if shift else kc[:A]
+    ref = layer_importance(q[rows.long()], kk, D ** -0.5, exact=True)
+    imp = torch.zeros(A, device=DEV)
+    for _ in range(2):  # accumulates across calls (layers)
+        ops.anchor_importance(q.to(DEV), rows.to(DEV), kc.to(DEV)[:A], shift, cos.to(DEV), sin.to(DEV), D ** -0.5, imp)
+    got = imp.cpu() / 2
+    assert torch.allclose(got, ref, rtol=2e-3, atol=1e-4), (got - ref).abs().max()
+    assert abs(float(got.sum()) - nq * nh) < 1e-2 * nq * nh  # softmax rows sum to one
+
+
+# ----------------------------------------------------------------------------- attention
+def _tol(dt):
+    return {torch.float32: 2e-5, torch.float16: 4e-3, torch.bfloat16: 2e-2}[dt]
+
+
+def test_attention_golden_all_modes(triton_ops):
+    _lib, ops, aa, att = _ops()
+    t = {k: v.to(DEV) for k, v in triton_ops.items() if k.startswith("att_")}
+    spl = int(t["att_shared_prefix_len"])
+    for tag, tol in (("f32", 2e-5), ("f16", 4e-3)):
+        args = (t[f"att_{tag}_q"], t[f"att_{tag}_kc"], t[f"att_{tag}_vc"], t[f"att_{tag}_cu_q"], t[f"att_{tag}_cu_k"])
+        plain = aa.acache_attention(*args, t[f"att_{tag}_logical"])
+        key = aa.acache_attention(*args, t[f"att_{tag}_logical"], None, spl, None, t[f"att_{tag}_shifts"],
+                                  t["att_cos"], t["att_sin"])
+        qs = aa.acache_attention(*args, t[f"att_{tag}_packed"], None, spl, t[f"att_{tag}_shared_lens"],
+                                 t[f"att_{tag}_shifts"], t["att_cos"], t["att_sin"])
+        for name, got in (("plain", plain), ("keyside", key), ("queryside", qs)):
+            err = (got.float() - t[f"att_{tag}_{name}"].float()).abs().max().item()
+            assert err < tol, (tag, name, err)
+    _lib.check_device_errors()
+
+
+def test_block_table_attention_golden(triton_ops):
+    _lib, ops, aa, att = _ops()
+    t = {k: v.to(DEV) for k, v in triton_ops.items() if k.startswith("bt_")}
+    got = aa.baseline_ragged_attention(t["bt_q"], t["bt_kc"], t["bt_vc"], t["bt_cu"], t["bt_cu"], t["bt_tables"])
+    assert (got - t["bt_ragged"]).abs().max() < 2e-5
+    got = aa.baseline_decode_attention(t["bt_qd"], t["bt_kc"], t["bt_vc"], t["bt_seqlens"], t["bt_tables"])
+    assert (got - t["bt_decode"]).abs().max() < 2e-5
+
+
+def _random_case(g, dt, nh, hkv, D, Bk, nb, q_lens, kv_lens, A=0, shifts=None):
+    """Random paged cache + per-request slot maps; with A > 0 the slots 0..A-1 are a
+    shared span placed at logical [shift, shift + A) of every request, minus a few anchors."""
+    import random
+
+    pyr = random.Random(int(torch.randint(0, 1 << 30, (1,), generator=g)))
+    kc = torch.randn(nb, Bk, hkv, D, generator=g).to(dt)
+    vc = torch.randn(nb, Bk, hkv, D, generator=g).to(dt)
+    q = torch.randn(sum(q_lens), nh, D, generator=g).to(dt)
+    logical, packed, shared_lens = [], [], []
+    for i, n in enumerate(kv_lens):
+        private = pyr.sample(range(A, nb * Bk), n)
+        if A:
+            s = shifts[i]
+            anchors = set(pyr.sample(range(s, s + A), max(1, A // 5)))
+            m = [(p - s) if (s <= p < s + A and p not in anchors) else private[p] for p in range(n)]
+        else:
+            m = private
+        logical += m
+        sh = [x for x in m if x < A]
+        packed += sh + [x for x in m if x >= A]
+        shared_lens.append(len(sh))
+    cu_q = torch.tensor([0, *np.cumsum(q_lens)], dtype=torch.int32)
+    cu_k = torch.tensor([0, *np.cumsum(kv_lens)], dtype=torch.int32)
+    return q, kc, vc, cu_q, cu_k, torch.tensor(logical, dtype=torch.int32), torch.tensor(packed, dtype=torch.int32), \
+        torch.tensor(shared_lens, dtype=torch.int32)
+
+
+@pytest.mark.parametrize("dt,nh,hkv,D", [
+    (torch.bfloat16, 8, 8, 128), (torch.bfloat16, 28, 4, 128), (torch.float16, 4, 2, 64),
+    (torch.float16, 4, 2, 160), (torch.float32, 4, 4, 16), (torch.bfloat16, 4, 4, 16)])
+def test_attention_random_vs_oracle(dt, nh, hkv, D):
+    from oracle import attention as oatt
+
+    _lib, ops, aa, att = _ops()
+    g = torch.Generator().manual_seed(7)
+    Bk, nb, A = 16, 40, 48
+    q_lens, kv_lens, shifts = [70, 1, 33, 130], [200, 90, 64, 333], [9, 0, 16, 101]
+    q, kc, vc, cu_q, cu_k, logical, packed, shl = _random_case(g, dt, nh, hkv, D, Bk, nb, q_lens, kv_lens, A, shifts)
+    cos, sin = _rope(512, D)
+    sh_t = torch.tensor(shifts, dtype=torch.int32)
+    d = lambda x: x.to(DEV)
+    tol = _tol(dt)
+    ref = oatt.acache_attention(q, kc, vc, cu_q, cu_k, logical)
+    got = aa.acache_attention(d(q), d(kc), d(vc), d(cu_q), d(cu_k), d(logical))
+    assert (got.cpu().float() - ref.float()).abs().max() < tol
+    ref = oatt.acache_attention(q, kc, vc, cu_q, cu_k, logical, None, A, None, sh_t, cos, sin)
+    got = aa.acache_attention(d(q), d(kc), d(vc), d(cu_q), d(cu_k), d(logical), None, A, None, d(sh_t), d(cos), d(sin))
+    assert (got.cpu().float() - ref.float()).abs().max() < tol
+    ref = oatt.acache_attention(q, kc, vc, cu_q, cu_k, packed, None, A, shl, sh_t, cos, sin)
+    got = aa.acache_attention(d(q), d(kc), d(vc), d(cu_q), d(cu_k), d(packed), None, A, d(shl), d(sh_t), d(cos), d(sin),
+                              max_seqlen_q=max(q_lens), max_seqlen_k=max(kv_lens))
+    assert (got.cpu().float() - ref.float()).abs().max() < tol
+    _lib.check_device_errors()
+
+
+def test_materialised_equals_key_side_relocation_bitwise():
+    """reference: nano-vdllm/tests/test_attention_kernels.py:168-234."""
+    _lib, ops, aa, att = _ops()
+    torch.manual_seed(0)
+    L, S, nh, hkv, D = 1, 32, 4, 2, 64
+    q_len, kv_len, a0, A, dst = 5, 13, 7, 3, 24
+    dt = torch.bfloat16
+    q = torch.randn(q_len, nh, D, device=DEV, dtype=dt)
+    k = torch.randn(L, S, hkv, D, device=DEV, dtype=dt)
+    v = torch.randn_like(k)
+    cos, sin = (x.to(DEV) for x in _rope(S, D))
+    key_slots = list(range(A, A + kv_len))
+    for lp, pos in enumerate(range(a0, a0 + A)):
+        key_slots[pos] = lp
+    cu_q = torch.tensor([0, q_len], device=DEV, dtype=torch.int32)
+    cu_k = torch.tensor([0, kv_len], device=DEV, dtype=torch.int32)
+    shifts = torch.tensor([a0], device=DEV, dtype=torch.int32)
+    key_side = aa.acache_attention(q, k[0].view(4, 8, hkv, D), v[0].view(4, 8, hkv, D), cu_q, cu_k,
+                                   torch.tensor(key_slots, device=DEV, dtype=torch.int32),
+                                   shared_prefix_len=A, affix_shifts=shifts, rope_cos=cos, rope_sin=sin)
+    aa.materialize_relocated_affix(k, v, cos, sin, dst, A, a0)
+    mat_slots = list(key_slots)
+    for lp, pos in enumerate(range(a0, a0 + A)):
+        mat_slots[pos] = dst + lp
+    mat = aa.acache_attention(q, k[0].view(4, 8, hkv, D), v[0].view(4, 8, hkv, D), cu_q, cu_k,
+                              torch.tensor(mat_slots, device=DEV, dtype=torch.int32))
+    assert torch.equal(mat, key_side)
+
+
+# ----------------------------------------------------------------------------- block ops
+@pytest.mark.parametrize("cols", [64, 4096, 3584, 1000])
+def test_rmsnorm_matches_reference_flow(cols):
+    _lib, ops, aa, att = _ops()
+    g = torch.Generator().manual_seed(8)
+    x = (torch.randn(37, cols, generator=g) * 3).to(torch.bfloat16)
+    w = torch.randn(cols, generator=g).to(torch.bfloat16)
+    xf = x.float()
+    ref = w * (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5)).to(torch.bfloat16)
+    got = ops.rmsnorm(x.to(DEV), w.to(DEV), 1e-5).cpu()
+    # the fp32 mean is reduced in a different order: allow one bf16 ulp on a few elements
+    diff = (got.float() - ref.float()).abs()
+    assert (diff <= ref.float().abs() * 2 ** -7 + 1e-6).all()
+    assert (diff > 0).float().mean() < 0.01
+
+
+@pytest.mark.parametrize("act", ["silu", "relu", "gelu"])
+def test_act_mul(act):
+    import torch.nn.functional as F
+
+    _lib, ops, aa, att = _ops()
+    g = torch.Generator().manual_seed(9)
+    a = (torch.randn(5, 1003, generator=g) * 2).to(torch.bfloat16)
+    b = torch.randn(5, 1003, generator=g).to(torch.bfloat16)
+    ref = {"silu": F.silu, "relu": F.relu, "gelu": F.gelu}[act](a) * b
+    got = ops.act_mul(a.to(DEV), b.to(DEV), act).cpu()
+    diff = (got.float() - ref.float()).abs()
+    assert (diff <= ref.float().abs() * 2 ** -7 + 1e-6).all()
+
+
+def test_transfer_tokens_golden_and_random():
+    from oracle import sampling
+
+    _lib, ops, aa, att = _ops()
+    z = load_npz("sampling.npz")
+    logits, x, mask = torch.from_numpy(z["logits"]), torch.from_numpy(z["x"]), torch.from_numpy(z["mask"])
+    mask_id = int(x[mask][0])
+    blocks = x.clone().to(DEV)
+    ops.transfer_tokens(logits.to(DEV), blocks, mask_id, float(z["threshold"]))
+    want = torch.where(torch.from_numpy(z["transfer"]), torch.from_numpy(z["x0"]), x)
+    assert torch.equal(blocks.cpu(), want)
+    g = torch.Generator().manual_seed(10)
+    B, T, V = 16, 32, 126464
+    lg = (torch.randn(B * T, V, generator=g) * 2).to(torch.bfloat16)
+    lg[torch.arange(0, B * T, 3), torch.randint(0, V, (len(range(0, B * T, 3)),), generator=g)] += 14.0
+    xb = torch.full((B, T), 126336, dtype=torch.int64)
+    xb[:, ::5] = 7
+    x0, ti = sampling.get_transfer_index(lg.view(B, T, V), xb == 126336, xb, 0.9)
+    want = torch.where(ti, x0, xb)
+    blocks = xb.clone().to(DEV)
+    ops.transfer_tokens(lg.to(DEV), blocks, 126336, 0.9)
+    assert torch.equal(blocks.cpu(), want)
