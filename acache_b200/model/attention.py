@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 from torch import nn
 
-from .. import _lib
+from .. import _lib, ops
 from .._lib import check, dtype_code, ptr, stream_ptr
 from ..utils import get_context
 from .acache_attention import acache_attention, baseline_decode_attention, baseline_ragged_attention
@@ -46,8 +46,10 @@ class Attention(nn.Module):
         self.shared_prefix_len = 0
         self.relocation_rope_cos = self.relocation_rope_sin = torch.tensor([])
         self.k_cache = self.v_cache = torch.tensor([])
-        # set by the engine: K/V of this step were already scattered by the fused RoPE+store kernel
+        # set by the model block: K/V of this step were already scattered by the fused RoPE+store kernel
         self.kv_already_stored = False
+        # set by the engine during the anchor-selection probe: one entry per request of the batch
+        self.probe = None
 
     def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
         ctx = get_context()
@@ -59,6 +61,14 @@ class Attention(nn.Module):
             q = q.reshape(bs * seqlen, self.num_heads, self.head_dim)
             k = k.reshape(bs * seqlen, self.num_kv_heads, self.head_dim)
             v = v.reshape(bs * seqlen, self.num_kv_heads, self.head_dim)
+        if self.probe:
+            # anchor-selection probe: add this layer's influence score of every affix token
+            # (reference: nano-vdllm/model_runner.py:730-773)
+            scale = self.scale if self.scale is not None else self.head_dim ** -0.5
+            flat_k = k_cache.view(-1, self.num_kv_heads, self.head_dim)
+            for p in self.probe:
+                ops.anchor_importance(q, p.q_rows, flat_k[: p.affix_len], p.affix_shift, p.rope_cos, p.rope_sin,
+                                      scale, p.importance)
         if not self.kv_already_stored:
             store_kvcache(k, v, k_cache, v_cache, ctx.slot_mapping)
         if ctx.use_acache:

@@ -120,6 +120,8 @@ class DreamModel(nn.Module):
         self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False, device=device, dtype=dtype)
         if init_params:
             self.reset_parameters(seed)
+        for p in self.parameters():  # serving only: no autograd state
+            p.requires_grad_(False)
 
     @property
     def device(self):

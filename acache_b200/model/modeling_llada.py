@@ -143,6 +143,8 @@ class LLaDAModelLM(nn.Module):
         self.model = LLaDAModel(config, device=device, dtype=dtype)
         if init_params:
             self.reset_parameters(seed)
+        for p in self.parameters():  # serving only: no autograd state
+            p.requires_grad_(False)
 
     @property
     def device(self):

@@ -187,4 +187,10 @@ def random_state_dict(spec: ArchSpec, seed: int, std: float = 0.02, dtype=torch.
             sd[b + "mlp.down_proj.weight"] = rn(spec.d_model, spec.ffn)
         sd["model.norm.weight"] = torch.ones(spec.d_model, dtype=dtype)
         sd["lm_head.weight"] = rn(spec.vocab, spec.d_model)
+    # A random output head can make the mask token itself the arg-max, and block decoding
+    # (here and in the reference) only ends when no mask is left.  Giving the mask row the
+    # weights of row 0 makes the two logits equal, and arg-max ties go to the lower index.
+    head = "model.transformer.ff_out.weight" if spec.kind == "llada" else "lm_head.weight"
+    if 0 < spec.mask_id < spec.vocab:
+        sd[head][spec.mask_id] = sd[head][0]
     return sd
