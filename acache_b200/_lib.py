@@ -88,8 +88,58 @@ def stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def check(status: int, what: str):
+# kernels launched through this binding since import (the benchmark reads the difference)
+LAUNCHES = 0
+
+# optional per-operator device timing: name -> [list of (start_event, end_event), work units]
+_TIMERS: dict | None = None
+
+
+def enable_kernel_timers(on: bool = True):
+    """Brackets every call of a timed operator with CUDA events on the launching stream.
+    Off by default; the benchmark turns it on to measure the dominant kernel live."""
+    global _TIMERS
+    _TIMERS = {} if on else None
+
+
+def kernel_timers() -> dict:
+    """name -> (total_ms, launches, work) resolved from the recorded events."""
+    out = {}
+    if _TIMERS:
+        torch.cuda.synchronize()
+        for name, rec in _TIMERS.items():
+            out[name] = (sum(a.elapsed_time(b) for a, b in rec["events"]), len(rec["events"]), rec["work"])
+    return out
+
+
+class timed:
+    """``with timed(name, work): launch`` - a no-op unless timers are enabled."""
+
+    __slots__ = ("name", "work", "start")
+
+    def __init__(self, name: str, work: float = 0.0):
+        self.name, self.work, self.start = name, work, None
+
+    def __enter__(self):
+        if _TIMERS is not None:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.start.record()
+        return self
+
+    def __exit__(self, *exc):
+        if self.start is not None:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            rec = _TIMERS.setdefault(self.name, {"events": [], "work": 0.0})
+            rec["events"].append((self.start, end))
+            rec["work"] += self.work
+        return False
+
+
+def check(status: int, what: str, launches: int = 1):
+    global LAUNCHES
     if status == 0:
+        LAUNCHES += launches
         return
     lib = load()
     msg = lib.acache_status_string(status).decode()

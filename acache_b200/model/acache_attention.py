@@ -20,6 +20,13 @@ from .. import _lib
 from .._lib import check, dtype_code, ptr, stream_ptr
 
 
+# Set by the engine before a forward so that the optional device timers can attribute an
+# attention launch to its phase and to its algorithmic work (bytes for decode, FLOPs for
+# refresh).  They do not influence the computation.
+ATTENTION_PHASE = "refresh"
+ATTENTION_WORK = 0.0
+
+
 def _require_cuda(*tensors):
     for t in tensors:
         assert t is None or t.is_cuda, "operator inputs must live on the GPU"
@@ -82,11 +89,12 @@ def _attention_call(q, out, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, max_q,
     lib = _lib.load()
     if read_slot_mapping is not None:
         rc, rs, rstride, rrows, rdt = _rope_args(rope_cos, rope_sin)
-        check(lib.acache_attention(
-            ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_cache), ptr(v_cache), num_slots, nh, hkv, D,
-            dtype_code(q.dtype), ptr(cu_seqlens_q), ptr(cu_seqlens_k), batch, int(max_q), int(max_k),
-            ptr(read_slot_mapping), float(softmax_scale), int(shared_prefix_len), ptr(shared_kv_lens),
-            ptr(affix_shifts), rc, rs, rstride, rrows, rdt, ptr(flag), stream_ptr()), "acache_attention")
+        with _lib.timed("attention_decode" if ATTENTION_PHASE == "decode" else "attention_refresh", ATTENTION_WORK):
+            check(lib.acache_attention(
+                ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_cache), ptr(v_cache), num_slots, nh, hkv, D,
+                dtype_code(q.dtype), ptr(cu_seqlens_q), ptr(cu_seqlens_k), batch, int(max_q), int(max_k),
+                ptr(read_slot_mapping), float(softmax_scale), int(shared_prefix_len), ptr(shared_kv_lens),
+                ptr(affix_shifts), rc, rs, rstride, rrows, rdt, ptr(flag), stream_ptr()), "acache_attention")
     else:
         check(lib.acache_paged_attention(
             ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_cache), ptr(v_cache), num_slots, nh, hkv, D,

@@ -29,6 +29,7 @@ import torch
 
 from . import _lib, ops
 from .block_manager import BlockManager
+from .model import acache_attention as aa
 from .model.acache_attention import materialize_relocated_affix
 from .model.modeling_common import build_rope_table
 from .sequence import Sequence
@@ -668,6 +669,19 @@ class ModelRunner:
         return admitted
 
     # ------------------------------------------------------------------ step metadata
+    def _note_attention_work(self, phase, q_lens, k_lens):
+        """Algorithmic work of one attention launch of the coming forward, for the optional
+        device timers: FLOPs ``4 q kv nh D`` and bytes (K and V read once per KV head, q read
+        and the output written once)."""
+        nh, hkv, D, _ = self._arch()
+        es = self.kv_cache.element_size()
+        q = np.asarray(q_lens, dtype=np.float64)
+        k = np.asarray(k_lens, dtype=np.float64)
+        flops = float((4.0 * q * k * nh * D).sum())
+        nbytes = float((2.0 * k * hkv * D * es + 2.0 * q * nh * D * es).sum())
+        aa.ATTENTION_PHASE = phase
+        aa.ATTENTION_WORK = nbytes if phase == "decode" else flops
+
     def prepare_block_tables(self, seqs):
         width = max(len(seq.block_table) for seq in seqs)
         table = np.full((len(seqs), width), -1, dtype=np.int32)
@@ -763,6 +777,7 @@ class ModelRunner:
             arrays["shifts"] = np.asarray(shifts, dtype=np.int32)
         dev = self._staging.ship(**arrays)
         self._last_cu_q_host = cu_q
+        self._note_attention_work("refresh", q_lens, k_lens)
         set_context(True, dev["cu_q"], dev["cu_k"], dev["kv_seqlens"], int(q_lens.max()), int(k_lens.max()),
                     dev["slots"], None, True, dev["read"], dev.get("shared_lens"), dev.get("shifts"))
         return dev["input_ids"], dev["positions"], dev["bqs"]
@@ -796,6 +811,7 @@ class ModelRunner:
         if not materialized:
             arrays["shifts"] = np.asarray(shifts, dtype=np.int32)
         dev = self._staging.ship(**arrays)
+        self._note_attention_work("decode", [T] * len(ps), k_lens)
         set_context(False, dev["cu_q"], dev["cu_k"], dev["kv_seqlens"], T, int(k_lens.max()), dev["slots"], None, True,
                     dev["read"], dev.get("shared_lens"), dev.get("shifts"))
         return dev["positions"]

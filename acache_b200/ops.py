@@ -61,7 +61,7 @@ def anchor_importance(q, q_rows, affix_k, affix_shift: int, rope_cos, rope_sin, 
     check(lib.acache_anchor_importance(
         ptr(q), q.stride(0), ptr(q_rows), n_q, nh, hkv, D, dtype_code(q.dtype), ptr(affix_k), affix_k.stride(0), A,
         int(affix_shift), rc, rs, rstride, rrows, rdt, float(scale), ptr(importance), ptr(scratch), scratch.numel(),
-        stream_ptr()), "anchor_importance")
+        stream_ptr()), "anchor_importance", 2)
 
 
 def rope_store(q, k, v, positions, rope_cos, rope_sin, k_cache=None, v_cache=None, slot_mapping=None):
@@ -117,5 +117,5 @@ def transfer_tokens(logits: torch.Tensor, blocks: torch.Tensor, mask_id: int, th
     conf = torch.empty(R, T, dtype=torch.float32, device=blocks.device)
     check(_lib.load().acache_transfer_tokens(ptr(logits), logits.stride(0), logits.shape[1], dtype_code(logits.dtype),
                                              ptr(blocks), R, T, int(mask_id), float(threshold), ptr(x0), ptr(conf),
-                                             stream_ptr()), "transfer_tokens")
+                                             stream_ptr()), "transfer_tokens", 2)
     return x0, conf
