@@ -373,14 +373,6 @@ template <typename T, typename TR> struct PromoteA { using type = float; };
 template <> struct PromoteA<__half, __half> { using type = __half; };
 template <> struct PromoteA<__nv_bfloat16, __nv_bfloat16> { using type = __nv_bfloat16; };
 
-struct AttnArgs {
-  const void* q; int64_t q_stride; void* out; int64_t o_stride; const void* k_cache; const void* v_cache;
-  int64_t num_slots; int n_heads, n_kv_heads, head_dim; const int32_t* cu_q; const int32_t* cu_k; int batch;
-  int max_q; const int32_t* slot_map; const int32_t* block_tables; int table_stride, block_size; float scale;
-  int shared_prefix_len; const int32_t* shared_kv_lens; const int32_t* affix_shifts; const void* rope_cos;
-  const void* rope_sin; int64_t rope_stride; int rope_rows; int32_t* err_flag; cudaStream_t st;
-};
-
 template <typename T, typename TR, int DMAX>
 static int launch_attention_simt(const AttnArgs& a) {
   using TC = typename PromoteA<T, TR>::type;

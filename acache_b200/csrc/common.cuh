@@ -77,6 +77,15 @@ __device__ __forceinline__ float rot_hi(float x1, float x2, float c, float s) {
   return round_to<TC>(__fadd_rn(a, b));
 }
 
+// arguments of one varlen attention launch (shared by the tensor-core and the general kernel)
+struct AttnArgs {
+  const void* q; int64_t q_stride; void* out; int64_t o_stride; const void* k_cache; const void* v_cache;
+  int64_t num_slots; int n_heads, n_kv_heads, head_dim; const int32_t* cu_q; const int32_t* cu_k; int batch;
+  int max_q; const int32_t* slot_map; const int32_t* block_tables; int table_stride, block_size; float scale;
+  int shared_prefix_len; const int32_t* shared_kv_lens; const int32_t* affix_shifts; const void* rope_cos;
+  const void* rope_sin; int64_t rope_stride; int rope_rows; int32_t* err_flag; cudaStream_t st;
+};
+
 // dispatch helpers ---------------------------------------------------------------
 #define ACACHE_DISPATCH_DTYPE(dtype, T, ...)                    \
   switch (dtype) {                                              \

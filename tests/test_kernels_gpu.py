@@ -415,3 +415,75 @@ def test_transfer_tokens_golden_and_random():
     blocks = xb.clone().to(DEV)
     ops.transfer_tokens(lg.to(DEV), blocks, 126336, 0.9)
     assert torch.equal(blocks.cpu(), want)
+
+
+# ----------------------------------------------------------------------------- tensor-core attention
+@pytest.mark.parametrize("dt,nh,hkv,D,q_lens,kv_lens", [
+    (torch.bfloat16, 32, 32, 128, [32, 32, 32], [1216, 1120, 1312]),          # block decode, MHA
+    (torch.bfloat16, 28, 4, 128, [32, 32], [1112, 920]),                      # block decode, GQA 7
+    (torch.bfloat16, 8, 8, 128, [480, 672, 1], [1120, 1312, 65]),             # refresh
+    (torch.float16, 14, 2, 64, [129, 300], [64, 577]),                        # head_dim 64, GQA 7
+    (torch.bfloat16, 4, 4, 128, [5, 0, 9], [3, 10, 0]),                       # empty / tiny requests
+])
+def test_attention_tensor_core_shapes(dt, nh, hkv, D, q_lens, kv_lens):
+    from oracle import attention as oatt
+
+    _lib, ops, aa, att = _ops()
+    g = torch.Generator().manual_seed(11)
+    Bk = 64
+    nb = (sum(kv_lens) + 200) // Bk + 4
+    A = 40
+    shifts = [17, 0, 33][: len(q_lens)]
+    q, kc, vc, cu_q, cu_k, logical, packed, shl = _random_case(g, dt, nh, hkv, D, Bk, nb, q_lens, kv_lens, 0, None)
+    d = lambda x: x.to(DEV)
+    tol = _tol(dt)
+    ref = oatt.acache_attention(q, kc, vc, cu_q, cu_k, logical)
+    got = aa.acache_attention(d(q), d(kc), d(vc), d(cu_q), d(cu_k), d(logical), max_seqlen_q=max(q_lens))
+    live = torch.cat([torch.full((n,), float(k > 0)) for n, k in zip(q_lens, kv_lens)]).bool()
+    assert (got.cpu().float() - ref.float())[live].abs().max() < tol
+    if min(kv_lens) > A + 40:
+        q, kc, vc, cu_q, cu_k, logical, packed, shl = _random_case(g, dt, nh, hkv, D, Bk, nb, q_lens, kv_lens, A, shifts)
+        cos, sin = _rope(2048, D)
+        sh_t = torch.tensor(shifts, dtype=torch.int32)
+        ref = oatt.acache_attention(q, kc, vc, cu_q, cu_k, packed, None, A, shl, sh_t, cos, sin)
+        got = aa.acache_attention(d(q), d(kc), d(vc), d(cu_q), d(cu_k), d(packed), None, A, d(shl), d(sh_t), d(cos),
+                                  d(sin), max_seqlen_q=max(q_lens), max_seqlen_k=max(kv_lens))
+        assert (got.cpu().float() - ref.float()).abs().max() < tol
+    _lib.check_device_errors()
+
+
+def test_attention_tensor_core_growing_scores_and_block_tables():
+    """Scores that grow tile after tile force the accumulator rescale path; K/V addressed
+    through block tables (baseline kernels' form)."""
+    from oracle import attention as oatt
+
+    _lib, ops, aa, att = _ops()
+    g = torch.Generator().manual_seed(12)
+    dt, nh, hkv, D, Bk = torch.bfloat16, 4, 2, 128, 16
+    lens = [700, 333]
+    nblk = [-(-n // Bk) for n in lens]
+    nb = sum(nblk) + 3
+    ids = torch.randperm(nb, generator=g).tolist()
+    bt = torch.full((2, max(nblk)), -1, dtype=torch.int32)
+    o = 0
+    for i, c in enumerate(nblk):
+        bt[i, :c] = torch.tensor(ids[o: o + c], dtype=torch.int32)
+        o += c
+    kc = torch.randn(nb, Bk, hkv, D, generator=g)
+    vc = torch.randn(nb, Bk, hkv, D, generator=g).to(dt)
+    q = torch.randn(sum(lens), nh, D, generator=g).to(dt)
+    # make later keys of request 0 much larger: the running maximum keeps jumping
+    for j in range(lens[0]):
+        kc[bt[0, j // Bk], j % Bk] *= 1.0 + 6.0 * j / lens[0]
+    kc = kc.to(dt)
+    cu = torch.tensor([0, lens[0], sum(lens)], dtype=torch.int32)
+    ref = oatt.baseline_ragged_attention(q, kc, vc, cu, cu, bt)
+    got = aa.baseline_ragged_attention(q.to(DEV), kc.to(DEV), vc.to(DEV), cu.to(DEV), cu.to(DEV), bt.to(DEV),
+                                       max_seqlen_q=max(lens))
+    assert (got.cpu().float() - ref.float()).abs().max() < 2e-2
+    qd = q[:64].reshape(2, 32, nh, D)
+    sl = torch.tensor(lens, dtype=torch.int32)
+    ref = oatt.baseline_decode_attention(qd, kc, vc, sl, bt)
+    got = aa.baseline_decode_attention(qd.to(DEV), kc.to(DEV), vc.to(DEV), sl.to(DEV), bt.to(DEV))
+    assert (got.cpu().float() - ref.float()).abs().max() < 2e-2
+    _lib.check_device_errors()
