@@ -111,6 +111,12 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <typename T> struct Fmt;
 template <> struct Fmt<__half> { static constexpr uint32_t id = 0; };
 template <> struct Fmt<__nv_bfloat16> { static constexpr uint32_t id = 1; };
@@ -255,27 +261,42 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
     if (i < nt0) { j0 = i * BN; j_end = n_shared; }
     else { j0 = n_shared + (i - nt0) * BN; j_end = kv_len; }
   };
-  auto load_kv = [&](int i) {
+  // Slots of a tile are looked up one tile before its copies are issued, so the dependent
+  // global load (slot -> row address) is never on the critical path.
+  constexpr int ITER = BN * CH / NT;   // rows handled per thread and tile
+  constexpr int RPI = NT / CH;         // rows covered per iteration
+  const int my_c = tid % CH, my_r = tid / CH;
+  auto fetch_slots = [&](int i, int32_t* slots) {
     int j0, j_end;
     tile_span(i, j0, j_end);
-    const uint32_t kb = smem_u32(sK) + (i & 1) * KV_BYTES, vb = smem_u32(sV) + (i & 1) * KV_BYTES;
-    for (int id = tid; id < BN * CH; id += NT) {
-      const int r = id / CH, c = id % CH;
-      const int j = j0 + r;
-      bool ok = j < j_end;
-      int64_t slot = 0;
-      if (ok) {
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+      const int j = j0 + my_r + it * RPI;
+      int64_t slot = -1;  // fits 32 bits: the dispatcher refuses larger caches
+      if (j < j_end) {
         if (slot_map) slot = slot_map[kv0 + j];
         else {
           const int blk = block_tables[(int64_t)b * table_stride + j / block_size];
-          slot = blk < 0 ? -1 : (int64_t)blk * block_size + j % block_size;
+          slot = blk < 0 ? -2 : (int64_t)blk * block_size + j % block_size;
         }
-        if (slot < 0 || slot >= num_slots) {
-          if (err_flag) atomicExch(err_flag, 3);
-          ok = false;
-          slot = 0;
-        }
+        if (slot < 0 || slot >= num_slots) slot = -2;  // reported when the copy is issued
       }
+      slots[it] = (int32_t)slot;
+    }
+  };
+  auto load_kv = [&](int i, const int32_t* slots) {
+    int j0, j_end;
+    tile_span(i, j0, j_end);
+    const uint32_t kb = smem_u32(sK) + (i & 1) * KV_BYTES, vb = smem_u32(sV) + (i & 1) * KV_BYTES;
+    const int c = my_c;
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+      const int r = my_r + it * RPI;
+      const int j = j0 + r;
+      int64_t slot = slots[it];
+      if (slot == -2 && err_flag) atomicExch(err_flag, 3);
+      const bool ok = slot >= 0;
+      if (!ok) slot = 0;
       const int64_t off = slot * kv_row + (int64_t)kvh * D + c * (16 / sizeof(T));
       const uint32_t so = swz<D>(BN, r, c);
       cp_async16(vb + so, v_cache + off, ok);
@@ -323,17 +344,27 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
 
   // ---- prologue ------------------------------------------------------------------------
   const bool start_rotated = nt0 > 0;
+  int32_t slots[ITER];
+  fetch_slots(0, slots);
   load_q(start_rotated);
-  load_kv(0);
+  load_kv(0, slots);
   cp_async_commit();
+  if (n_tiles > 1) fetch_slots(1, slots);
 
+  // a warp is live when at least one of its 32 rows is a real (query, head) pair
+  const bool warp_live = m0 + warp * 32 < vrows;
+  if (!warp_live) {  // its rows of P are never written: keep them zero so the MMA reads no junk
+#pragma unroll
+    for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(sP + tid * 128 + (c << 4)) = make_uint4(0, 0, 0, 0);
+  }
   float m_ref = -INFINITY, l_sum = 0.f;
   bool failed = false;
   uint32_t s[64];
 
   for (int i = 0; i < n_tiles; ++i) {
-    if (i + 1 < n_tiles) load_kv(i + 1);
+    if (i + 1 < n_tiles) load_kv(i + 1, slots);
     cp_async_commit();
+    if (i + 2 < n_tiles) fetch_slots(i + 2, slots);
     cp_async_wait<1>();          // tile i (and the query tile) have landed for this thread
     fence_proxy_async();
     tc_fence_before();
@@ -356,52 +387,54 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
     }
     bool ok = mbar_wait(bar_s, (uint32_t)(i & 1));
     tc_fence_after();
-    tmem_ld32(t_lane + kColS, s);
-    tmem_ld32(t_lane + kColS + 32, s + 32);
-    tmem_wait_ld();
-
-    // online softmax of this thread's row, exp2 domain
-    const int valid = j_end - j0;  // >= 1
-    float mx = -INFINITY;
-#pragma unroll
-    for (int c = 0; c < BN; ++c) {
-      const float v = (c < valid) ? __uint_as_float(s[c]) * scale_log2 : -INFINITY;
-      s[c] = __float_as_uint(v);
-      mx = fmaxf(mx, v);
-    }
     // the previous P V product must be done before O is rescaled or P overwritten
     if (i > 0) ok = mbar_wait(bar_o, (uint32_t)((i - 1) & 1)) && ok;
     tc_fence_after();
-    const bool grow = mx > m_ref + 8.0f;  // also true on the first tile (m_ref = -inf)
-    if (__any_sync(0xFFFFFFFFu, grow) && i > 0) {
-      const float f = grow ? exp2f(m_ref - mx) : 1.0f;   // exp2f(-inf) = 0 cannot happen here: m_ref finite for i > 0
-      l_sum *= f;
-      uint32_t o[32];
+    if (warp_live) {  // warps whose 32 rows are all padding skip the softmax (their P rows stay zero)
+      tmem_ld32(t_lane + kColS, s);
+      tmem_ld32(t_lane + kColS + 32, s + 32);
+      tmem_wait_ld();
+      // online softmax of this thread's row, exp2 domain; raw scores are scaled inside the fma
+      const int valid = j_end - j0;  // >= 1
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < BN; ++c) {
+        const float v = (c < valid) ? __uint_as_float(s[c]) : -INFINITY;
+        s[c] = __float_as_uint(v);
+        mx = fmaxf(mx, v);
+      }
+      mx *= scale_log2;
+      const bool grow = mx > m_ref + 8.0f;  // also true on the first tile (m_ref = -inf)
+      if (__any_sync(0xFFFFFFFFu, grow) && i > 0) {
+        const float f = grow ? ex2(m_ref - mx) : 1.0f;
+        l_sum *= f;
+        uint32_t o[32];
 #pragma unroll 1
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        tmem_ld32(t_lane + kColO + c0, o);
-        tmem_wait_ld();
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          tmem_ld32(t_lane + kColO + c0, o);
+          tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * f);
-        tmem_st32(t_lane + kColO + c0, o);
+          for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * f);
+          tmem_st32(t_lane + kColO + c0, o);
+        }
+        tmem_wait_st();
       }
-      tmem_wait_st();
-    }
-    if (grow) m_ref = mx;
-    float rs = 0.f;
+      if (grow) m_ref = mx;
+      float rs = 0.f;
 #pragma unroll
-    for (int c = 0; c < BN; c += 8) {
-      uint32_t w[4];
+      for (int c = 0; c < BN; c += 8) {
+        uint32_t w[4];
 #pragma unroll
-      for (int e = 0; e < 8; e += 2) {
-        const float p0 = exp2f(__uint_as_float(s[c + e]) - m_ref);
-        const float p1 = exp2f(__uint_as_float(s[c + e + 1]) - m_ref);
-        rs += p0 + p1;
-        w[e / 2] = pack2<T>(p0, p1);
+        for (int e = 0; e < 8; e += 2) {
+          const float p0 = ex2(fmaf(__uint_as_float(s[c + e]), scale_log2, -m_ref));
+          const float p1 = ex2(fmaf(__uint_as_float(s[c + e + 1]), scale_log2, -m_ref));
+          rs += p0 + p1;
+          w[e / 2] = pack2<T>(p0, p1);
+        }
+        *reinterpret_cast<uint4*>(sP + tid * 128 + (((c / 8) ^ (tid & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      *reinterpret_cast<uint4*>(sP + tid * 128 + (((c / 8) ^ (tid & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      l_sum += rs;
     }
-    l_sum += rs;
 
     // query tile swap at the partition boundary: every S product against the rotated
     // queries has completed (bar_s of this tile was awaited)
@@ -505,7 +538,7 @@ static int by_dim(const AttnArgs& a) {
 // Declines (ACACHE_EUNSUPPORTED) what this kernel does not cover: fp32 caches, head sizes
 // other than 64/128, unaligned tensors.
 int attention_tc_dispatch(const AttnArgs& a, int dtype, int rope_dtype) {
-  if (dtype == ACACHE_F32) return ACACHE_EUNSUPPORTED;
+  if (dtype == ACACHE_F32 || a.num_slots >= (1ll << 31)) return ACACHE_EUNSUPPORTED;
   if (a.head_dim != 64 && a.head_dim != 128) return ACACHE_EUNSUPPORTED;
   if (!aligned16(a.q) || !aligned16(a.out) || !aligned16(a.k_cache) || !aligned16(a.v_cache)) return ACACHE_EUNSUPPORTED;
   if (a.q_stride % 8 != 0 || a.o_stride % 8 != 0) return ACACHE_EUNSUPPORTED;

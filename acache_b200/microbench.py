@@ -1,0 +1,223 @@
+"""Per-kernel timing at the shapes of the served workloads, with roofline fractions.
+
+    python -m acache_b200.microbench [name ...] [--iters N] [--json]
+
+Each case builds seeded synthetic inputs on the GPU (working sets larger than the 126 MB
+L2 where the kernel is bandwidth-bound, or an L2 flush between iterations), warms up,
+times ``iters`` launches with CUDA events on the launching stream and prints the
+algorithmic bytes or FLOPs per launch, the achieved rate and its fraction of the
+measured peak (``MEASURED_PEAKS.json`` beside the repository root when present).
+It is also the small, single-kernel program used for profiler captures.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+from pathlib import Path
+
+import torch
+
+from . import _lib, ops
+from .model import acache_attention as aa
+from .model import attention as att
+from .model.modeling_common import build_rope_table
+
+ROOT = Path(__file__).resolve().parents[1]
+DEV = "cuda"
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def _time(fn, iters, flush=None, warmup=3):
+    for _ in range(warmup):
+        if flush is not None:
+            flush.zero_()
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / iters * 1e-3
+
+
+def _flush_buffer():
+    return torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+
+
+def case_relocate(L, A, hkv, D, R, dtype, shifts_hi, Bk=256):
+    """Affix relocation + RoPE for R requests: source read once, R rotated copies written."""
+    nb = -(-A // Bk) * (R + 1)
+    k = torch.randn(L, nb * Bk, hkv, D, device=DEV, dtype=dtype)
+    v = torch.randn_like(k)
+    cos, sin = build_rope_table(shifts_hi + 1, D, 500000.0, torch.float32, DEV)
+    g = torch.Generator().manual_seed(0)
+    shifts = torch.randint(1, shifts_hi, (R,), generator=g).to(torch.int32).to(DEV)
+    per = -(-A // Bk)
+    tables = torch.arange(per, per * (R + 1), dtype=torch.int32, device=DEV).view(R, per)
+    es = k.element_size()
+    nbytes = 2 * L * A * hkv * D * es * (1 + R)
+    fn = lambda: aa.relocate_affix_batched(k, v, cos, sin, A, shifts, dst_block_tables=tables, block_size=Bk)
+    return fn, dict(bytes=nbytes, unit_bytes_per_request=4 * L * A * hkv * D * es)
+
+
+def case_store(N, hkv, D, dtype):
+    nb = N // 256 + 2
+    key = torch.randn(N, hkv, D, device=DEV, dtype=dtype)
+    val = torch.randn_like(key)
+    kc = torch.zeros(nb, 256, hkv, D, device=DEV, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    slots = torch.randperm(nb * 256, device=DEV)[:N].to(torch.int32)
+    fn = lambda: att.store_kvcache(key, val, kc, vc, slots)
+    return fn, dict(bytes=4 * N * hkv * D * key.element_size())
+
+
+def case_attention(B, q_len, kv_lo, kv_hi, nh, hkv, D, dtype=torch.bfloat16, affix=0, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    kv_lens = torch.randint(kv_lo, kv_hi + 1, (B,), generator=g).tolist()
+    Bk = 256
+    nb = sum(-(-n // Bk) for n in kv_lens) + 8
+    kc = torch.randn(nb, Bk, hkv, D, device=DEV, dtype=dtype)
+    vc = torch.randn_like(kc)
+    q = torch.randn(B * q_len, nh, D, device=DEV, dtype=dtype)
+    cu_q = torch.arange(0, (B + 1) * q_len, q_len, dtype=torch.int32, device=DEV)
+    cu_k = torch.zeros(B + 1, dtype=torch.int32)
+    cu_k[1:] = torch.cumsum(torch.tensor(kv_lens), 0)
+    maps, blk = [], -(-affix // Bk) if affix else 0
+    for n in kv_lens:
+        own = n - affix
+        c = -(-own // Bk)
+        private = (torch.arange(c * Bk) + blk * Bk)[:own]
+        blk += c
+        maps.append(torch.cat([torch.arange(affix), private]))
+    rsm = torch.cat(maps).to(torch.int32).to(DEV)
+    es = q.element_size()
+    flops = sum(4.0 * q_len * n * nh * D for n in kv_lens)
+    nbytes = sum(2.0 * n * hkv * D * es + 2.0 * q_len * nh * D * es for n in kv_lens)
+    cu_k = cu_k.to(DEV)
+    fn = lambda: aa.acache_attention(q, kc, vc, cu_q, cu_k, rsm, max_seqlen_q=q_len, max_seqlen_k=max(kv_lens))
+    return fn, dict(bytes=nbytes, flops=flops)
+
+
+def case_topk(B, A, k):
+    s = torch.randn(B, A, device=DEV)
+    fn = lambda: ops.anchor_topk(s, k, True)
+    return fn, dict(bytes=B * (4 * A + 8 * k))
+
+
+def case_importance(nq, nh, hkv, D, A, shift):
+    q = torch.randn(nq + 160, nh, D, device=DEV, dtype=torch.bfloat16)
+    rows = torch.arange(160, 160 + nq, dtype=torch.int32, device=DEV)
+    kc = torch.randn(A, hkv, D, device=DEV, dtype=torch.bfloat16)
+    cos, sin = build_rope_table(max(shift + 1, 2), D, 500000.0, torch.float32, DEV)
+    imp = torch.zeros(A, device=DEV)
+    fn = lambda: ops.anchor_importance(q, rows, kc, shift, cos, sin, D ** -0.5, imp)
+    return fn, dict(flops=2.0 * 2 * nh * nq * A * D)  # two passes over the scores
+
+
+def case_transfer(R, T, V):
+    logits = torch.randn(R * T, V, device=DEV, dtype=torch.bfloat16)
+    blocks = torch.full((R, T), 126336, dtype=torch.int64, device=DEV)
+    work = blocks.clone()
+
+    def fn():
+        work.copy_(blocks)
+        ops.transfer_tokens(logits, work, 126336, 0.9)
+
+    return fn, dict(bytes=R * T * V * 2)
+
+
+def case_rope_store(n, nh, hkv, D):
+    qkv = torch.randn(n, (nh + 2 * hkv) * D, device=DEV, dtype=torch.bfloat16)
+    q, k, v = (qkv[:, : nh * D].view(n, nh, D), qkv[:, nh * D: (nh + hkv) * D].view(n, hkv, D),
+               qkv[:, (nh + hkv) * D:].view(n, hkv, D))
+    pos = torch.randint(0, 1300, (n,), device=DEV)
+    cos, sin = build_rope_table(2048, D, 500000.0, torch.float32, DEV)
+    nb = n // 256 + 2
+    kc = torch.zeros(nb, 256, hkv, D, device=DEV, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    slots = torch.randperm(nb * 256, device=DEV)[:n].to(torch.int32)
+    fn = lambda: ops.rope_store(q, k, v, pos, cos, sin, kc, vc, slots)
+    return fn, dict(bytes=n * D * 2 * (2 * nh + 2 * hkv + 2 * hkv + hkv))  # q,k rw; k,v cache w; v r
+
+
+CASES = {
+    # name: (builder, bound)
+    "relocate_cfg1_fp32": (lambda: case_relocate(2, 512, 8, 128, 4, torch.float32, 1024), "hbm"),
+    "relocate_dream_infix": (lambda: case_relocate(28, 600, 4, 128, 32, torch.bfloat16, 128), "hbm"),
+    "relocate_llada_800": (lambda: case_relocate(32, 800, 32, 128, 4, torch.bfloat16, 1024), "hbm"),
+    "relocate_llada_8192_1req": (lambda: case_relocate(8, 8192, 32, 128, 1, torch.bfloat16, 4104), "hbm"),
+    "store_refresh_llada": (lambda: case_store(4 * 576, 32, 128, torch.bfloat16), "hbm"),
+    "rope_store_decode_llada": (lambda: case_rope_store(512, 32, 32, 128), "hbm"),
+    "rope_store_refresh_llada": (lambda: case_rope_store(4 * 576, 32, 32, 128), "hbm"),
+    "attention_decode_llada": (lambda: case_attention(16, 32, 1120, 1312, 32, 32, 128, affix=800), "hbm"),
+    "attention_decode_dream": (lambda: case_attention(32, 32, 920, 1112, 28, 4, 128, affix=600), "hbm"),
+    "attention_decode_long": (lambda: case_attention(64, 8, 9224, 12296, 32, 32, 128, affix=8192), "hbm"),
+    "attention_refresh_llada": (lambda: case_attention(4, 576, 1120, 1312, 32, 32, 128, affix=800), "tensor"),
+    "attention_refresh_long": (lambda: case_attention(2, 3400, 9224, 12296, 32, 32, 128, affix=8192), "tensor"),
+    "attention_prefill_8192": (lambda: case_attention(1, 8192, 8192, 8192, 32, 32, 128), "tensor"),
+    "topk_cfg1": (lambda: case_topk(4, 512, 103), "latency"),
+    "topk_llada_bs16": (lambda: case_topk(16, 800, 160), "latency"),
+    "topk_long_bs64": (lambda: case_topk(64, 8192, 820), "latency"),
+    "importance_llada": (lambda: case_importance(256, 32, 32, 128, 800, 0), "tensor"),
+    "importance_long": (lambda: case_importance(8, 32, 32, 128, 8192, 2000), "tensor"),
+    "transfer_tokens_llada": (lambda: case_transfer(16, 32, 126464), "hbm"),
+}
+
+
+def run(names, iters, as_json=False):
+    hbm, tf, src = peaks()
+    flush = _flush_buffer()
+    results = {}
+    for name in names:
+        build, bound = CASES[name]
+        fn, work = build()
+        sec = _time(fn, iters, flush)
+        rec = dict(us=sec * 1e6, bound=bound)
+        if "bytes" in work:
+            rec["GBps"] = work["bytes"] / sec / 1e9
+            rec["hbm_frac"] = rec["GBps"] / hbm
+        if "flops" in work:
+            rec["TFLOPs"] = work["flops"] / sec / 1e12
+            rec["tensor_frac"] = rec["TFLOPs"] / tf
+        rec.update({k: v for k, v in work.items()})
+        results[name] = rec
+        if not as_json:
+            extra = " ".join(f"{k}={v:.4g}" for k, v in rec.items() if isinstance(v, float))
+            print(f"{name:28s} {extra}  [{bound}, peaks {src}]", flush=True)
+        del fn
+        torch.cuda.empty_cache()
+    _lib.check_device_errors()
+    if as_json:
+        print(json.dumps(dict(peaks=dict(hbm_gbs=hbm, bf16_tflops=tf, source=src), results=results)))
+    return results
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("names", nargs="*")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--json", action="store_true")
+    args = ap.parse_args(argv)
+    names = args.names or list(CASES)
+    for n in names:
+        if n not in CASES:
+            sys.exit(f"unknown case {n}; choose from {', '.join(CASES)}")
+    run(names, args.iters, args.json)
+
+
+if __name__ == "__main__":
+    main()

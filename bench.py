@@ -264,11 +264,15 @@ def run_ours(args):
     e0.record()
     nfe = 0
     recompute_ms, recompute_calls = 0.0, 0
+    sections = {}
     for seqs in prebuilt:
         outs, n = runner.generate_with_acache(seqs)
         nfe += n
         recompute_ms += runner.last_timing.get("cache_forward", 0.0) * 1e3
         recompute_calls += runner.last_timing.get("cache_forward_calls", 0)
+        for k, v in runner.last_timing.items():
+            if isinstance(v, float) and not k.startswith("kv_cache"):
+                sections[k] = sections.get(k, 0.0) + v * 1e3 / args.steps
         assert all(o is not None and len(o) == GEN for o in outs)
     e1.record()
     sync_all()
@@ -329,7 +333,7 @@ def run_ours(args):
             e2e={"value": tokens / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             gpu_launches=launches, roofline=roof, cpu_baseline=cpu,
             anchor_recompute_ms=recompute_ms / max(recompute_calls, 1), nfe_per_step=nfe / args.steps,
-            affix_broadcast_ms=bcast_ms)
+            affix_broadcast_ms=bcast_ms, sections_ms_per_step={k: round(v, 2) for k, v in sections.items()})
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
