@@ -162,7 +162,10 @@ def err_flag(device: torch.device) -> torch.Tensor:
     idx = device.index if device.index is not None else torch.cuda.current_device()
     flag = _err_flags.get(idx)
     if flag is None:
-        flag = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        # made (and later cleared) under inference mode so that it can be reset no matter
+        # whether the caller runs inside or outside of torch.inference_mode()
+        with torch.inference_mode():
+            flag = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
         _err_flags[idx] = flag
     return flag
 
@@ -177,5 +180,6 @@ def check_device_errors(device: torch.device | None = None):
     flag = err_flag(device)
     code = int(flag.item())
     if code:
-        flag.zero_()
+        with torch.inference_mode():
+            flag.zero_()
         raise AcacheError(f"device-side index check failed: {_ERR_TEXT.get(code, code)}")
