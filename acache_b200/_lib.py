@@ -34,6 +34,10 @@ _SIGNATURES = {
     "acache_anchor_importance": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                          c_int64, c_int, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_float,
                                          c_void_p, c_void_p, c_int64, c_void_p]),
+    "acache_anchor_importance_static_scratch_bytes": (c_int64, []),
+    "acache_anchor_importance_static": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                                c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_int64, c_int,
+                                                c_int, c_float, c_void_p, c_void_p]),
     "acache_attention": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int,
                                  c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_int,
                                  c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
@@ -147,6 +151,8 @@ def check(status: int, what: str, launches: int = 1):
         msg += ": " + lib.acache_last_cuda_error().decode()
     if status == -1:
         raise ValueError(f"{what}: {msg}")
+    if status == -4:
+        raise OverflowError(f"{what}: {msg}")
     if status == -2:
         raise NotImplementedError(f"{what}: {msg}")
     raise AcacheError(f"{what}: {msg}")

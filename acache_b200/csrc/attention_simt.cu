@@ -515,3 +515,54 @@ extern "C" int acache_anchor_importance(const void* q, int64_t q_stride, const i
 #undef IMP
   return ACACHE_EINVAL;
 }
+
+// ------------------------------------------------------------------------------------
+// Anchor influence score without any allocation by anybody.
+//
+// Some hosts of this library may not allocate device memory at the moment they need a
+// score: a serving loop that has handed the whole GPU to its own arena (so cudaMalloc
+// fails or blocks), a plugin that is only ever given its input and output buffers, or a
+// latency-critical path where the implicit device synchronisation of cudaMalloc/cudaFree
+// is not acceptable.  For them the per-CTA partial sums live in this fixed array that is
+// part of the library image; every GPU that loads the library carries it until the
+// process exits.
+namespace acache {
+constexpr int64_t kStaticScratchFloats = 2 * 1024 * 1024;  // 8 MiB
+static __device__ __align__(256) float g_importance_scratch[kStaticScratchFloats];
+
+// In host code `g_importance_scratch` is only a handle for the runtime, not an address a
+// kernel can use; the device address is looked up once per device, with that device
+// current, and kept here.
+constexpr int kMaxDevices = 64;
+static float* g_scratch_addr[kMaxDevices] = {};
+}  // namespace acache
+
+extern "C" int64_t acache_anchor_importance_static_scratch_bytes(void) {
+  return acache::kStaticScratchFloats * (int64_t)sizeof(float);
+}
+
+extern "C" int acache_anchor_importance_static(const void* q, int64_t q_stride, const int32_t* q_rows, int n_q_rows,
+                                               int n_heads, int n_kv_heads, int head_dim, int dtype,
+                                               const void* affix_k, int64_t k_slot_stride, int affix_len,
+                                               int affix_shift, const void* rope_cos, const void* rope_sin,
+                                               int64_t rope_row_stride, int rope_rows, int rope_dtype, float scale,
+                                               float* importance, void* stream) {
+  // sizes first: a request that needs more partial-sum space than the fixed array holds is
+  // refused here, before anything touches the device
+  const int64_t need = acache_anchor_importance_scratch_bytes(n_q_rows, n_heads, affix_len);
+  if (need > acache_anchor_importance_static_scratch_bytes()) return ACACHE_ELIMIT;
+  int dev = -1;
+  ACACHE_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return ACACHE_ELIMIT;
+  if (g_scratch_addr[dev] == nullptr) {
+    // first call on this device: resolve the array's device address (no allocation happens;
+    // do this first call outside of any stream capture)
+    float* p = nullptr;
+    ACACHE_CUDA_CHECK(cudaGetSymbolAddress((void**)&p, g_importance_scratch));
+    if (p == nullptr) return ACACHE_ECUDA;
+    g_scratch_addr[dev] = p;
+  }
+  return acache_anchor_importance(q, q_stride, q_rows, n_q_rows, n_heads, n_kv_heads, head_dim, dtype, affix_k,
+                                  k_slot_stride, affix_len, affix_shift, rope_cos, rope_sin, rope_row_stride,
+                                  rope_rows, rope_dtype, scale, importance, g_scratch_addr[dev], need, stream);
+}

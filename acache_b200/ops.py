@@ -64,6 +64,33 @@ def anchor_importance(q, q_rows, affix_k, affix_shift: int, rope_cos, rope_sin, 
         stream_ptr()), "anchor_importance", 2)
 
 
+def anchor_importance_noalloc(q, q_rows, affix_k, affix_shift: int, rope_cos, rope_sin, scale: float, importance):
+    """``anchor_importance`` for callers that may not allocate device memory (a host that owns
+    the whole GPU through its own arena, a plugin that only gets input and output buffers, a
+    loop that cannot take the stall of an allocation).  The per-CTA partial sums go to a fixed
+    8 MiB array inside the library instead of a caller-provided or torch-allocated buffer, and
+    this wrapper itself creates no tensor.  Raises ``OverflowError`` when
+    ``ceil(n_q / 32) * n_heads * affix_len`` floats do not fit that array.  Calls share the
+    array: do not let two of them overlap on different streams.  The first call on a device
+    resolves the array's address and should be made before any stream capture."""
+    assert q.is_cuda and q.dim() == 3 and q.stride(2) == 1 and q.stride(1) == q.shape[2]
+    assert q_rows.dtype == torch.int32 and q_rows.is_cuda
+    assert affix_k.dim() == 3 and affix_k.stride(2) == 1 and affix_k.stride(1) == affix_k.shape[2]
+    assert importance.dtype == torch.float32 and importance.is_contiguous()
+    n_q, (nh, D) = q_rows.numel(), q.shape[1:]
+    A, hkv = affix_k.shape[:2]
+    if n_q == 0 or A == 0:
+        return
+    if affix_shift != 0:
+        rc, rs, rstride, rrows, rdt = ptr(rope_cos), ptr(rope_sin), rope_cos.stride(0), rope_cos.shape[0], dtype_code(rope_cos.dtype)
+    else:
+        rc, rs, rstride, rrows, rdt = None, None, 0, 0, _lib.F32
+    check(_lib.load().acache_anchor_importance_static(
+        ptr(q), q.stride(0), ptr(q_rows), n_q, nh, hkv, D, dtype_code(q.dtype), ptr(affix_k), affix_k.stride(0), A,
+        int(affix_shift), rc, rs, rstride, rrows, rdt, float(scale), ptr(importance), stream_ptr()),
+        "anchor_importance_static", 2)
+
+
 def rope_store(q, k, v, positions, rope_cos, rope_sin, k_cache=None, v_cache=None, slot_mapping=None):
     """Rotates ``q [n, nh, D]`` and ``k [n, Hkv, D]`` in place by table rows
     ``positions`` and scatters the rotated ``k`` and ``v`` to ``slot_mapping``

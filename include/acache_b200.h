@@ -120,6 +120,29 @@ ACACHE_API int acache_anchor_importance(const void* q, int64_t q_stride, const i
                              int64_t rope_row_stride, int rope_rows, int rope_dtype, float scale,
                              float* importance, void* scratch, int64_t scratch_bytes, void* stream);
 
+/* The same computation for callers that cannot provide scratch memory and must not cause an
+ * allocation: hosts that have given the whole device to their own memory arena, plugins that
+ * only ever receive their input and output buffers, and latency-critical loops that cannot
+ * afford the device-wide synchronisation an allocation implies.  This entry point has no
+ * counterpart in the reference.  The partial sums go to a fixed array of
+ * acache_anchor_importance_static_scratch_bytes() bytes (8 MiB) that is part of the library
+ * image on every GPU that loads it; a request whose
+ * acache_anchor_importance_scratch_bytes(n_q_rows, n_heads, affix_len) exceeds that returns
+ * ACACHE_ELIMIT and does nothing.  Neither this call nor anything it calls allocates or frees
+ * memory.  The first call on a device looks the array's device address up (once per device,
+ * for the device current at that time); make that first call before any stream capture.
+ * All calls on a device share the one array and it keeps whatever the last call left in it:
+ * nothing in it needs clearing between calls (every entry that is read was written by the same
+ * call), but two calls whose kernels overlap on the GPU (different streams) race on it -
+ * serialise them.  Results are identical to acache_anchor_importance. */
+ACACHE_API int64_t acache_anchor_importance_static_scratch_bytes(void);
+ACACHE_API int acache_anchor_importance_static(const void* q, int64_t q_stride, const int32_t* q_rows, int n_q_rows,
+                                               int n_heads, int n_kv_heads, int head_dim, int dtype,
+                                               const void* affix_k, int64_t k_slot_stride, int affix_len,
+                                               int affix_shift, const void* rope_cos, const void* rope_sin,
+                                               int64_t rope_row_stride, int rope_rows, int rope_dtype, float scale,
+                                               float* importance, void* stream);
+
 /* ------------------------------------------------------------------ varlen attention, slot map
  * Replaces acache_attention (nano-vdllm/model/acache_attention.py:338-514,643-738):
  * bidirectional attention of ragged queries q[total_q, n_heads, head_dim] (rows q_stride
