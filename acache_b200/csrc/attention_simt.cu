@@ -409,6 +409,12 @@ int attention_simt_dispatch(const AttnArgs& a, int dtype, int rope_dtype) {
   return ACACHE_EINVAL;
 }
 
+// implemented in importance_tc.cu
+int importance_tc_dispatch(const void* q, int64_t q_stride, const int32_t* q_rows, int n_q, int n_heads, int n_kv_heads,
+                           int head_dim, int dtype, const void* affix_k, int64_t k_slot_stride, int affix_len,
+                           int affix_shift, const void* rope_cos, const void* rope_sin, int64_t rope_stride,
+                           int rope_dtype, float scale, float* partial, int* n_partials, cudaStream_t st);
+
 // implemented in attention_tc.cu: returns ACACHE_EUNSUPPORTED when it declines the shape
 int attention_tc_dispatch(const AttnArgs& a, int dtype, int rope_dtype);
 
@@ -503,6 +509,21 @@ extern "C" int acache_anchor_importance(const void* q, int64_t q_stride, const i
   if (head_dim % (2 * E) != 0 || head_dim > 256 || k_slot_stride % E != 0 || !aligned16(affix_k))
     return ACACHE_EUNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
+  {
+    // tensor-core path for bf16/fp16 with head_dim 64/128; it needs no more partial rows than
+    // acache_anchor_importance_scratch_bytes() provides
+    int n_partials = 0;
+    const int rc = importance_tc_dispatch(q, q_stride, q_rows, n_q_rows, n_heads, n_kv_heads, head_dim, dtype, affix_k,
+                                          k_slot_stride, affix_len, affix_shift, rope_cos, rope_sin, rope_row_stride,
+                                          rope_dtype, scale, (float*)scratch, &n_partials, st);
+    if (rc == ACACHE_OK) {
+      importance_reduce_kernel<<<(affix_len + 255) / 256, 256, 0, st>>>((const float*)scratch, n_partials, affix_len,
+                                                                        importance);
+      ACACHE_LAUNCH_CHECK();
+      return ACACHE_OK;
+    }
+    if (rc != ACACHE_EUNSUPPORTED) return rc;
+  }
 #define IMP(T, TR)                                                                                                  \
   return launch_importance<T, TR>(q, q_stride, q_rows, n_q_rows, n_heads, n_kv_heads, head_dim, affix_k,            \
                                   k_slot_stride, affix_len, affix_shift, rope_cos, rope_sin, rope_row_stride,       \
