@@ -21,9 +21,11 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
-// bounded wait: false when the phase did not complete in time
+// bounded wait: false when the phase did not complete within about half a second
+constexpr long long kWaitCycles = 1000000000ll;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t it = 0; it < (1u << 22); ++it) {
+  const long long t0 = clock64();
+  for (uint32_t it = 0;; ++it) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -31,9 +33,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done) : "r"(bar), "r"(parity) : "memory");
     if (done) return true;
-    if (it > 1024) __nanosleep(64);
+    if ((it & 63) == 63) {
+      if (clock64() - t0 > kWaitCycles) return false;
+      __nanosleep(32);
+    }
   }
-  return false;
 }
 
 // shared-memory matrix descriptor, 128-byte swizzle, atoms of 8 rows x 128 B

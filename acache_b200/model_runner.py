@@ -853,14 +853,15 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ generation loops
     @torch.inference_mode()
-    def generate_with_dual_cache(self, prompts):
+    def generate_with_dual_cache(self, prompts, arrival_times=None):
         """No-reuse baseline: every refresh recomputes all tokens of the request
         (reference: model_runner.py:1473-1723)."""
-        return self._generate(prompts, reuse=False)
+        return self._generate(prompts, reuse=False, arrival_times=arrival_times)
 
     @torch.inference_mode()
-    def generate_with_acache(self, prompts):
-        """Generation with affix-KV reuse (reference: model_runner.py:2032-2277)."""
+    def generate_with_acache(self, prompts, arrival_times=None):
+        """Generation with affix-KV reuse (reference: model_runner.py:2032-2277).  With
+        ``arrival_times`` the prompts are served as a request stream (see ``_generate``)."""
         timing = self._new_timing("acache", len(prompts))
         self.last_timing = timing if timing is not None else {}
         prev, self._active_timing = self._active_timing, timing
@@ -872,8 +873,8 @@ class ModelRunner:
             self._active_timing = prev
         if not prefix:
             self._resolve_timing()
-            return self.generate_with_dual_cache(prompts)
-        return self._generate(prompts, reuse=True, prefix=prefix, timing=timing)
+            return self.generate_with_dual_cache(prompts, arrival_times)
+        return self._generate(prompts, reuse=True, prefix=prefix, timing=timing, arrival_times=arrival_times)
 
     def _refresh(self, batched, working_blocks, rows_host, reuse, timing):
         """Refresh forward of the requests in ``rows_host`` (indices into ``batched``) in
@@ -919,7 +920,11 @@ class ModelRunner:
             self._finish_timing(timing, "cache_update", t0)
             reset_context()
 
-    def _generate(self, prompts, reuse, prefix=(), timing=None):
+    def _generate(self, prompts, reuse, prefix=(), timing=None, arrival_times=None):
+        """Continuous-batching loop shared by both generation modes.  ``arrival_times`` (seconds
+        from the start of the call, ascending, one per prompt) turns the hand-over of all prompts
+        up front into a request stream: a request is only admissible once it has arrived, and
+        admission is also attempted at every block boundary, not only when a request retires."""
         cfg = self.config
         dev = self.device
         T, mask_id = cfg.block_length, cfg.mask_id
@@ -936,17 +941,31 @@ class ModelRunner:
         index_of = {seq.seq_id: i for i, seq in enumerate(prompts)}
         next_idx = 0
         batched: list[Sequence] = []
+        t_begin = time.perf_counter()
+        self.last_completion_times = [None] * len(prompts)
+        if arrival_times is not None:
+            assert len(arrival_times) == len(prompts) and list(arrival_times) == sorted(arrival_times)
+
+        def n_visible():
+            if arrival_times is None:
+                return len(prompts)
+            now = time.perf_counter() - t_begin
+            n = next_idx
+            while n < len(prompts) and arrival_times[n] <= now:
+                n += 1
+            return n
 
         def admit(allow_resize):
             nonlocal next_idx
+            visible = prompts if arrival_times is None else prompts[: n_visible()]
             if reuse:
-                new, nxt = self._collect_admissible_sequences(prompts, next_idx, len(batched), max_num_seqs)
+                new, nxt = self._collect_admissible_sequences(visible, next_idx, len(batched), max_num_seqs)
                 n_ok = self._admit_sequences_with_acache(batched, new, prefix, allow_kv_cache_resize=allow_resize)
                 next_idx = nxt - (len(new) - n_ok)
             else:
-                while (next_idx < len(prompts) and len(batched) < max_num_seqs
-                       and self.block_manager.can_allocate(prompts[next_idx])):
-                    seq = prompts[next_idx]
+                while (next_idx < len(visible) and len(batched) < max_num_seqs
+                       and self.block_manager.can_allocate(visible[next_idx])):
+                    seq = visible[next_idx]
                     self.block_manager.allocate(seq)
                     self._record_kv_cache_usage(timing)
                     batched.append(seq)
@@ -954,6 +973,8 @@ class ModelRunner:
 
         try:
             t0 = self._start_timing()
+            if arrival_times is not None and prompts and arrival_times[0] > 0:
+                time.sleep(max(arrival_times[0] - (time.perf_counter() - t_begin), 0.0))
             admit(True)
             self._finish_timing(timing, "scheduler", t0)
             if not batched and prompts:
@@ -968,7 +989,20 @@ class ModelRunner:
             # most block_length steps unless the model keeps predicting the mask token itself
             # (the reference would then spin forever); stop with an error instead.
             steps_on_key, step_cap = 0, 8 * T + 8
-            while batched:
+            while batched or next_idx < len(prompts):
+                if not batched:
+                    # idle replica: wait for the next arrival, then start it like a first batch
+                    if arrival_times is None:
+                        raise RuntimeError("No requests could be admitted under the current KV-cache budget.")
+                    time.sleep(max(arrival_times[next_idx] - (time.perf_counter() - t_begin), 0.0))
+                    admit(True)
+                    if not batched:
+                        raise RuntimeError("No requests could be admitted under the current KV-cache budget.")
+                    working = torch.full((len(batched), T), mask_id, dtype=torch.int64, device=dev)
+                    self._refresh(batched, working, list(range(len(batched))), reuse, timing)
+                    total_nfe += len(batched)
+                    decode_key = None
+                    continue
                 counts = (working == mask_id).sum(dim=1).tolist()  # the step's one host sync
                 self.d2h_bytes += 8 * len(counts)
                 done_rows = [r for r, c in enumerate(counts) if c == 0]
@@ -987,8 +1021,11 @@ class ModelRunner:
                             self.block_manager.deallocate(seq)
                             retired.add(r)
                             outputs[index_of[seq.seq_id]] = seq.generated_token_ids
+                            self.last_completion_times[index_of[seq.seq_id]] = time.perf_counter() - t_begin
                     working[rows_t] = mask_id
-                    if retired:
+                    newcomers = (arrival_times is not None and len(batched) - len(retired) < max_num_seqs
+                                 and n_visible() > next_idx)
+                    if retired or newcomers:
                         keep_rows = [r for r in range(len(batched)) if r not in retired]
                         batched = [batched[r] for r in keep_rows]
                         admit(len(batched) == 0)
@@ -1009,7 +1046,7 @@ class ModelRunner:
                         decode_key = None
                         continue
                 if not batched:
-                    break
+                    continue
                 active = [r for r, c in enumerate(counts) if c > 0]
                 if not active:
                     continue

@@ -280,3 +280,35 @@ def test_anchor_selection_oom_recovery_is_host_side(hf_llada, monkeypatch):
     assert fired and runner.config.num_kvcache_blocks == 24
     for c, seq in zip(cases, seqs):
         assert seq.token_ids == arrays[f"{c['tag']}::tokens"].tolist()
+
+
+def test_request_stream_with_arrival_times_gives_the_same_tokens():
+    """Requests handed over as a stream (arrival times) instead of all at once: admission happens
+    at block boundaries as requests arrive, each request's tokens are unchanged."""
+    from acache_b200.dp import poisson_arrival_times
+    from acache_b200.model_runner import ModelRunner
+    from acache_b200.sequence import Sequence
+    from oracle.engine import generate_with_acache
+    from oracle.models import ArchSpec, OracleModel, random_state_dict
+
+    rng = random.Random(13)
+    arch = ArchSpec("llada", n_layers=2, d_model=64, n_heads=4, n_kv_heads=4, ffn=96, vocab=160, rope_theta=10000.0,
+                    rms_eps=1e-5, act="silu", mask_id=159)
+    weights = random_state_dict(arch, seed=21, std=0.3)
+    A, G, T = 11, 8, 4
+    affix = [rng.randint(1, 150) for _ in range(A)]
+    reqs = _random_requests(rng, arch, 5, A, G, ["prefix", "infix"], affix)
+    oracle = OracleModel(arch, weights, torch.float32)
+    o_req = [dict(tokens=list(r["prompt"]) + [arch.mask_id] * G, affix_start=r["affix_start"], affix_end=r["affix_end"],
+                  generation_start=len(r["prompt"]), gen_length=G) for r in reqs]
+    want, want_nfe, _ = generate_with_acache(oracle, o_req, anchor_ratio=0.3, threshold=0.6, block_length=T)
+    hf_cfg, model = _llada(arch, weights, torch.float32)
+    cfg = _serve_config(hf_cfg, arch, "llada", torch.float32, threshold=0.6, anchor_ratio=0.3, max_num_seqs=3,
+                        num_kvcache_blocks=32, block_length=T, gen_length=G)
+    runner = ModelRunner(model, cfg)
+    seqs = [Sequence(r["prompt"], block_length=T, gen_length=G, cache_block_size=8, mask_id=arch.mask_id,
+                     prompt_affix_start=r["affix_start"], prompt_affix_end=r["affix_end"]) for r in reqs]
+    times = poisson_arrival_times(len(seqs), rate_per_s=40.0, seed=2)
+    outs, nfe = runner.generate_with_acache(seqs, arrival_times=times)
+    assert outs == want and nfe == want_nfe
+    assert all(t is not None and t >= a for t, a in zip(runner.last_completion_times, times))
