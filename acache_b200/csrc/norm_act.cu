@@ -56,6 +56,65 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const T* __restrict__ x, i
   }
 }
 
+// x_new = x + delta (rounded to T, written back in place of x), y = rmsnorm(x_new): the residual
+// add of the previous sub-layer fused into the normalisation that follows it
+template <typename T, int VPT>
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(T* __restrict__ x, int64_t x_stride, const T* __restrict__ delta,
+                                                          int64_t d_stride, const T* __restrict__ w, T* __restrict__ y,
+                                                          int64_t y_stride, int n_cols, float eps) {
+  constexpr int E = 16 / sizeof(T);
+  const int row = blockIdx.x;
+  T* xr = x + (int64_t)row * x_stride;
+  const T* dr = delta + (int64_t)row * d_stride;
+  T* yr = y + (int64_t)row * y_stride;
+  const int nvec = n_cols / E;
+  Vec16<T> v[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * 256;
+    if (c < nvec) {
+      Vec16<T> a, b;
+      a.u = *reinterpret_cast<const uint4*>(xr + (int64_t)c * E);
+      b.u = ld_global_nc(dr + (int64_t)c * E);
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        v[i].e[e] = from_f32<T>(to_f32<T>(a.e[e]) + to_f32<T>(b.e[e]));
+        const float f = to_f32<T>(v[i].e[e]);
+        ss = fmaf(f, f, ss);
+      }
+      *reinterpret_cast<uint4*>(xr + (int64_t)c * E) = v[i].u;
+    }
+  }
+  __shared__ float red[8];
+  __shared__ float s_scale;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < 8; ++i) t += red[i];
+    s_scale = rsqrtf(t / (float)n_cols + eps);
+  }
+  __syncthreads();
+  const float sc = s_scale;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * 256;
+    if (c < nvec) {
+      Vec16<T> wv, o;
+      wv.u = *reinterpret_cast<const uint4*>(w + (int64_t)c * E);
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const float n = round_to<T>(to_f32<T>(v[i].e[e]) * sc);
+        o.e[e] = from_f32<T>(to_f32<T>(wv.e[e]) * n);
+      }
+      *reinterpret_cast<uint4*>(yr + (int64_t)c * E) = o.u;
+    }
+  }
+}
+
 // generic row kernel for widths the register kernel does not cover
 template <typename T>
 __global__ void __launch_bounds__(256) rmsnorm_generic_kernel(const T* __restrict__ x, int64_t x_stride,
@@ -161,6 +220,31 @@ extern "C" int acache_act_mul(const void* gate, const void* up, void* y, int64_t
   if (blocks > kNumSMs * 8) blocks = kNumSMs * 8;
   ACACHE_DISPATCH_DTYPE(dtype, T, {
     act_mul_kernel<T><<<(int)blocks, 256, 0, st>>>((const T*)gate, (const T*)up, (T*)y, n_vec, n, act);
+  });
+  ACACHE_LAUNCH_CHECK();
+  return ACACHE_OK;
+}
+
+extern "C" int acache_add_rmsnorm(void* x, int64_t x_stride, const void* delta, int64_t d_stride, const void* weight,
+                                  void* y, int64_t y_stride, int n_rows, int n_cols, float eps, int dtype,
+                                  void* stream) {
+  if (!dtype_ok(dtype) || n_rows < 0 || n_cols <= 0) return ACACHE_EINVAL;
+  if (n_rows == 0) return ACACHE_OK;
+  if (!x || !delta || !weight || !y) return ACACHE_EINVAL;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int E = 16 / dtype_bytes(dtype);
+  const bool vec = n_cols % E == 0 && x_stride % E == 0 && y_stride % E == 0 && d_stride % E == 0 && aligned16(x) &&
+                   aligned16(y) && aligned16(weight) && aligned16(delta);
+  const int nvec = n_cols / E;
+  if (!vec || nvec > 1024) return ACACHE_EUNSUPPORTED;
+  ACACHE_DISPATCH_DTYPE(dtype, T, {
+    if (nvec <= 256) {
+      add_rmsnorm_kernel<T, 1><<<n_rows, 256, 0, st>>>((T*)x, x_stride, (const T*)delta, d_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps);
+    } else if (nvec <= 512) {
+      add_rmsnorm_kernel<T, 2><<<n_rows, 256, 0, st>>>((T*)x, x_stride, (const T*)delta, d_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps);
+    } else {
+      add_rmsnorm_kernel<T, 4><<<n_rows, 256, 0, st>>>((T*)x, x_stride, (const T*)delta, d_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps);
+    }
   });
   ACACHE_LAUNCH_CHECK();
   return ACACHE_OK;

@@ -39,5 +39,12 @@ class RMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(size, device=device, dtype=dtype))
         self.eps = eps
 
-    def forward(self, x):
-        return ops.rmsnorm(x, self.weight, self.eps)
+    def forward(self, x, delta=None):
+        """``delta`` (optional): a residual update that is added to ``x`` IN PLACE before the
+        normalisation (one fused kernel)."""
+        if delta is None:
+            return ops.rmsnorm(x, self.weight, self.eps)
+        if x.shape[-1] % (16 // x.element_size()) != 0 or x.shape[-1] > 1024 * (16 // x.element_size()):
+            x.add_(delta)  # row shapes the fused kernel does not take
+            return ops.rmsnorm(x, self.weight, self.eps)
+        return ops.add_rmsnorm(x, delta, self.weight, self.eps)

@@ -91,9 +91,12 @@ class DreamDecoderLayer(nn.Module):
         self.input_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps, **kw)
         self.post_attention_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps, **kw)
 
-    def forward(self, x, position_ids, max_pos):
-        x = x + self.self_attn(self.input_layernorm(x), position_ids, max_pos)
-        return x + self.mlp(self.post_attention_layernorm(x))
+    def forward(self, x, position_ids, max_pos, delta=None):
+        """Returns ``(x, delta)``: ``x`` is updated in place, the MLP output is left pending so the
+        next normalisation adds it (residual add fused into the norm kernel)."""
+        h = self.input_layernorm(x, delta)
+        h = self.post_attention_layernorm(x, self.self_attn(h, position_ids, max_pos))
+        return x, self.mlp(h)
 
 
 class DreamBaseModel(nn.Module):
@@ -153,13 +156,15 @@ class DreamModel(nn.Module):
         if max_pos is None:
             max_pos = int(pos.max().item()) + 1
         x = self.model.embed_tokens(ids)
+        delta = None
         for layer in self.model.layers:
-            x = layer(x, pos, max_pos)
+            x, delta = layer(x, pos, max_pos, delta)
         logits = None
         if compute_logits:
             if logits_keep_indices is not None:
                 x = x.index_select(0, logits_keep_indices)
-            logits = self.lm_head(self.model.norm(x))
+                delta = delta.index_select(0, logits_keep_indices) if delta is not None else None
+            logits = self.lm_head(self.model.norm(x, delta))
             if logits_keep_indices is None:
                 logits = logits.view(*shape, -1)
         return SimpleNamespace(logits=logits, hidden_states=None)

@@ -56,12 +56,15 @@ class LLaDALlamaBlock(nn.Module):
             self.q_proj.bias.data, self.k_proj.bias.data, self.v_proj.bias.data = b[:d], b[d:d + kvd], b[d + kvd:]
             self._qkv_b = b
 
-    def forward(self, x: torch.Tensor, position_ids: torch.Tensor, max_pos: int) -> torch.Tensor:
-        """``x [n, d]`` rows of the ragged batch, ``position_ids [n]`` int64."""
+    def forward(self, x: torch.Tensor, position_ids: torch.Tensor, max_pos: int, delta=None):
+        """``x [n, d]`` rows of the ragged batch (updated in place), ``position_ids [n]`` int64;
+        ``delta`` is the previous block's feed-forward output, still to be added to ``x``.
+        Returns ``(x, delta)`` with this block's feed-forward output pending in the same way, so
+        that every residual add is fused into the normalisation that follows it."""
         cfg = self.config
         n = x.shape[0]
         nh, hkv, D = cfg.n_heads, cfg.effective_n_kv_heads, cfg.d_model // cfg.n_heads
-        h = self.attn_norm(x)
+        h = self.attn_norm(x, delta)
         if self._qkv_w is not None:
             qkv = F.linear(h, self._qkv_w, self._qkv_b)
             q, k, v = qkv[:, : nh * D], qkv[:, nh * D: (nh + hkv) * D], qkv[:, (nh + hkv) * D:]
@@ -80,10 +83,8 @@ class LLaDALlamaBlock(nn.Module):
             attn.kv_already_stored = False
         att = attn(q, k, v).reshape(n, nh * D)
         attn.kv_already_stored = False
-        x = x + self.attn_out(att)
-        h = self.ff_norm(x)
-        x = x + self.ff_out(ops.act_mul(self.ff_proj(h), self.up_proj(h), cfg.activation_type))
-        return x
+        h = self.ff_norm(x, self.attn_out(att))
+        return x, self.ff_out(ops.act_mul(self.ff_proj(h), self.up_proj(h), cfg.activation_type))
 
 
 class LLaDAModel(nn.Module):
@@ -115,13 +116,15 @@ class LLaDAModel(nn.Module):
         x = self.transformer["wte"](ids)
         if self.config.input_emb_norm:
             x = x * (self.config.d_model ** 0.5)
+        delta = None
         for block in self.transformer["blocks"]:
-            x = block(x, pos, max_pos)
+            x, delta = block(x, pos, max_pos, delta)
         logits = None
         if compute_logits:
             if logits_keep_indices is not None:
                 x = x.index_select(0, logits_keep_indices)
-            x = self.transformer["ln_f"](x)
+                delta = delta.index_select(0, logits_keep_indices) if delta is not None else None
+            x = self.transformer["ln_f"](x, delta)
             if self.config.weight_tying:
                 logits = F.linear(x, self.transformer["wte"].weight)
             else:

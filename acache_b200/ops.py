@@ -124,6 +124,19 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     return y.view(shape)
 
 
+def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """``x += delta`` (in place, rounded to x.dtype) and returns ``rmsnorm(x)``: the residual add of
+    the previous sub-layer fused into the normalisation that follows it."""
+    shape = x.shape
+    x2, d2 = x.view(-1, shape[-1]), delta.reshape(-1, shape[-1])
+    assert x2.stride(1) == 1 and d2.stride(1) == 1 and x2.shape == d2.shape
+    y = torch.empty_like(x2)
+    check(_lib.load().acache_add_rmsnorm(ptr(x2), x2.stride(0), ptr(d2), d2.stride(0), ptr(weight), ptr(y), y.stride(0),
+                                         x2.shape[0], x2.shape[1], float(eps), dtype_code(x.dtype), stream_ptr()),
+          "add_rmsnorm")
+    return y.view(shape)
+
+
 def act_mul(gate: torch.Tensor, up: torch.Tensor, act: str = "silu") -> torch.Tensor:
     """``act(gate) * up`` (reference: nano-vdllm/model/modeling_llada.py:757-763)."""
     assert gate.shape == up.shape and gate.is_contiguous() and up.is_contiguous()

@@ -182,6 +182,13 @@ ACACHE_API int acache_paged_attention(const void* q, int64_t q_stride, void* out
  * nano-vdllm/model/modeling_dream.py:76-81): y = weight * cast(x_f32 * rsqrt(mean(x_f32^2) + eps)). */
 ACACHE_API int acache_rmsnorm(const void* x, int64_t x_stride, const void* weight, void* y, int64_t y_stride, int n_rows,
                    int n_cols, float eps, int dtype, void* stream);
+/* Residual add fused into the normalisation that follows it (the two eager ops `x = x + delta;
+ * h = norm(x)` of nano-vdllm/model/modeling_llada.py:740-752): x (in place) = x + delta rounded to
+ * `dtype`, y = RMSNorm(x).  Needs 16-byte aligned rows of at most 1024 vectors, else
+ * ACACHE_EUNSUPPORTED. */
+ACACHE_API int acache_add_rmsnorm(void* x, int64_t x_stride, const void* delta, int64_t d_stride, const void* weight,
+                                  void* y, int64_t y_stride, int n_rows, int n_cols, float eps, int dtype,
+                                  void* stream);
 /* y = act(gate) * up, act: 0 = SiLU, 1 = ReLU, 2 = GELU(erf)
  * (nano-vdllm/model/modeling_llada.py:757-763, nano-vdllm/model/modeling_dream.py:297-303). */
 ACACHE_API int acache_act_mul(const void* gate, const void* up, void* y, int64_t n, int act, int dtype, void* stream);

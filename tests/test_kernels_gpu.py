@@ -379,6 +379,19 @@ def test_rmsnorm_matches_reference_flow(cols):
     assert (diff > 0).float().mean() < 0.01
 
 
+def test_add_rmsnorm_equals_add_then_rmsnorm():
+    _lib, ops, aa, att = _ops()
+    g = torch.Generator().manual_seed(18)
+    for cols in (64, 4096, 3584):
+        x = (torch.randn(33, cols, generator=g) * 3).to(torch.bfloat16).to(DEV)
+        d = torch.randn(33, cols, generator=g).to(torch.bfloat16).to(DEV)
+        w = torch.randn(cols, generator=g).to(torch.bfloat16).to(DEV)
+        want_x = x + d
+        want_y = ops.rmsnorm(want_x, w, 1e-5)
+        got_y = ops.add_rmsnorm(x, d, w, 1e-5)
+        assert torch.equal(x, want_x) and torch.equal(got_y, want_y)
+
+
 @pytest.mark.parametrize("act", ["silu", "relu", "gelu"])
 def test_act_mul(act):
     import torch.nn.functional as F
