@@ -29,6 +29,9 @@ _SIGNATURES = {
     "acache_rope_store": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int,
                                   c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p,
                                   c_void_p, c_int64, c_void_p, c_void_p]),
+    "acache_qkv_rope_scatter": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                        c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_int64,
+                                        c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "acache_anchor_topk": (c_int, [c_void_p, c_int, c_int, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "acache_anchor_importance_scratch_bytes": (c_int64, [c_int, c_int, c_int]),
     "acache_anchor_importance": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,

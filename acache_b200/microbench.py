@@ -154,6 +154,28 @@ def case_rope_store(n, nh, hkv, D):
     return fn, dict(bytes=n * D * 2 * (2 * nh + 2 * hkv + 2 * hkv + hkv))  # q,k rw; k,v cache w; v r
 
 
+def case_qkv(n, hidden, nh, hkv, D, fused):
+    import torch.nn.functional as F
+
+    x = torch.randn(n, hidden, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn((nh + 2 * hkv) * D, hidden, device=DEV, dtype=torch.bfloat16) * hidden ** -0.5
+    pos = torch.randint(0, 1300, (n,), device=DEV)
+    cos, sin = build_rope_table(2048, D, 500000.0, torch.float32, DEV)
+    nb = n // 256 + 2
+    kc = torch.zeros(nb, 256, hkv, D, device=DEV, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    slots = torch.randperm(nb * 256, device=DEV)[:n].to(torch.int32)
+
+    def unfused():
+        qkv = F.linear(x, w)
+        q, k, v = (qkv[:, : nh * D].view(n, nh, D), qkv[:, nh * D: (nh + hkv) * D].view(n, hkv, D),
+                   qkv[:, (nh + hkv) * D:].view(n, hkv, D))
+        ops.rope_store(q, k, v, pos, cos, sin, kc, vc, slots)
+
+    fn = (lambda: ops.qkv_rope_scatter(x, w, None, nh, hkv, D, pos, cos, sin, kc, vc, slots)) if fused else unfused
+    return fn, dict(flops=2.0 * n * hidden * (nh + 2 * hkv) * D, bytes=2.0 * (nh + 2 * hkv) * D * hidden)
+
+
 CASES = {
     # name: (builder, bound)
     "relocate_cfg1_fp32": (lambda: case_relocate(2, 512, 8, 128, 4, torch.float32, 1024), "hbm"),
@@ -169,6 +191,12 @@ CASES = {
     "attention_refresh_llada": (lambda: case_attention(4, 576, 1120, 1312, 32, 32, 128, affix=800), "tensor"),
     "attention_refresh_long": (lambda: case_attention(2, 3400, 9224, 12296, 32, 32, 128, affix=8192), "tensor"),
     "attention_prefill_8192": (lambda: case_attention(1, 8192, 8192, 8192, 32, 32, 128), "tensor"),
+    "qkv_fused_decode_llada": (lambda: case_qkv(512, 4096, 32, 32, 128, True), "tensor"),
+    "qkv_cublas_decode_llada": (lambda: case_qkv(512, 4096, 32, 32, 128, False), "tensor"),
+    "qkv_fused_refresh_llada": (lambda: case_qkv(2304, 4096, 32, 32, 128, True), "tensor"),
+    "qkv_cublas_refresh_llada": (lambda: case_qkv(2304, 4096, 32, 32, 128, False), "tensor"),
+    "qkv_fused_decode_dream": (lambda: case_qkv(1024, 3584, 28, 4, 128, True), "tensor"),
+    "qkv_cublas_decode_dream": (lambda: case_qkv(1024, 3584, 28, 4, 128, False), "tensor"),
     "topk_cfg1": (lambda: case_topk(4, 512, 103), "latency"),
     "topk_llada_bs16": (lambda: case_topk(16, 800, 160), "latency"),
     "topk_long_bs64": (lambda: case_topk(64, 8192, 820), "latency"),

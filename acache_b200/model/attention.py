@@ -59,8 +59,9 @@ class Attention(nn.Module):
         if batched:
             bs, seqlen = q.shape[:2]
             q = q.reshape(bs * seqlen, self.num_heads, self.head_dim)
-            k = k.reshape(bs * seqlen, self.num_kv_heads, self.head_dim)
-            v = v.reshape(bs * seqlen, self.num_kv_heads, self.head_dim)
+            if k is not None:  # None: this step's K/V already sit in the cache (fused projection)
+                k = k.reshape(bs * seqlen, self.num_kv_heads, self.head_dim)
+                v = v.reshape(bs * seqlen, self.num_kv_heads, self.head_dim)
         if self.probe:
             # anchor-selection probe: add this layer's influence score of every affix token
             # (reference: nano-vdllm/model_runner.py:730-773)

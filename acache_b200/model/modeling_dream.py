@@ -17,7 +17,7 @@ from .. import ops
 from ..utils import get_context
 from .attention import Attention
 from .configuration import DreamConfig
-from .modeling_common import RMSNorm, RopeCache
+from .modeling_common import RMSNorm, RopeCache, project_qkv
 
 
 class DreamMLP(nn.Module):
@@ -62,21 +62,12 @@ class DreamSdpaAttention(nn.Module):
     def forward(self, x, position_ids, max_pos):
         n = x.shape[0]
         nh, hkv, D = self.num_heads, self.num_key_value_heads, self.head_dim
-        if self._qkv_w is not None:
-            qkv = F.linear(x, self._qkv_w, self._qkv_b)
-            q, k, v = qkv[:, : nh * D], qkv[:, nh * D: (nh + hkv) * D], qkv[:, (nh + hkv) * D:]
-        else:
-            q, k, v = self.q_proj(x), self.k_proj(x), self.v_proj(x)
-        q, k, v = q.view(n, nh, D), k.view(n, hkv, D), v.view(n, hkv, D)
         cos, sin = self.rotary_emb.get(max_pos, x.device)
         ctx = get_context()
         attn = self.attn
-        if attn.k_cache.numel() and ctx.slot_mapping is not None:
-            ops.rope_store(q, k, v, position_ids, cos, sin, attn.k_cache, attn.v_cache, ctx.slot_mapping)
-            attn.kv_already_stored = True
-        else:
-            ops.rope_store(q, k, None, position_ids, cos, sin)
-            attn.kv_already_stored = False
+        if self._qkv_w is None:
+            self.fuse_qkv()
+        q, k, v = project_qkv(x, self._qkv_w, self._qkv_b, nh, hkv, D, position_ids, cos, sin, attn, ctx)
         o = attn(q, k, v).reshape(n, nh * D)
         attn.kv_already_stored = False
         return self.o_proj(o)

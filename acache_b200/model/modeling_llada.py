@@ -19,7 +19,7 @@ from .. import ops
 from ..utils import get_context
 from .attention import Attention
 from .configuration import LLaDAConfig
-from .modeling_common import RMSNorm, RopeCache
+from .modeling_common import RMSNorm, RopeCache, project_qkv
 
 
 class LLaDALlamaBlock(nn.Module):
@@ -65,22 +65,12 @@ class LLaDALlamaBlock(nn.Module):
         n = x.shape[0]
         nh, hkv, D = cfg.n_heads, cfg.effective_n_kv_heads, cfg.d_model // cfg.n_heads
         h = self.attn_norm(x, delta)
-        if self._qkv_w is not None:
-            qkv = F.linear(h, self._qkv_w, self._qkv_b)
-            q, k, v = qkv[:, : nh * D], qkv[:, nh * D: (nh + hkv) * D], qkv[:, (nh + hkv) * D:]
-        else:
-            q, k, v = self.q_proj(h), self.k_proj(h), self.v_proj(h)
-        q, k, v = q.view(n, nh, D), k.view(n, hkv, D), v.view(n, hkv, D)
         cos, sin = self.rotary_emb.get(max_pos, x.device)
         ctx = get_context()
         attn = self.attn
-        if attn.k_cache.numel() and ctx.slot_mapping is not None:
-            # RoPE of q/k and the scatter of k/v into the paged cache in one pass
-            ops.rope_store(q, k, v, position_ids, cos, sin, attn.k_cache, attn.v_cache, ctx.slot_mapping)
-            attn.kv_already_stored = True
-        else:
-            ops.rope_store(q, k, None, position_ids, cos, sin)
-            attn.kv_already_stored = False
+        if self._qkv_w is None:
+            self.fuse_qkv()
+        q, k, v = project_qkv(h, self._qkv_w, self._qkv_b, nh, hkv, D, position_ids, cos, sin, attn, ctx)
         att = attn(q, k, v).reshape(n, nh * D)
         attn.kv_already_stored = False
         h = self.ff_norm(x, self.attn_out(att))

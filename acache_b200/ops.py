@@ -112,6 +112,28 @@ def rope_store(q, k, v, positions, rope_cos, rope_sin, k_cache=None, v_cache=Non
         stream_ptr()), "rope_store")
 
 
+def qkv_rope_scatter(x, w_qkv, bias, n_heads, n_kv_heads, head_dim, positions, rope_cos, rope_sin, k_cache, v_cache,
+                     slot_mapping):
+    """Fused QKV projection + RoPE + K/V scatter of ``x [n, hidden]`` (one tcgen05 GEMM with a
+    fused epilogue, replacing three ``nn.Linear`` calls, the rotary embedding and ``store_kvcache``
+    of the reference block).  Returns the rotated queries ``[n, n_heads, head_dim]``; the rotated
+    keys and the values only exist in the paged cache.  Raises ``NotImplementedError`` for shapes
+    the kernel does not take (the caller then uses the library GEMM + ``rope_store``)."""
+    n, hidden = x.shape
+    assert x.stride(1) == 1 and w_qkv.is_contiguous() and w_qkv.shape == ((n_heads + 2 * n_kv_heads) * head_dim, hidden)
+    assert positions.dtype == torch.int64 and positions.numel() == n
+    assert slot_mapping.dtype == torch.int32 and slot_mapping.numel() == n
+    q = torch.empty(n, n_heads, head_dim, dtype=x.dtype, device=x.device)
+    num_slots = k_cache.numel() // (n_kv_heads * head_dim)
+    flag = _lib.err_flag(x.device)
+    check(_lib.load().acache_qkv_rope_scatter(
+        ptr(x), x.stride(0), n, hidden, ptr(w_qkv), ptr(bias), n_heads, n_kv_heads, head_dim, dtype_code(x.dtype),
+        ptr(positions), ptr(rope_cos), ptr(rope_sin), rope_cos.stride(0), rope_cos.shape[0], dtype_code(rope_cos.dtype),
+        ptr(q), q.stride(0), ptr(k_cache), ptr(v_cache), ptr(slot_mapping), num_slots, ptr(flag), stream_ptr()),
+        "qkv_rope_scatter")
+    return q
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     """``weight * cast(x * rsqrt(mean(x^2) + eps))`` with the mean in fp32
     (reference: nano-vdllm/model/modeling_llada.py:308-323)."""

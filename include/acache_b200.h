@@ -92,6 +92,24 @@ ACACHE_API int acache_rope_store(void* q, int64_t q_stride, void* k, int64_t k_s
                       int64_t rope_row_stride, int rope_rows, int rope_dtype, void* k_cache, void* v_cache,
                       const int32_t* slot_mapping, int64_t num_slots, int32_t* err_flag, void* stream);
 
+/* ------------------------------------------------------------------ fused QKV projection
+ * Replaces, for the rows of one forward, the three projections q_proj / k_proj / v_proj
+ * (nano-vdllm/model/modeling_llada.py:687-704,738; Dream with bias: modeling_dream.py:351-354,
+ * 452-454), the rotary embedding (modeling_llada.py:412-453) and store_kvcache
+ * (model/attention.py:34-41) by ONE tcgen05 GEMM with a fused epilogue:
+ *   [q | k | v] = x[n_rows, hidden] . w_qkv[(n_heads + 2 n_kv_heads) * head_dim, hidden]^T (+ bias)
+ *   q, k rotated by table row positions[i]; q -> out_q[i, :] (rows q_stride apart);
+ *   rotated k and v -> caches at slot_mapping[i] (-1 skips the row's k/v).
+ * Each head's projection is rounded to `dtype` before the rotation, as an unfused GEMM would
+ * leave it.  16-bit dtypes, head_dim 128, hidden a multiple of 64, 16-byte aligned rows; anything
+ * else returns ACACHE_EUNSUPPORTED (use the library GEMM + acache_rope_store then). */
+ACACHE_API int acache_qkv_rope_scatter(const void* x, int64_t x_stride, int n_rows, int hidden, const void* w_qkv,
+                                       const void* bias, int n_heads, int n_kv_heads, int head_dim, int dtype,
+                                       const int64_t* positions, const void* rope_cos, const void* rope_sin,
+                                       int64_t rope_row_stride, int rope_rows, int rope_dtype, void* out_q,
+                                       int64_t q_stride, void* k_cache, void* v_cache, const int32_t* slot_mapping,
+                                       int64_t num_slots, int32_t* err_flag, void* stream);
+
 /* ------------------------------------------------------------------ anchor top-k
  * Replaces torch.topk + sort + add in anchor selection (nano-vdllm/model_runner.py:833-843;
  * llada/generate_ACache.py:225-262).  scores: fp32 [n_rows, row_stride] (first n_cols of

@@ -500,3 +500,51 @@ def test_attention_tensor_core_growing_scores_and_block_tables():
     got = aa.baseline_decode_attention(qd.to(DEV), kc.to(DEV), vc.to(DEV), sl.to(DEV), bt.to(DEV))
     assert (got.cpu().float() - ref.float()).abs().max() < 2e-2
     _lib.check_device_errors()
+
+
+# ----------------------------------------------------------------------------- fused QKV GEMM
+@pytest.mark.parametrize("kind,n,hidden,nh,hkv", [("llada", 300, 512, 4, 4), ("dream", 77, 448, 7, 1),
+                                                   ("llada", 512, 4096, 32, 32)])
+def test_qkv_rope_scatter_matches_unfused_path(kind, n, hidden, nh, hkv):
+    """tcgen05 GEMM with the fused bias + RoPE + cache-scatter epilogue against the unfused
+    sequence (fp32 reference GEMM rounded to bf16, oracle RoPE, oracle scatter).  The only
+    difference allowed is the accumulation order of the projection (bf16 tolerance 2e-2)."""
+    from oracle import kv_ops
+    from oracle.rope import dream_rope_qk, llada_rope_qk
+
+    _lib, ops, aa, att = _ops()
+    g = torch.Generator().manual_seed(20)
+    D, dt = 128, torch.bfloat16
+    N = (nh + 2 * hkv) * D
+    x = torch.randn(n, hidden, generator=g).to(dt)
+    w = (torch.randn(N, hidden, generator=g) * hidden ** -0.5).to(dt)
+    bias = (torch.randn(N, generator=g) * 0.1).to(dt) if kind == "dream" else None
+    pos = torch.randint(0, 900, (n,), generator=g)
+    nb, Bk = n // 64 + 2, 64
+    slots = torch.randperm(nb * Bk, generator=g)[:n].to(torch.int32)
+    slots[3] = -1
+    theta = 500000.0
+    ref = x.float() @ w.float().T
+    if bias is not None:
+        ref = ref + bias.float()
+    ref = ref.to(dt)
+    q_ref, k_ref, v_ref = ref[:, : nh * D].view(n, nh, D), ref[:, nh * D: (nh + hkv) * D].view(n, hkv, D), \
+        ref[:, (nh + hkv) * D:].view(n, hkv, D)
+    if kind == "llada":
+        q_ref, k_ref = llada_rope_qk(q_ref, k_ref, pos, theta)
+        cos, sin = _rope(1024, D, theta, torch.float32)
+    else:
+        q_ref, k_ref = dream_rope_qk(q_ref, k_ref, pos, theta)
+        cos, sin = _rope(1024, D, theta, dt)
+    kc, vc = torch.zeros(nb, Bk, hkv, D, dtype=dt), torch.zeros(nb, Bk, hkv, D, dtype=dt)
+    kv_ops.store_kvcache(k_ref, v_ref, kc, vc, slots)
+    kcd, vcd = torch.zeros_like(kc, device=DEV), torch.zeros_like(vc, device=DEV)
+    q = ops.qkv_rope_scatter(x.to(DEV), w.to(DEV), None if bias is None else bias.to(DEV), nh, hkv, D, pos.to(DEV),
+                             cos.to(DEV), sin.to(DEV), kcd, vcd, slots.to(DEV))
+    tol = 3e-2
+    assert (q.cpu().float() - q_ref.float()).abs().max() < tol
+    assert (kcd.cpu().float() - kc.float()).abs().max() < tol
+    assert (vcd.cpu().float() - vc.float()).abs().max() < tol
+    # rows with slot -1 and unused slots stay untouched
+    assert float(kcd.cpu().float().abs().sum(dim=(-1, -2)).view(-1)[~torch.isin(torch.arange(nb * Bk), slots.long())].sum()) == 0
+    _lib.check_device_errors()
