@@ -111,7 +111,7 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- CPU arm
-def cpu_reference_sample(layers: int = 2, n_requests: int = 2, gen_length: int = BLOCK, seed: int = 0):
+def cpu_reference_sample(layers: int = 2, n_requests: int = 4, gen_length: int = BLOCK, seed: int = 0):
     """The CPU restatement of the reference path (oracle/) on a bounded sample of the
     workload: the LLaDA-8B architecture truncated to ``layers`` layers in fp32, the 800-token
     affix, ``n_requests`` requests, ``gen_length`` generated tokens each (one block).  Time is
@@ -167,7 +167,9 @@ def run_reference(args):
     line = dict(impl="reference", metric="generated tok/s/box LLaDA-8B-arch bs16 affix reuse", value=value, unit="tok/s",
                 n_gpus=args.gpus, steps=steps, warmup=min(args.warmup, 1), ms_per_step=secs * 1e3,
                 higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
-                config={"workload": WORKLOAD, "impl": "CPU restatement of the reference path (oracle/)"},
+                config={"workload": WORKLOAD, "batch_per_gpu": BATCH, "layers": 32, "parallelism": f"dp{args.gpus}",
+                        "l2": "weights (16 GB) and K/V re-read every step exceed the 126 MB L2"},
+                note="CPU restatement of the reference path (oracle/) on the host cores; see cpu_baseline.sample",
                 cpu_baseline=base, e2e={"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 gpu_launches=0)
     print(json.dumps(line))
@@ -296,9 +298,12 @@ def run_ours(args):
     d2h = (runner.d2h_bytes - d2h0) / args.steps
 
     times = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
+    counts = torch.tensor([float(launches), h2d, d2h], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(counts, op=dist.ReduceOp.SUM)
     dev_ms, e2e_ms = times.tolist()
+    launches, h2d, d2h = int(counts[0].item()), counts[1].item(), counts[2].item()
     tokens = args.steps * args.batch * GEN * world
 
     if rank == 0:
