@@ -44,6 +44,11 @@ _SIGNATURES = {
     "acache_attention": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int,
                                  c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_int,
                                  c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
+    "acache_attention_grouped_scratch_bytes": (c_int64, [c_int, c_int, c_int, c_int, c_int]),
+    "acache_attention_grouped": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int,
+                                         c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                                         c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,
+                                         c_int, c_void_p, c_int64, c_void_p, c_void_p]),
     "acache_paged_attention": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int,
                                        c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int,
                                        c_int, c_float, c_void_p, c_void_p]),
@@ -182,7 +187,10 @@ def err_flag(device: torch.device) -> torch.Tensor:
 
 
 _ERR_TEXT = {1: "slot outside the cache", 2: "position outside the RoPE table", 3: "read slot outside the cache",
-             4: "relocation shift outside the RoPE table"}
+             4: "relocation shift outside the RoPE table", 5: "a bounded wait inside a kernel ran out",
+             6: "shared memory of a tensor-core kernel is not 1024-byte aligned",
+             7: "requests of a group do not name the same shared span"}
+ACACHE_EUNSUPPORTED = -2
 
 
 def check_device_errors(device: torch.device | None = None):
@@ -193,4 +201,7 @@ def check_device_errors(device: torch.device | None = None):
     if code:
         with torch.inference_mode():
             flag.zero_()
+        from .model.acache_attention import reset_grouped_scratch
+
+        reset_grouped_scratch()  # its tickets may have been left odd by the failed call
         raise AcacheError(f"device-side index check failed: {_ERR_TEXT.get(code, code)}")

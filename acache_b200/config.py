@@ -36,6 +36,10 @@ class Config:
     kv_cache_dtype: str = "bfloat16"
     # capture the block-decode step in a CUDA graph (same arithmetic, fewer launches)
     use_cuda_graphs: bool = False
+    # block decode: hand attention every request's shared span as the same run of slots (with -1
+    # where an anchor's private copy replaces the shared row) and stage it once per four requests
+    # (same result as the logical order up to the order of the floating-point sums)
+    group_shared_span: bool = True
     # eos id and block size aliases read by the block scheduler
     eos: int = -1
 

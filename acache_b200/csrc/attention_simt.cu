@@ -21,11 +21,13 @@ struct KvAddr {
   __device__ __forceinline__ int64_t slot(int j) const {
     if (slot_map) return slot_map[j];
     const int b = block_table[j / block_size];
-    return b < 0 ? -1 : (int64_t)b * block_size + j % block_size;
+    return b < 0 ? -2 : (int64_t)b * block_size + j % block_size;
   }
 };
 
 // Stage rows [j0, j0 + kBN) of K (optionally rotated) and V into shared memory as fp32.
+// A slot of -1 marks a key that takes no part (its row is zeroed and dead[row] is set);
+// any other slot outside the cache is an error (flagged, treated the same way).
 template <typename T, typename TR, typename TC, bool WITH_V>
 __device__ __forceinline__ void stage_kv_tile(float* Ks, float* Vs, int ldk, int ldv, const T* __restrict__ k_cache,
                                               const T* __restrict__ v_cache, int64_t num_slots, int kv_row,
@@ -33,7 +35,7 @@ __device__ __forceinline__ void stage_kv_tile(float* Ks, float* Vs, int ldk, int
                                               int rot_mode /*0 none, 1 key-side by (j - slot), 2 fixed row*/,
                                               int shared_prefix_len, int fixed_row, const TR* __restrict__ rope_cos,
                                               const TR* __restrict__ rope_sin, int64_t rope_stride, int rope_rows,
-                                              int32_t* err_flag) {
+                                              int32_t* err_flag, int* dead = nullptr) {
   constexpr int E = 16 / sizeof(T);
   const int half = D / 2;
   const int cph = half / E;
@@ -47,10 +49,11 @@ __device__ __forceinline__ void stage_kv_tile(float* Ks, float* Vs, int ldk, int
     if (ok) {
       slot = addr.slot(j);
       if (slot < 0 || slot >= num_slots) {
-        if (err_flag) atomicExch(err_flag, 3);
+        if (slot != -1 && err_flag) atomicExch(err_flag, 3);
         ok = false;
       }
     }
+    if (dead && d == 0) dead[jj] = ok ? 0 : 1;
     if (ok) {
       const T* kp = k_cache + slot * kv_row + head_off + d;
       Vec16<T> a, b;
@@ -143,6 +146,7 @@ __global__ void __launch_bounds__(kThreads) attention_simt_kernel(
   float* Ks = Qr + kBM * ld;        // [kBN][ld]
   float* Vs = Ks + kBN * ld;        // [kBN][D]
   float* Ps = Vs + kBN * D;         // [kBM][kBN+1]
+  int* dead = reinterpret_cast<int*>(Ps + kBM * (kBN + 1));  // [kBN] keys of the tile that take no part
 
   const int b = blockIdx.y, h = blockIdx.z;
   const int q0 = cu_q[b], q_len = cu_q[b + 1] - q0;
@@ -202,14 +206,14 @@ __global__ void __launch_bounds__(kThreads) attention_simt_kernel(
       __syncthreads();
       stage_kv_tile<T, TR, TC, true>(Ks, Vs, ld, D, k_cache, v_cache, num_slots, kv_row, kvh * D, D, addr, j0, j_end,
                                      (relocate && !query_side) ? 1 : 0, shared_prefix_len, 0, rope_cos, rope_sin,
-                                     rope_stride, rope_rows, err_flag);
+                                     rope_stride, rope_rows, err_flag, dead);
       __syncthreads();
       float s[8];
       score_row(Qp, Ks, ld, D, i, g, s);
       float mx = -INFINITY;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
-        s[c] = (j0 + g * 8 + c < j_end) ? s[c] * scale : -INFINITY;
+        s[c] = dead[g * 8 + c] ? -INFINITY : s[c] * scale;
         mx = fmaxf(mx, s[c]);
       }
       mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
@@ -377,7 +381,7 @@ template <typename T, typename TR, int DMAX>
 static int launch_attention_simt(const AttnArgs& a) {
   using TC = typename PromoteA<T, TR>::type;
   const int D = a.head_dim, ld = D + 1;
-  const size_t smem = sizeof(float) * ((size_t)2 * kBM * ld + (size_t)kBN * ld + (size_t)kBN * D + (size_t)kBM * (kBN + 1));
+  const size_t smem = sizeof(float) * ((size_t)2 * kBM * ld + (size_t)kBN * ld + (size_t)kBN * D + (size_t)kBM * (kBN + 1) + kBN);
   auto kern = attention_simt_kernel<T, TR, TC, DMAX>;
   ACACHE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid((a.max_q + kBM - 1) / kBM, a.batch, a.n_heads);
@@ -417,6 +421,9 @@ int importance_tc_dispatch(const void* q, int64_t q_stride, const int32_t* q_row
 
 // implemented in attention_tc.cu: returns ACACHE_EUNSUPPORTED when it declines the shape
 int attention_tc_dispatch(const AttnArgs& a, int dtype, int rope_dtype);
+int attention_split_dispatch(const AttnArgs& a, int dtype, int rope_dtype, int total_q, void* scratch,
+                             int64_t scratch_bytes);
+int64_t attention_split_scratch_bytes(int total_q, int n_heads, int head_dim, int batch, int n_kv_heads);
 
 }  // namespace acache
 
@@ -450,6 +457,34 @@ extern "C" int acache_attention(const void* q, int64_t q_stride, void* out, int6
              shared_kv_lens, affix_shifts, rope_cos, rope_sin, rope_row_stride, rope_rows, err_flag,
              (cudaStream_t)stream};
   return attention_common(a, dtype, rope_dtype);
+}
+
+extern "C" int64_t acache_attention_grouped_scratch_bytes(int total_q, int n_heads, int head_dim, int batch,
+                                                          int n_kv_heads) {
+  return attention_split_scratch_bytes(total_q, n_heads, head_dim, batch, n_kv_heads);
+}
+
+extern "C" int acache_attention_grouped(const void* q, int64_t q_stride, void* out, int64_t o_stride,
+                                        const void* k_cache, const void* v_cache, int64_t num_slots, int n_heads,
+                                        int n_kv_heads, int head_dim, int dtype, const int32_t* cu_seqlens_q,
+                                        const int32_t* cu_seqlens_k, int batch, int total_q, int max_seqlen_q,
+                                        const int32_t* read_slot_mapping, float softmax_scale, int shared_prefix_len,
+                                        const int32_t* shared_kv_lens, const int32_t* affix_shifts,
+                                        const void* rope_cos, const void* rope_sin, int64_t rope_row_stride,
+                                        int rope_rows, int rope_dtype, void* scratch, int64_t scratch_bytes,
+                                        int32_t* err_flag, void* stream) {
+  if (!dtype_ok(dtype) || !dtype_ok(rope_dtype)) return ACACHE_EINVAL;
+  if (batch < 0 || total_q < 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || n_heads % n_kv_heads != 0)
+    return ACACHE_EINVAL;
+  if (batch == 0 || max_seqlen_q <= 0 || total_q == 0) return ACACHE_OK;
+  if (!q || !out || !k_cache || !v_cache || !cu_seqlens_q || !cu_seqlens_k || !read_slot_mapping) return ACACHE_EINVAL;
+  const bool relocate = shared_prefix_len > 0 && affix_shifts != nullptr;
+  if (relocate && (!rope_cos || !rope_sin || rope_rows <= 0)) return ACACHE_EINVAL;
+  AttnArgs a{q, q_stride, out, o_stride, k_cache, v_cache, num_slots, n_heads, n_kv_heads, head_dim, cu_seqlens_q,
+             cu_seqlens_k, batch, max_seqlen_q, read_slot_mapping, nullptr, 0, 1, softmax_scale, shared_prefix_len,
+             shared_kv_lens, affix_shifts, rope_cos, rope_sin, rope_row_stride, rope_rows, err_flag,
+             (cudaStream_t)stream};
+  return attention_split_dispatch(a, dtype, rope_dtype, total_q, scratch, scratch_bytes);
 }
 
 extern "C" int acache_paged_attention(const void* q, int64_t q_stride, void* out, int64_t o_stride,

@@ -4,9 +4,13 @@
 // One CTA (128 threads) = one (request, KV head, tile of 128 "virtual rows").  A virtual
 // row is a (query, head-of-the-GQA-group) pair, so all query heads that share a KV head
 // share one pass over its K/V.  Per tile of 64 keys:
-//   * K and V rows are gathered through the slot map (or block table) with 16-byte
-//     cp.async into shared memory in the 128-byte-swizzled layout the MMA descriptors
-//     expect (double buffered, the next tile is in flight during the current one),
+//   * every warp reads the tile's 64 slot-map entries (two per lane) two tiles ahead; an
+//     entry of -1 is a key that takes no part (its row is zero-filled and its score masked);
+//   * K and V rows are gathered with 16-byte cp.async into shared memory in the
+//     128-byte-swizzled layout the MMA descriptors expect (double buffered, the next tile
+//     is in flight during the current one).  Loads of tile i+1 are issued after the S
+//     product of tile i has been queued and the P V product of tile i-1, the last reader of
+//     the stage they overwrite, has completed;
 //   * S = Q K^T      : tcgen05.mma, A = Q (K-major), B = K rows (K-major), fp32 in TMEM,
 //   * thread t owns row t (TMEM lane t): tcgen05.ld of its 64 scores, online softmax
 //     in the exp2 domain, P written back to shared memory as the A operand,
@@ -16,6 +20,17 @@
 // Query-side relocation: the first shared_kv_lens[b] keys are scored against queries
 // rotated by the inverse shift, then the query tile is swapped for the plain one.
 // Key-side relocation: keys of the shared span are rotated while they are staged.
+//
+// Shared-span grouping (SPLIT = true, block decode): when every request has at most 32
+// virtual rows and the first shared_kv_lens[b] entries of all requests name the same slots
+// (up to holes), the keys are split in two kinds of work items:
+//   A  (4 consecutive requests, KV head): warp w holds the rows of request 4a+w; the shared
+//      span is staged ONCE for the four requests (slot = the union of their entries), each
+//      warp masks its own request's holes;
+//   B  (request, KV head): the request's remaining keys.
+// Each item leaves its unnormalised O, reference maximum and row sum in scratch, then takes a
+// ticket per (request, KV head); the second arrival folds the other part into its own and
+// writes the output, so there is no wait between CTAs and no second kernel.
 // Every mbarrier wait is bounded; on expiry the kernel raises the error flag, frees its
 // TMEM and returns.
 #include "common.cuh"
@@ -28,10 +43,20 @@ namespace tc {
 constexpr int BM = 128;      // virtual rows per CTA
 constexpr int BN = 64;       // keys per tile
 constexpr int NT = 128;      // threads
+constexpr int GROUP = 4;     // requests per shared-span work item (one per warp)
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kColS = 0, kColO = 128;
 
-template <typename T, typename TR, typename TC, int D, bool KEYSIDE>
+struct SplitArgs {
+  int n_items_a;        // work items of kind A = ceil(batch / GROUP) * n_kv_heads
+  int batch;
+  int64_t total_rows;   // total_q * n_heads
+  int32_t* tickets;     // [batch * n_kv_heads], even between launches
+  float* part_ml;       // [2][total_rows][2]  reference maximum (log2 domain) and row sum
+  float* part_o;        // [2][total_rows][D]  unnormalised accumulator
+};
+
+template <typename T, typename TR, typename TC, int D, bool KEYSIDE, bool SPLIT>
 __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
     const T* __restrict__ q, int64_t q_stride, T* __restrict__ out, int64_t o_stride, const T* __restrict__ k_cache,
     const T* __restrict__ v_cache, int64_t num_slots, int n_heads, int n_kv_heads, const int32_t* __restrict__ cu_q,
@@ -39,7 +64,7 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
     int table_stride, int block_size, float scale_log2, int shared_prefix_len,
     const int32_t* __restrict__ shared_kv_lens,
     const int32_t* __restrict__ affix_shifts, const TR* __restrict__ rope_cos, const TR* __restrict__ rope_sin,
-    int64_t rope_stride, int rope_rows, int32_t* err_flag) {
+    int64_t rope_stride, int rope_rows, int32_t* err_flag, SplitArgs sp) {
   constexpr int CH = D * (int)sizeof(T) / 16;     // 16-byte chunks per row
   constexpr int Q_BYTES = BM * D * (int)sizeof(T);
   constexpr int KV_BYTES = BN * D * (int)sizeof(T);
@@ -57,44 +82,77 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
   uint8_t* sP = sV + 2 * KV_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);  // [0] = S done, [1] = O done
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+  // per request of the item (one unless this is a kind-A item): first query row, virtual
+  // rows, first slot-map entry, rotation row
+  int* rq_q0 = reinterpret_cast<int*>(tmem_slot + 1);
+  int* rq_vrows = rq_q0 + GROUP;
+  int* rq_kv0 = rq_vrows + GROUP;
+  int* rq_shift = rq_kv0 + GROUP;
 
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int b = blockIdx.y, kvh = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = n_heads / n_kv_heads;
-  const int q0 = cu_q[b], q_len = cu_q[b + 1] - q0;
-  const int m0 = blockIdx.x * BM;
-  const int vrows = q_len * g;
-  if (m0 >= vrows) return;
-  const int kv0 = cu_k[b], kv_len = max(cu_k[b + 1] - kv0, 0);
   const int kv_row = n_kv_heads * D;
-
   const bool query_side = shared_kv_lens != nullptr && affix_shifts != nullptr;
-  int n_shared = 0, shift = 0;
-  if (query_side) {
-    n_shared = min(max(shared_kv_lens[b], 0), kv_len);
-    shift = affix_shifts[b];
-    if (shift < 0 || shift >= rope_rows) {
-      if (tid == 0 && err_flag) atomicExch(err_flag, 4);
-      n_shared = 0;
+
+  // ---- which work item ----------------------------------------------------------------------
+  int b, kvh, m0;
+  bool kind_a = false;
+  if (SPLIT) {
+    m0 = 0;
+    if ((int)blockIdx.x < sp.n_items_a) {
+      kind_a = true;
+      b = ((int)blockIdx.x / n_kv_heads) * GROUP;
+      kvh = (int)blockIdx.x % n_kv_heads;
+    } else {
+      const int x = (int)blockIdx.x - sp.n_items_a;
+      b = x / n_kv_heads;
+      kvh = x % n_kv_heads;
     }
+  } else {
+    b = blockIdx.y;
+    kvh = blockIdx.z;
+    m0 = blockIdx.x * BM;
   }
-  const int nt0 = (n_shared + BN - 1) / BN;
-  const int nt1 = (kv_len - n_shared + BN - 1) / BN;
+  const int n_req = kind_a ? min(GROUP, sp.batch - b) : 1;
+  if (tid < GROUP) {
+    int q0r = 0, vr = 0, kv0r = 0, sh = 0;
+    if (tid < n_req) {
+      q0r = cu_q[b + tid];
+      vr = (cu_q[b + tid + 1] - q0r) * g;
+      kv0r = cu_k[b + tid];
+      if (query_side) {
+        sh = affix_shifts[b + tid];
+        if (sh < 0 || sh >= rope_rows) {
+          if (err_flag) atomicExch(err_flag, 4);
+          sh = 0;
+        }
+      }
+    }
+    rq_q0[tid] = q0r;
+    rq_vrows[tid] = vr;
+    rq_kv0[tid] = kv0r;
+    rq_shift[tid] = sh;
+  }
+  const int kv0 = cu_k[b], kv_len = max(cu_k[b + 1] - kv0, 0);
+  // shared_kv_lens splits the keys in two runs that are tiled separately; with affix_shifts the
+  // first run is scored against inverse-rotated queries (query-side relocation)
+  int n_shared = 0;
+  if (shared_kv_lens != nullptr) n_shared = min(max(shared_kv_lens[b], 0), kv_len);
+  if (kind_a) {
+    for (int r = 1; r < n_req; ++r)  // grouping contract: one span length for the whole group
+      if (min(max(shared_kv_lens[b + r], 0), max(cu_k[b + r + 1] - cu_k[b + r], 0)) != n_shared) {
+        if (tid == 0 && err_flag) atomicExch(err_flag, 7);
+      }
+  }
+  // tiles of the first run, tiles of the second run (an item of kind A has only the first,
+  // an item of kind B only the second)
+  const int nt0 = (SPLIT && !kind_a) ? 0 : (n_shared + BN - 1) / BN;
+  const int nt1 = (SPLIT && kind_a) ? 0 : (kv_len - n_shared + BN - 1) / BN;
   const int n_tiles = nt0 + nt1;
 
-  // this thread's virtual row
-  const int vr = m0 + tid;
-  const bool row_ok = vr < vrows;
-  const int qi = row_ok ? vr / g : 0;
-  const int head = kvh * g + (row_ok ? vr % g : 0);
-  T* out_row = out + (int64_t)(q0 + qi) * o_stride + (int64_t)head * D;
-
-  if (n_tiles == 0) {  // no keys: zeros
-    if (row_ok) {
-      for (int c = 0; c < CH; ++c) *reinterpret_cast<uint4*>(out_row + c * (16 / sizeof(T))) = make_uint4(0, 0, 0, 0);
-    }
-    return;
-  }
+  // this thread's row: request slot ri of the item, virtual row vr
+  const int ri = kind_a ? warp : 0;
+  const int vr = kind_a ? lane : m0 + tid;
 
   const uint32_t bar_s = smem_u32(&bars[0]), bar_o = smem_u32(&bars[1]);
   if (tid == 0) {
@@ -102,6 +160,26 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
     mbar_init(bar_o, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  __syncthreads();
+  const int my_vrows = rq_vrows[ri];
+  int item_rows = 0;  // rows of the item that exist at all
+#pragma unroll
+  for (int r = 0; r < GROUP; ++r) item_rows = max(item_rows, rq_vrows[r]);
+  if (!kind_a && m0 >= my_vrows) return;
+  if (kind_a && item_rows == 0) return;
+  const bool row_ok = vr < my_vrows;
+  const int qi = row_ok ? vr / g : 0;
+  const int head = kvh * g + (row_ok ? vr % g : 0);
+  const int64_t q_row = (int64_t)rq_q0[ri] + qi;
+  T* out_row = out + q_row * o_stride + (int64_t)head * D;
+
+  if (!SPLIT && n_tiles == 0) {  // no keys: zeros
+    if (row_ok) {
+      for (int c = 0; c < CH; ++c) *reinterpret_cast<uint4*>(out_row + c * (16 / sizeof(T))) = make_uint4(0, 0, 0, 0);
+    }
+    return;
+  }
+
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -117,10 +195,11 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
     // chunk id = it*NT + tid: 16 consecutive threads cover one row
     for (int id = tid; id < BM * CH; id += NT) {
       const int r = id / CH, c = id % CH;
-      const int v = m0 + r;
-      const bool ok = v < vrows;
+      const int rr = kind_a ? (r >> 5) : 0;             // request slot of the row
+      const int v = kind_a ? (r & 31) : m0 + r;
+      const bool ok = v < rq_vrows[rr];
       const int rq = ok ? v / g : 0, rh = kvh * g + (ok ? v % g : 0);
-      const T* src = q + (int64_t)(q0 + rq) * q_stride + (int64_t)rh * D + c * (16 / sizeof(T));
+      const T* src = q + (int64_t)(rq_q0[rr] + rq) * q_stride + (int64_t)rh * D + c * (16 / sizeof(T));
       const uint32_t dst = smem_u32(sQ) + swz<D>(BM, r, c);
       if (!rotated) {
         cp_async16(dst, src, ok);
@@ -134,6 +213,7 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
           a.u = *reinterpret_cast<const uint4*>(src);
           bb.u = *reinterpret_cast<const uint4*>(src + D / 2);
         }
+        const int shift = rq_shift[rr];
         const TR* cr = rope_cos + (int64_t)shift * rope_stride;
         const TR* sr = rope_sin + (int64_t)shift * rope_stride;
         const int d = c * E;
@@ -152,40 +232,77 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
     if (i < nt0) { j0 = i * BN; j_end = n_shared; }
     else { j0 = n_shared + (i - nt0) * BN; j_end = kv_len; }
   };
-  // Slots of a tile are looked up one tile before its copies are issued, so the dependent
-  // global load (slot -> row address) is never on the critical path.
-  constexpr int ITER = BN * CH / NT;   // rows handled per thread and tile
+  // ---- slot lookup -----------------------------------------------------------------------
+  // Entry codes: >= 0 a slot, -1 a key that takes no part, -2 an entry outside the cache
+  // (reported), -3 past the end of the run.  Lane l holds rows l and l + 32 of the tile.
+  constexpr int ITER = BN * CH / NT;   // rows gathered per thread and tile
   constexpr int RPI = NT / CH;         // rows covered per iteration
   const int my_c = tid % CH, my_r = tid / CH;
-  auto fetch_slots = [&](int i, int32_t* slots) {
+  // The words of the slot map (or block table) are only LOADED here, two tiles ahead, and not
+  // looked at before the end of the iteration, so no warp waits for them.
+  constexpr int NR = SPLIT ? GROUP : 1;   // requests whose entries a warp reads
+  auto fetch_raw = [&](int i, int32_t (&raw)[NR][2]) {
     int j0, j_end;
     tile_span(i, j0, j_end);
 #pragma unroll
-    for (int it = 0; it < ITER; ++it) {
-      const int j = j0 + my_r + it * RPI;
-      int64_t slot = -1;  // fits 32 bits: the dispatcher refuses larger caches
-      if (j < j_end) {
-        if (slot_map) slot = slot_map[kv0 + j];
-        else {
-          const int blk = block_tables[(int64_t)b * table_stride + j / block_size];
-          slot = blk < 0 ? -2 : (int64_t)blk * block_size + j % block_size;
-        }
-        if (slot < 0 || slot >= num_slots) slot = -2;  // reported when the copy is issued
+    for (int r = 0; r < NR; ++r) {
+      const int first = (SPLIT && kind_a) ? rq_kv0[r] : kv0;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int j = j0 + h * 32 + lane;
+        int32_t v = 0;
+        if (j < j_end && r < n_req) v = slot_map ? slot_map[first + j] : block_tables[(int64_t)b * table_stride + j / block_size];
+        raw[r][h] = v;
       }
-      slots[it] = (int32_t)slot;
     }
   };
-  auto load_kv = [&](int i, const int32_t* slots) {
+  // e0/e1: the entries the rows are fetched from (kind A: the union over the group's requests);
+  // dead: the rows this warp's own request may not see
+  auto interpret = [&](int i, const int32_t (&raw)[NR][2], int32_t& e0, int32_t& e1, uint32_t& dead_lo,
+                       uint32_t& dead_hi) {
     int j0, j_end;
     tile_span(i, j0, j_end);
+    int32_t uni[2] = {-3, -3}, own[2] = {-3, -3};
+    bool clash = false;
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int j = j0 + h * 32 + lane;
+        int32_t code = -3;
+        if (j < j_end && r < n_req) {
+          int64_t slot = raw[r][h];
+          if (slot_map) {
+            code = slot == -1 ? -1 : ((slot < 0 || slot >= num_slots) ? -2 : (int32_t)slot);
+          } else {
+            slot = slot < 0 ? -2 : slot * block_size + j % block_size;
+            code = (slot < 0 || slot >= num_slots) ? -2 : (int32_t)slot;  // fits 32 bits: the dispatcher refuses larger caches
+          }
+        }
+        clash |= code >= 0 && uni[h] >= 0 && code != uni[h];
+        uni[h] = max(uni[h], code);
+        if (r == ((SPLIT && kind_a) ? warp : 0)) own[h] = code;
+      }
+    }
+    e0 = uni[0];
+    e1 = uni[1];
+    dead_lo = __ballot_sync(0xFFFFFFFFu, own[0] < 0);
+    dead_hi = __ballot_sync(0xFFFFFFFFu, own[1] < 0);
+    if (err_flag) {
+      if (clash) atomicExch(err_flag, 7);  // grouping contract: one span for the whole group
+      if (uni[0] == -2 || uni[1] == -2) atomicExch(err_flag, 3);
+    }
+  };
+  auto load_kv = [&](int i, int32_t e0, int32_t e1) {
     const uint32_t kb = smem_u32(sK) + (i & 1) * KV_BYTES, vb = smem_u32(sV) + (i & 1) * KV_BYTES;
+    int j0, j_end;
+    tile_span(i, j0, j_end);
     const int c = my_c;
 #pragma unroll
     for (int it = 0; it < ITER; ++it) {
       const int r = my_r + it * RPI;
       const int j = j0 + r;
-      int64_t slot = slots[it];
-      if (slot == -2 && err_flag) atomicExch(err_flag, 3);
+      int64_t slot = __shfl_sync(0xFFFFFFFFu, (it * RPI < 32) ? e0 : e1, r & 31);
       const bool ok = slot >= 0;
       if (!ok) slot = 0;
       const int64_t off = slot * kv_row + (int64_t)kvh * D + c * (16 / sizeof(T));
@@ -233,129 +350,141 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
   const uint32_t idesc_s = make_idesc(Fmt<T>::id, 0, BN, BM);
   const uint32_t idesc_o = make_idesc(Fmt<T>::id, 1, D, BM);
 
-  // ---- prologue ------------------------------------------------------------------------
-  const bool start_rotated = nt0 > 0;
-  int32_t slots[ITER];
-  fetch_slots(0, slots);
-  load_q(start_rotated);
-  load_kv(0, slots);
-  cp_async_commit();
-  if (n_tiles > 1) fetch_slots(1, slots);
-
   // a warp is live when at least one of its 32 rows is a real (query, head) pair
-  const bool warp_live = m0 + warp * 32 < vrows;
-  if (!warp_live) {  // its rows of P are never written: keep them zero so the MMA reads no junk
-#pragma unroll
-    for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(sP + tid * 128 + (c << 4)) = make_uint4(0, 0, 0, 0);
-  }
+  const bool warp_live = kind_a ? my_vrows > 0 : m0 + warp * 32 < my_vrows;
   float m_ref = -INFINITY, l_sum = 0.f;
   bool failed = false;
-  uint32_t s[64];
 
-  for (int i = 0; i < n_tiles; ++i) {
-    if (i + 1 < n_tiles) load_kv(i + 1, slots);
+  if (n_tiles > 0) {
+    // ---- prologue ----------------------------------------------------------------------
+    const bool start_rotated = query_side && nt0 > 0;
+    int32_t e_nxt0, e_nxt1, raw[NR][2];
+    uint32_t dead_lo, dead_hi, dead_nxt_lo = 0, dead_nxt_hi = 0;
+    fetch_raw(0, raw);
+    interpret(0, raw, e_nxt0, e_nxt1, dead_lo, dead_hi);
+    load_q(start_rotated);
+    load_kv(0, e_nxt0, e_nxt1);
     cp_async_commit();
-    if (i + 2 < n_tiles) fetch_slots(i + 2, slots);
-    cp_async_wait<1>();          // tile i (and the query tile) have landed for this thread
-    fence_proxy_async();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-
-    int j0, j_end;
-    tile_span(i, j0, j_end);
-    const uint32_t kb = smem_u32(sK) + (i & 1) * KV_BYTES, vb = smem_u32(sV) + (i & 1) * KV_BYTES;
-
-    if (tid == 0) {
-#pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks) {
-        const uint32_t a_off = (ks / 4) * (BM * 128) + (ks % 4) * 32;
-        const uint32_t b_off = (ks / 4) * (BN * 128) + (ks % 4) * 32;
-        mma_ss(tmem_base + kColS, make_desc(smem_u32(sQ) + a_off, 16, 1024), make_desc(kb + b_off, 16, 1024), idesc_s,
-               ks > 0 ? 1u : 0u);
-      }
-      mma_commit(bar_s);
+    if (n_tiles > 1) {
+      fetch_raw(1, raw);
+      interpret(1, raw, e_nxt0, e_nxt1, dead_nxt_lo, dead_nxt_hi);
     }
-    bool ok = mbar_wait(bar_s, (uint32_t)(i & 1));
-    tc_fence_after();
-    // the previous P V product must be done before O is rescaled or P overwritten
-    if (i > 0) ok = mbar_wait(bar_o, (uint32_t)((i - 1) & 1)) && ok;
-    tc_fence_after();
-    if (warp_live) {  // warps whose 32 rows are all padding skip the softmax (their P rows stay zero)
-      tmem_ld32(t_lane + kColS, s);
-      tmem_ld32(t_lane + kColS + 32, s + 32);
-      tmem_wait_ld();
-      // online softmax of this thread's row, exp2 domain; raw scores are scaled inside the fma
-      const int valid = j_end - j0;  // >= 1
-      float mx = -INFINITY;
+    if (!warp_live) {  // its rows of P are never written: keep them zero so the MMA reads no junk
 #pragma unroll
-      for (int c = 0; c < BN; ++c) {
-        const float v = (c < valid) ? __uint_as_float(s[c]) : -INFINITY;
-        s[c] = __float_as_uint(v);
-        mx = fmaxf(mx, v);
-      }
-      mx *= scale_log2;
-      const bool grow = mx > m_ref + 8.0f;  // also true on the first tile (m_ref = -inf)
-      if (__any_sync(0xFFFFFFFFu, grow) && i > 0) {
-        const float f = grow ? ex2(m_ref - mx) : 1.0f;
-        l_sum *= f;
-        uint32_t o[32];
-#pragma unroll 1
-        for (int c0 = 0; c0 < D; c0 += 32) {
-          tmem_ld32(t_lane + kColO + c0, o);
-          tmem_wait_ld();
-#pragma unroll
-          for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * f);
-          tmem_st32(t_lane + kColO + c0, o);
-        }
-        tmem_wait_st();
-      }
-      if (grow) m_ref = mx;
-      float rs = 0.f;
-#pragma unroll
-      for (int c = 0; c < BN; c += 8) {
-        uint32_t w[4];
-#pragma unroll
-        for (int e = 0; e < 8; e += 2) {
-          const float p0 = ex2(fmaf(__uint_as_float(s[c + e]), scale_log2, -m_ref));
-          const float p1 = ex2(fmaf(__uint_as_float(s[c + e + 1]), scale_log2, -m_ref));
-          rs += p0 + p1;
-          w[e / 2] = pack2<T>(p0, p1);
-        }
-        *reinterpret_cast<uint4*>(sP + tid * 128 + (((c / 8) ^ (tid & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-      l_sum += rs;
+      for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(sP + tid * 128 + (c << 4)) = make_uint4(0, 0, 0, 0);
     }
+    uint32_t s[64];
 
-    // query tile swap at the partition boundary: every S product against the rotated
-    // queries has completed (bar_s of this tile was awaited)
-    const bool swap_q = start_rotated && i == nt0 - 1 && nt1 > 0;
-    if (swap_q) {
-      load_q(false);
+    for (int i = 0; i < n_tiles; ++i) {
+      if (i + 2 < n_tiles) fetch_raw(i + 2, raw);   // looked at when the iteration ends
+      cp_async_wait<0>();          // tile i (and the query tile) have landed for this thread
+      fence_proxy_async();
+      tc_fence_before();
+      __syncthreads();
+      tc_fence_after();
+
+      const uint32_t kb = smem_u32(sK) + (i & 1) * KV_BYTES, vb = smem_u32(sV) + (i & 1) * KV_BYTES;
+      if (tid == 0) {
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t a_off = (ks / 4) * (BM * 128) + (ks % 4) * 32;
+          const uint32_t b_off = (ks / 4) * (BN * 128) + (ks % 4) * 32;
+          mma_ss(tmem_base + kColS, make_desc(smem_u32(sQ) + a_off, 16, 1024), make_desc(kb + b_off, 16, 1024), idesc_s,
+                 ks > 0 ? 1u : 0u);
+        }
+        mma_commit(bar_s);
+      }
+      // the previous P V product must be done before its K/V stage is refilled, O is rescaled
+      // or P overwritten
+      bool ok = true;
+      if (i > 0) ok = mbar_wait(bar_o, (uint32_t)((i - 1) & 1));
+      if (i + 1 < n_tiles) load_kv(i + 1, e_nxt0, e_nxt1);
       cp_async_commit();
-      cp_async_wait<0>();
-    }
-    fence_proxy_async();
-    tc_fence_before();
-    if (__syncthreads_or(!ok)) { failed = true; break; }
-    tc_fence_after();
-
-    if (tid == 0) {
+      ok = mbar_wait(bar_s, (uint32_t)(i & 1)) && ok;
+      tc_fence_after();
+      if (warp_live) {  // warps whose 32 rows are all padding skip the softmax (their P rows stay zero)
+        tmem_ld32(t_lane + kColS, s);
+        tmem_ld32(t_lane + kColS + 32, s + 32);
+        tmem_wait_ld();
+        // online softmax of this thread's row, exp2 domain; raw scores are scaled inside the fma
+        float mx = -INFINITY;
 #pragma unroll
-      for (int ks = 0; ks < BN / 16; ++ks) {
-        mma_ss(tmem_base + kColO, make_desc(smem_u32(sP) + ks * 32, 16, 1024),
-               make_desc(vb + ks * 2048, BN * 128, 1024), idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
+        for (int c = 0; c < BN; ++c) {
+          const bool dead = ((c < 32 ? dead_lo : dead_hi) >> (c & 31)) & 1u;
+          const float v = dead ? -INFINITY : __uint_as_float(s[c]);
+          s[c] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
+        mx *= scale_log2;
+        const bool grow = mx > m_ref + 8.0f;  // also true on the first tile with a live key (m_ref = -inf)
+        if (__any_sync(0xFFFFFFFFu, grow) && i > 0) {
+          const float f = grow ? ex2(m_ref - mx) : 1.0f;
+          l_sum *= f;
+          uint32_t o[32];
+#pragma unroll 1
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            tmem_ld32(t_lane + kColO + c0, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * f);
+            tmem_st32(t_lane + kColO + c0, o);
+          }
+          tmem_wait_st();
+        }
+        if (grow) m_ref = mx;
+        const float m_use = m_ref == -INFINITY ? 0.f : m_ref;   // no live key so far: every p is 0
+        float rs = 0.f;
+#pragma unroll
+        for (int c = 0; c < BN; c += 8) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 8; e += 2) {
+            const float p0 = ex2(fmaf(__uint_as_float(s[c + e]), scale_log2, -m_use));
+            const float p1 = ex2(fmaf(__uint_as_float(s[c + e + 1]), scale_log2, -m_use));
+            rs += p0 + p1;
+            w[e / 2] = pack2<T>(p0, p1);
+          }
+          *reinterpret_cast<uint4*>(sP + tid * 128 + (((c / 8) ^ (tid & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        l_sum += rs;
       }
-      mma_commit(bar_o);
+
+      // query tile swap at the partition boundary: every S product against the rotated
+      // queries has completed (bar_s of this tile was awaited)
+      const bool swap_q = start_rotated && i == nt0 - 1 && nt1 > 0;
+      if (swap_q) {
+        load_q(false);
+        cp_async_commit();
+        cp_async_wait<0>();
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      if (__syncthreads_or(!ok)) { failed = true; break; }
+      tc_fence_after();
+
+      if (tid == 0) {
+#pragma unroll
+        for (int ks = 0; ks < BN / 16; ++ks) {
+          mma_ss(tmem_base + kColO, make_desc(smem_u32(sP) + ks * 32, 16, 1024),
+                 make_desc(vb + ks * 2048, BN * 128, 1024), idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
+        }
+        mma_commit(bar_o);
+      }
+      dead_lo = dead_nxt_lo;
+      dead_hi = dead_nxt_hi;
+      if (i + 2 < n_tiles) interpret(i + 2, raw, e_nxt0, e_nxt1, dead_nxt_lo, dead_nxt_hi);
+    }
+
+    if (!failed) {
+      bool ok = mbar_wait(bar_o, (uint32_t)((n_tiles - 1) & 1));
+      tc_fence_after();
+      if (__syncthreads_or(!ok)) failed = true;
     }
   }
 
-  if (!failed) {
-    bool ok = mbar_wait(bar_o, (uint32_t)((n_tiles - 1) & 1));
-    tc_fence_after();
-    if (__syncthreads_or(!ok)) failed = true;
-  }
-  if (!failed) {
+  if (failed) {
+    if (tid == 0 && err_flag) atomicExch(err_flag, 5);
+  } else if (!SPLIT) {
     const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
     uint32_t o[32];
 #pragma unroll 1
@@ -374,8 +503,85 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
         }
       }
     }
-  } else if (tid == 0 && err_flag) {
-    atomicExch(err_flag, 5);
+  } else if (warp_live) {
+    // ---- publish this part, take a ticket, the second arrival folds both parts ------------------
+    // (one party = one warp = the rows of one request and KV head)
+    const int side = kind_a ? 0 : 1;
+    const int64_t grow = q_row * n_heads + head;           // row of the [total_q, n_heads] grid
+    float* my_o = sp.part_o + ((int64_t)side * sp.total_rows + grow) * D;
+    float* my_ml = sp.part_ml + ((int64_t)side * sp.total_rows + grow) * 2;
+    const bool have = n_tiles > 0;                          // otherwise O was never written: it counts as 0
+    uint32_t o[32];
+#pragma unroll 1
+    for (int c0 = 0; c0 < D; c0 += 32) {
+      if (have) {
+        tmem_ld32(t_lane + kColO + c0, o);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) o[c] = 0u;
+      }
+      if (row_ok) {
+#pragma unroll
+        for (int c = 0; c < 32; c += 4)
+          __stcg(reinterpret_cast<uint4*>(my_o + c0 + c), make_uint4(o[c], o[c + 1], o[c + 2], o[c + 3]));
+      }
+    }
+    if (row_ok) __stcg(reinterpret_cast<float2*>(my_ml), make_float2(m_ref, l_sum));
+    __threadfence();
+    __syncwarp();
+    int ticket = 0;
+    if (lane == 0) ticket = atomicAdd(sp.tickets + (int64_t)(b + ri) * n_kv_heads + kvh, 1);
+    ticket = __shfl_sync(0xFFFFFFFFu, ticket, 0);
+    if (ticket & 1) {  // the other part is already in scratch
+      __threadfence();
+      const float* ot_o = sp.part_o + ((int64_t)(1 - side) * sp.total_rows + grow) * D;
+      const float* ot_ml = sp.part_ml + ((int64_t)(1 - side) * sp.total_rows + grow) * 2;
+      float2 ml = make_float2(-INFINITY, 0.f);
+      if (row_ok) ml = __ldcg(reinterpret_cast<const float2*>(ot_ml));
+      const float m_all = fmaxf(m_ref, ml.x);
+      const float w_own = m_ref == -INFINITY ? 0.f : ex2(m_ref - m_all);
+      const float w_oth = ml.x == -INFINITY ? 0.f : ex2(ml.x - m_all);
+      // products and sums are rounded one by one (no fused multiply-add): the result is the same
+      // whichever part arrives second
+      const float l_all = __fadd_rn(__fmul_rn(l_sum, w_own), __fmul_rn(ml.y, w_oth));
+      const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
+      const float a_own = w_own * inv, a_oth = w_oth * inv;
+      auto fold = [&](uint32_t own, float oth) { return __fadd_rn(__fmul_rn(__uint_as_float(own), a_own), __fmul_rn(oth, a_oth)); };
+      // the other part's row is fetched one 32-column chunk ahead of its use
+      float4 x[8], xn[8];
+      auto fetch_other = [&](int c0, float4 (&dst)[8]) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          dst[c] = row_ok ? __ldcg(reinterpret_cast<const float4*>(ot_o + c0 + 4 * c)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      };
+      fetch_other(0, x);
+#pragma unroll 1
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        if (c0 + 32 < D) fetch_other(c0 + 32, xn);
+        if (have) {
+          tmem_ld32(t_lane + kColO + c0, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) o[c] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 8) {
+            const float4 xa = x[c / 4], xb = x[c / 4 + 1];
+            uint4 w;
+            w.x = pack2<T>(fold(o[c], xa.x), fold(o[c + 1], xa.y));
+            w.y = pack2<T>(fold(o[c + 2], xa.z), fold(o[c + 3], xa.w));
+            w.z = pack2<T>(fold(o[c + 4], xb.x), fold(o[c + 5], xb.y));
+            w.w = pack2<T>(fold(o[c + 6], xb.z), fold(o[c + 7], xb.w));
+            *reinterpret_cast<uint4*>(out_row + c0 + c) = w;
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < 8; ++c) x[c] = xn[c];
+      }
+    }
   }
   cp_async_wait<0>();
   tc_fence_before();
@@ -390,38 +596,58 @@ template <> struct PromoteT<__half, __half> { using type = __half; };
 template <> struct PromoteT<__nv_bfloat16, __nv_bfloat16> { using type = __nv_bfloat16; };
 
 template <typename T, typename TR, int D>
-static int launch(const AttnArgs& a) {
+static int launch(const AttnArgs& a, const SplitArgs* split) {
   using TC = typename PromoteT<T, TR>::type;
-  constexpr size_t smem = BM * D * sizeof(T) + 4 * BN * D * sizeof(T) + BM * BN * sizeof(T) + 64;
+  constexpr size_t smem = BM * D * sizeof(T) + 4 * BN * D * sizeof(T) + BM * BN * sizeof(T) + 128;
   const int g = a.n_heads / a.n_kv_heads;
-  dim3 grid((a.max_q * g + BM - 1) / BM, a.batch, a.n_kv_heads);
   const bool relocate = a.shared_prefix_len > 0 && a.affix_shifts != nullptr;
   const bool query_side = relocate && a.shared_kv_lens != nullptr;
   const bool key_side = relocate && !query_side;
-#define ACACHE_TC_LAUNCH(KS)                                                                                          \
+  SplitArgs sp{};
+  dim3 grid((a.max_q * g + BM - 1) / BM, a.batch, a.n_kv_heads);
+  if (split) {
+    sp = *split;
+    grid = dim3(sp.n_items_a + a.batch * a.n_kv_heads, 1, 1);
+  }
+#define ACACHE_TC_LAUNCH(KS, SPL)                                                                                     \
   do {                                                                                                                \
-    auto kern = attention_tc_kernel<T, TR, TC, D, KS>;                                                                \
+    auto kern = attention_tc_kernel<T, TR, TC, D, KS, SPL>;                                                           \
     ACACHE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));            \
     kern<<<grid, NT, smem, a.st>>>((const T*)a.q, a.q_stride, (T*)a.out, a.o_stride, (const T*)a.k_cache,             \
                                    (const T*)a.v_cache, a.num_slots, a.n_heads, a.n_kv_heads, a.cu_q, a.cu_k,         \
                                    a.slot_map, a.block_tables, a.table_stride, a.block_size,                          \
-                                   a.scale * 1.4426950408889634f, a.shared_prefix_len,                                \
-                                   query_side ? a.shared_kv_lens : nullptr, query_side ? a.affix_shifts : nullptr,    \
-                                   (const TR*)a.rope_cos, (const TR*)a.rope_sin, a.rope_stride, a.rope_rows,          \
-                                   a.err_flag);                                                                       \
+                                   a.scale * 1.4426950408889634f, a.shared_prefix_len, a.shared_kv_lens,              \
+                                   relocate ? a.affix_shifts : nullptr, (const TR*)a.rope_cos, (const TR*)a.rope_sin, \
+                                   a.rope_stride, a.rope_rows, a.err_flag, sp);                                       \
   } while (0)
-  if (key_side) ACACHE_TC_LAUNCH(true);
-  else ACACHE_TC_LAUNCH(false);
+  if (split) ACACHE_TC_LAUNCH(false, true);
+  else if (key_side) ACACHE_TC_LAUNCH(true, false);
+  else ACACHE_TC_LAUNCH(false, false);
 #undef ACACHE_TC_LAUNCH
   ACACHE_LAUNCH_CHECK();
   return ACACHE_OK;
 }
 
 template <typename T, typename TR>
-static int by_dim(const AttnArgs& a) {
-  if (a.head_dim == 128) return launch<T, TR, 128>(a);
-  if (a.head_dim == 64) return launch<T, TR, 64>(a);
+static int by_dim(const AttnArgs& a, const SplitArgs* split) {
+  if (a.head_dim == 128) return launch<T, TR, 128>(a, split);
+  if (a.head_dim == 64) return launch<T, TR, 64>(a, split);
   return ACACHE_EUNSUPPORTED;
+}
+
+static int by_dtype(const AttnArgs& a, int dtype, int rope_dtype, const SplitArgs* split) {
+  if (dtype == ACACHE_F32 || a.num_slots >= (1ll << 31)) return ACACHE_EUNSUPPORTED;
+  if (a.head_dim != 64 && a.head_dim != 128) return ACACHE_EUNSUPPORTED;
+  if (!aligned16(a.q) || !aligned16(a.out) || !aligned16(a.k_cache) || !aligned16(a.v_cache)) return ACACHE_EUNSUPPORTED;
+  if (a.q_stride % 8 != 0 || a.o_stride % 8 != 0) return ACACHE_EUNSUPPORTED;
+  if (dtype == ACACHE_BF16) {
+    if (rope_dtype == ACACHE_F32) return by_dim<__nv_bfloat16, float>(a, split);
+    if (rope_dtype == ACACHE_BF16) return by_dim<__nv_bfloat16, __nv_bfloat16>(a, split);
+    return by_dim<__nv_bfloat16, __half>(a, split);
+  }
+  if (rope_dtype == ACACHE_F32) return by_dim<__half, float>(a, split);
+  if (rope_dtype == ACACHE_F16) return by_dim<__half, __half>(a, split);
+  return by_dim<__half, __nv_bfloat16>(a, split);
 }
 
 }  // namespace tc
@@ -429,18 +655,37 @@ static int by_dim(const AttnArgs& a) {
 // Declines (ACACHE_EUNSUPPORTED) what this kernel does not cover: fp32 caches, head sizes
 // other than 64/128, unaligned tensors.
 int attention_tc_dispatch(const AttnArgs& a, int dtype, int rope_dtype) {
-  if (dtype == ACACHE_F32 || a.num_slots >= (1ll << 31)) return ACACHE_EUNSUPPORTED;
-  if (a.head_dim != 64 && a.head_dim != 128) return ACACHE_EUNSUPPORTED;
-  if (!aligned16(a.q) || !aligned16(a.out) || !aligned16(a.k_cache) || !aligned16(a.v_cache)) return ACACHE_EUNSUPPORTED;
-  if (a.q_stride % 8 != 0 || a.o_stride % 8 != 0) return ACACHE_EUNSUPPORTED;
-  if (dtype == ACACHE_BF16) {
-    if (rope_dtype == ACACHE_F32) return tc::by_dim<__nv_bfloat16, float>(a);
-    if (rope_dtype == ACACHE_BF16) return tc::by_dim<__nv_bfloat16, __nv_bfloat16>(a);
-    return tc::by_dim<__nv_bfloat16, __half>(a);
-  }
-  if (rope_dtype == ACACHE_F32) return tc::by_dim<__half, float>(a);
-  if (rope_dtype == ACACHE_F16) return tc::by_dim<__half, __half>(a);
-  return tc::by_dim<__half, __nv_bfloat16>(a);
+  return tc::by_dtype(a, dtype, rope_dtype, nullptr);
+}
+
+// Scratch of the shared-span grouping: tickets (kept even between launches, so the buffer is
+// zeroed once and then reused), then per part and output row the reference maximum, the row
+// sum and the unnormalised accumulator in fp32.
+static int64_t split_ticket_bytes(int batch, int n_kv_heads) {
+  return (((int64_t)batch * n_kv_heads * 4 + 255) / 256) * 256;
+}
+int64_t attention_split_scratch_bytes(int total_q, int n_heads, int head_dim, int batch, int n_kv_heads) {
+  if (total_q <= 0 || n_heads <= 0 || head_dim <= 0 || batch <= 0 || n_kv_heads <= 0) return 0;
+  return split_ticket_bytes(batch, n_kv_heads) + (int64_t)2 * total_q * n_heads * (head_dim + 2) * 4;
+}
+
+// Shared-span grouping; declines what it does not cover (also: relocation on the key side,
+// block tables, more than 32 virtual rows per request, no shared_kv_lens).
+int attention_split_dispatch(const AttnArgs& a, int dtype, int rope_dtype, int total_q, void* scratch,
+                             int64_t scratch_bytes) {
+  if (!a.slot_map || !a.shared_kv_lens) return ACACHE_EUNSUPPORTED;
+  if (a.n_kv_heads <= 0 || a.n_heads % a.n_kv_heads != 0) return ACACHE_EINVAL;
+  if (a.max_q * (a.n_heads / a.n_kv_heads) > 32) return ACACHE_EUNSUPPORTED;
+  const int64_t need = attention_split_scratch_bytes(total_q, a.n_heads, a.head_dim, a.batch, a.n_kv_heads);
+  if (!scratch || scratch_bytes < need || !aligned16(scratch)) return ACACHE_EINVAL;
+  tc::SplitArgs sp;
+  sp.n_items_a = ((a.batch + tc::GROUP - 1) / tc::GROUP) * a.n_kv_heads;
+  sp.batch = a.batch;
+  sp.total_rows = (int64_t)total_q * a.n_heads;
+  sp.tickets = reinterpret_cast<int32_t*>(scratch);
+  sp.part_ml = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + split_ticket_bytes(a.batch, a.n_kv_heads));
+  sp.part_o = sp.part_ml + (int64_t)2 * sp.total_rows * 2;
+  return tc::by_dtype(a, dtype, rope_dtype, &sp);
 }
 
 }  // namespace acache

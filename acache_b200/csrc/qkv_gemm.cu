@@ -14,8 +14,6 @@
 //   warps 2-5   epilogue: thread = row (TMEM lane); both halves (d, d + 64) of a head are in the
 //               same thread, so the rotation needs no exchange; overlaps with the next tile's MMAs.
 // All waits are bounded and watch a CTA-wide abort flag.
-#include <cuda.h>
-
 #include "common.cuh"
 #include "tcgen05.cuh"
 
@@ -47,12 +45,6 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
       __nanosleep(32);
     }
   }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
 }
 
 template <typename T, typename TR, typename TC>
@@ -242,36 +234,9 @@ __global__ void __launch_bounds__(NT, 1) qkv_rope_scatter_kernel(
   }
 }
 
-// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda)
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
-}
-
-// [rows, cols] row-major 16-bit matrix, box = 128 rows x 64 columns, 128-byte swizzle
 static bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t row_stride_elems,
                      int dtype) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)row_stride_elems * 2};
-  cuuint32_t box[2] = {64, 128};
-  cuuint32_t estr[2] = {1, 1};
-  const CUtensorMapDataType dt = dtype == ACACHE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  return fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
-         CUDA_SUCCESS;
+  return make_tensor_map_2d(map, base, rows, cols, row_stride_elems, 128, dtype);
 }
 
 template <typename T, typename TR> struct PromoteQ { using type = float; };

@@ -85,30 +85,46 @@ def case_store(N, hkv, D, dtype):
     return fn, dict(bytes=4 * N * hkv * D * key.element_size())
 
 
-def case_attention(B, q_len, kv_lo, kv_hi, nh, hkv, D, dtype=torch.bfloat16, affix=0, seed=0):
+def case_attention(B, q_len, kv_lo, kv_hi, nh, hkv, D, dtype=torch.bfloat16, affix=0, seed=0, layout="logical",
+                   grouped=False):
+    """``affix`` > 0: slots 0..affix-1 are the shared span, every 5th of its tokens is an anchor
+    with a private copy.  layout "logical": keys in position order (anchors interrupt the span
+    every 5 slots); "runs": the span as one run with holes, then the private slots (what the
+    engine hands over in block decode, together with ``grouped``: the span is staged once per
+    four requests)."""
     g = torch.Generator().manual_seed(seed)
     kv_lens = torch.randint(kv_lo, kv_hi + 1, (B,), generator=g).tolist()
     Bk = 256
-    nb = sum(-(-n // Bk) for n in kv_lens) + 8
+    k_anchor = len(range(2, affix, 5)) if affix else 0
+    nb = sum(-(-(n + k_anchor) // Bk) for n in kv_lens) + 8
     kc = torch.randn(nb, Bk, hkv, D, device=DEV, dtype=dtype)
     vc = torch.randn_like(kc)
     q = torch.randn(B * q_len, nh, D, device=DEV, dtype=dtype)
     cu_q = torch.arange(0, (B + 1) * q_len, q_len, dtype=torch.int32, device=DEV)
-    cu_k = torch.zeros(B + 1, dtype=torch.int32)
-    cu_k[1:] = torch.cumsum(torch.tensor(kv_lens), 0)
-    maps, blk = [], -(-affix // Bk) if affix else 0
+    maps, spans, blk = [], [], -(-affix // Bk) if affix else 0
     for n in kv_lens:
         own = n - affix
-        c = -(-own // Bk)
-        private = (torch.arange(c * Bk) + blk * Bk)[:own]
+        c = -(-(own + k_anchor) // Bk)
+        private = (torch.arange(c * Bk) + blk * Bk)[: own + k_anchor]
         blk += c
-        maps.append(torch.cat([torch.arange(affix), private]))
+        span = torch.arange(affix)
+        if layout == "runs":
+            span[2:affix:5] = -1
+            maps.append(torch.cat([span, private]))
+        else:
+            span[2:affix:5] = private[:k_anchor]
+            maps.append(torch.cat([span, private[k_anchor:]]))
+        spans.append(affix)
+    cu_k = torch.zeros(B + 1, dtype=torch.int32)
+    cu_k[1:] = torch.cumsum(torch.tensor([m.numel() for m in maps]), 0)
     rsm = torch.cat(maps).to(torch.int32).to(DEV)
+    split = torch.tensor(spans, dtype=torch.int32, device=DEV) if (affix and layout == "runs") else None
     es = q.element_size()
     flops = sum(4.0 * q_len * n * nh * D for n in kv_lens)
     nbytes = sum(2.0 * n * hkv * D * es + 2.0 * q_len * nh * D * es for n in kv_lens)
     cu_k = cu_k.to(DEV)
-    fn = lambda: aa.acache_attention(q, kc, vc, cu_q, cu_k, rsm, max_seqlen_q=q_len, max_seqlen_k=max(kv_lens))
+    fn = lambda: aa.acache_attention(q, kc, vc, cu_q, cu_k, rsm, None, 0, split, max_seqlen_q=q_len,
+                                     max_seqlen_k=max(kv_lens), group_shared_span=grouped)
     return fn, dict(bytes=nbytes, flops=flops)
 
 
@@ -185,9 +201,15 @@ CASES = {
     "store_refresh_llada": (lambda: case_store(4 * 576, 32, 128, torch.bfloat16), "hbm"),
     "rope_store_decode_llada": (lambda: case_rope_store(512, 32, 32, 128), "hbm"),
     "rope_store_refresh_llada": (lambda: case_rope_store(4 * 576, 32, 32, 128), "hbm"),
-    "attention_decode_llada": (lambda: case_attention(16, 32, 1120, 1312, 32, 32, 128, affix=800), "hbm"),
+    "attention_decode_llada": (lambda: case_attention(16, 32, 1120, 1312, 32, 32, 128, affix=800, layout="runs",
+                                                      grouped=True), "hbm"),
+    "attention_decode_llada_per_request": (lambda: case_attention(16, 32, 1120, 1312, 32, 32, 128, affix=800), "hbm"),
+    "attention_decode_llada_runs_per_request": (lambda: case_attention(16, 32, 1120, 1312, 32, 32, 128, affix=800,
+                                                                       layout="runs"), "hbm"),
     "attention_decode_dream": (lambda: case_attention(32, 32, 920, 1112, 28, 4, 128, affix=600), "hbm"),
-    "attention_decode_long": (lambda: case_attention(64, 8, 9224, 12296, 32, 32, 128, affix=8192), "hbm"),
+    "attention_decode_long": (lambda: case_attention(64, 8, 9224, 12296, 32, 32, 128, affix=8192, layout="runs",
+                                                     grouped=True), "hbm"),
+    "attention_decode_long_per_request": (lambda: case_attention(64, 8, 9224, 12296, 32, 32, 128, affix=8192), "hbm"),
     "attention_refresh_llada": (lambda: case_attention(4, 576, 1120, 1312, 32, 32, 128, affix=800), "tensor"),
     "attention_refresh_long": (lambda: case_attention(2, 3400, 9224, 12296, 32, 32, 128, affix=8192), "tensor"),
     "attention_prefill_8192": (lambda: case_attention(1, 8192, 8192, 8192, 32, 32, 128), "tensor"),

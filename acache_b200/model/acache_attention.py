@@ -80,7 +80,7 @@ def relocate_affix_batched(k_cache, v_cache, rope_cos, rope_sin, affix_len: int,
 
 def _attention_call(q, out, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, max_q, max_k, softmax_scale, *,
                     read_slot_mapping=None, block_tables=None, shared_prefix_len=0, shared_kv_lens=None,
-                    affix_shifts=None, rope_cos=None, rope_sin=None):
+                    affix_shifts=None, rope_cos=None, rope_sin=None, group_shared_span=False):
     total_q, nh, D = q.shape
     hkv = k_cache.shape[-2]
     num_slots = k_cache.numel() // (hkv * D)
@@ -90,6 +90,18 @@ def _attention_call(q, out, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, max_q,
     if read_slot_mapping is not None:
         rc, rs, rstride, rrows, rdt = _rope_args(rope_cos, rope_sin)
         with _lib.timed("attention_decode" if ATTENTION_PHASE == "decode" else "attention_refresh", ATTENTION_WORK):
+            if group_shared_span and shared_kv_lens is not None:
+                need = lib.acache_attention_grouped_scratch_bytes(total_q, nh, D, batch, hkv)
+                scratch = _grouped_scratch(q.device, need)
+                status = lib.acache_attention_grouped(
+                    ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_cache), ptr(v_cache), num_slots, nh, hkv, D,
+                    dtype_code(q.dtype), ptr(cu_seqlens_q), ptr(cu_seqlens_k), batch, total_q, int(max_q),
+                    ptr(read_slot_mapping), float(softmax_scale), int(shared_prefix_len), ptr(shared_kv_lens),
+                    ptr(affix_shifts), rc, rs, rstride, rrows, rdt, ptr(scratch), scratch.numel(), ptr(flag),
+                    stream_ptr())
+                if status != _lib.ACACHE_EUNSUPPORTED:
+                    check(status, "acache_attention_grouped")
+                    return
             check(lib.acache_attention(
                 ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_cache), ptr(v_cache), num_slots, nh, hkv, D,
                 dtype_code(q.dtype), ptr(cu_seqlens_q), ptr(cu_seqlens_k), batch, int(max_q), int(max_k),
@@ -101,6 +113,25 @@ def _attention_call(q, out, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, max_q,
             dtype_code(q.dtype), ptr(cu_seqlens_q), ptr(cu_seqlens_k), batch, int(max_q), int(max_k),
             ptr(block_tables), block_tables.stride(0), k_cache.shape[1], float(softmax_scale), ptr(flag),
             stream_ptr()), "paged_attention")
+
+
+_GROUPED_SCRATCH: dict = {}
+
+
+def _grouped_scratch(device, nbytes: int) -> torch.Tensor:
+    """Per-device scratch of ``acache_attention_grouped``: zeroed when it is created or grown and
+    after a reported device error (its tickets must start even), otherwise reused as it is."""
+    key = (device.type, device.index)
+    buf = _GROUPED_SCRATCH.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=device)
+        _GROUPED_SCRATCH[key] = buf
+    return buf
+
+
+def reset_grouped_scratch():
+    """Forget the scratch buffers (the next call allocates zeroed ones)."""
+    _GROUPED_SCRATCH.clear()
 
 
 def _check_qkv(q, k_cache, v_cache):
@@ -117,9 +148,14 @@ def _max_len(cu):
 
 def acache_attention(q, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, read_slot_mapping, softmax_scale=None,
                      shared_prefix_len: int = 0, shared_kv_lens=None, affix_shifts=None, rope_cos=None, rope_sin=None,
-                     *, max_seqlen_q: int | None = None, max_seqlen_k: int | None = None):
+                     *, max_seqlen_q: int | None = None, max_seqlen_k: int | None = None,
+                     group_shared_span: bool = False):
     """Bidirectional varlen attention through a flat slot map (reference:
-    acache_attention.py:643-738)."""
+    acache_attention.py:643-738).  An entry of -1 in ``read_slot_mapping`` is a key that takes
+    no part; ``shared_kv_lens`` without relocation only splits the keys into two runs.
+    ``group_shared_span``: the caller guarantees that the first ``shared_kv_lens[b]`` entries of
+    all requests name the same slots up to holes; block decode then stages that span once per
+    four requests (falls back to the plain kernel for shapes the grouped one declines)."""
     _check_qkv(q, k_cache, v_cache)
     _require_cuda(cu_seqlens_q, cu_seqlens_k, read_slot_mapping)
     batch = cu_seqlens_q.numel() - 1
@@ -141,11 +177,13 @@ def acache_attention(q, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, read_slot_
         if shared_kv_lens is not None:
             assert shared_kv_lens.is_cuda and shared_kv_lens.numel() == batch
     else:
-        shared_prefix_len, shared_kv_lens, affix_shifts, rope_cos, rope_sin = 0, None, None, None, None
+        # shared_kv_lens alone stays: it only splits the keys into two separately tiled runs
+        shared_prefix_len, affix_shifts, rope_cos, rope_sin = 0, None, None, None
     out = torch.empty_like(q)
     _attention_call(q, out, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k or 0,
                     softmax_scale, read_slot_mapping=read_slot_mapping, shared_prefix_len=shared_prefix_len,
-                    shared_kv_lens=shared_kv_lens, affix_shifts=affix_shifts, rope_cos=rope_cos, rope_sin=rope_sin)
+                    shared_kv_lens=shared_kv_lens, affix_shifts=affix_shifts, rope_cos=rope_cos, rope_sin=rope_sin,
+                    group_shared_span=group_shared_span)
     return out
 
 

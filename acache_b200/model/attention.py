@@ -78,7 +78,8 @@ class Attention(nn.Module):
                 q, k_cache, v_cache, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.read_slot_mapping, self.scale,
                 self.shared_prefix_len, ctx.shared_kv_lens, ctx.affix_shifts,
                 self.relocation_rope_cos if relocating else None, self.relocation_rope_sin if relocating else None,
-                max_seqlen_q=ctx.max_seqlen_q or None, max_seqlen_k=ctx.max_seqlen_k or None)
+                max_seqlen_q=ctx.max_seqlen_q or None, max_seqlen_k=ctx.max_seqlen_k or None,
+                group_shared_span=ctx.group_shared_span)
         elif ctx.is_caching:
             o = baseline_ragged_attention(q, k_cache, v_cache, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.block_tables,
                                           self.scale, max_seqlen_q=ctx.max_seqlen_q or None)

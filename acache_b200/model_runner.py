@@ -53,6 +53,34 @@ def attention_read_layout(seq, use_query_relocation: bool, shared_prefix_len: in
     return shared + private, len(shared)
 
 
+def attention_read_runs(seq):
+    """Read order in which every request names the shared span the same way: the affix span
+    as the consecutive slots it occupies, with -1 (a key that takes no part) where a private
+    copy replaces the shared row, then those private copies, then the request's other tokens.
+    Attention does not depend on the order of the keys, so the result equals the logical
+    order of ``seq.read_slot_map`` up to the order of the floating-point sums; block decode
+    can then stage the span once for several requests.
+    Returns ``(slots, affix_len, first slot of the span)``."""
+    cached = getattr(seq, "_read_runs", None)
+    if cached is not None and cached[0] is seq.read_slot_map:
+        return cached[1:]
+    slots = np.asarray(seq.read_slot_map, dtype=np.int32)
+    a0, a1 = seq.affix_start, seq.affix_end
+    if not getattr(seq, "acache_enabled", False) or a1 <= a0:
+        out = (slots, 0, -1)
+    else:
+        span = slots[a0:a1].copy()
+        start = span - np.arange(a1 - a0, dtype=np.int32)      # slot the run would start at
+        values, counts = np.unique(start, return_counts=True)
+        first = int(values[np.argmax(counts)])
+        moved = start != first
+        private = span[moved]
+        span[moved] = -1
+        out = (np.concatenate([span, private, slots[:a0], slots[a1:]]), a1 - a0, first)
+    seq._read_runs = (seq.read_slot_map,) + out
+    return out
+
+
 class _Staging:
     """Packs the integer arrays of one step into a single pinned buffer and moves it to
     the device with one copy; returns typed device views."""
@@ -306,6 +334,22 @@ class ModelRunner:
 
     def _attention_read_layout(self, seq, use_query_relocation: bool):
         return attention_read_layout(seq, use_query_relocation, self.shared_prefix_len)
+
+    def _group_shared_span(self, seqs, relocation_materialized: bool, use_query_relocation: bool) -> bool:
+        """Whether block decode hands attention the run layout (``attention_read_runs``) and lets it
+        stage the shared span once per group of requests.  Needs: every request reads the same
+        span (same first slot, same length); at most 32 (query, head-in-group) rows per request;
+        no key-side relocation, which rotates a key by (its index - its slot) and so needs the
+        logical order."""
+        if not getattr(self.config, "group_shared_span", True) or len(seqs) < 2:
+            return False
+        if self._affix_relocation_enabled and not relocation_materialized and not use_query_relocation:
+            return False
+        n_heads, n_kv, _, _ = self._arch()
+        if self.config.block_length * (n_heads // n_kv) > 32 or self.kv_cache.dtype == torch.float32:
+            return False
+        spans = {attention_read_runs(s)[1:] for s in seqs}
+        return len(spans) == 1 and next(iter(spans))[0] > 0
 
     def _use_query_side_affix_relocation(self, relocation_materialized: bool):
         return self._affix_relocation_enabled and not relocation_materialized and self.config.max_num_seqs != 1
@@ -792,21 +836,22 @@ class ModelRunner:
         materialized = all(getattr(s, "relocated_affix_materialized", False) for s in ps)
         use_qr = self._use_query_side_affix_relocation(materialized)
         k_lens = np.asarray([len(s) for s in ps], dtype=np.int64)
-        cu_k = np.zeros(len(ps) + 1, dtype=np.int32)
-        cu_k[1:] = np.cumsum(k_lens)
+        grouped = self._group_shared_span(ps, materialized, use_qr)
         starts, slots, read, shared_lens, shifts = [], [], [], [], []
         for s in ps:
             st = s.generation_start + s.current_block_idx * T
             starts.append(st)
             slots.append(np.asarray(s.read_slot_map[st: st + T], dtype=np.int32))
-            layout, n_shared = self._attention_read_layout(s, use_qr)
+            layout, n_shared = attention_read_runs(s)[:2] if grouped else self._attention_read_layout(s, use_qr)
             read.append(np.asarray(layout, dtype=np.int32))
             shared_lens.append(n_shared)
             shifts.append(s.affix_start if self._affix_relocation_enabled else 0)
+        cu_k = np.zeros(len(ps) + 1, dtype=np.int32)
+        cu_k[1:] = np.cumsum([r.shape[0] for r in read])
         pos = np.asarray(starts, dtype=np.int64)[:, None] + np.arange(T, dtype=np.int64)[None, :]
         arrays = dict(positions=pos, cu_q=np.arange(0, (len(ps) + 1) * T, T, dtype=np.int32), cu_k=cu_k,
                       kv_seqlens=k_lens.astype(np.int32), slots=np.concatenate(slots), read=np.concatenate(read))
-        if use_qr:
+        if use_qr or grouped:
             arrays["shared_lens"] = np.asarray(shared_lens, dtype=np.int32)
         if not materialized:
             arrays["shifts"] = np.asarray(shifts, dtype=np.int32)
@@ -814,6 +859,7 @@ class ModelRunner:
         self._note_attention_work("decode", [T] * len(ps), k_lens)
         set_context(False, dev["cu_q"], dev["cu_k"], dev["kv_seqlens"], T, int(k_lens.max()), dev["slots"], None, True,
                     dev["read"], dev.get("shared_lens"), dev.get("shifts"))
+        get_context().group_shared_span = grouped
         return dev["positions"]
 
     # ------------------------------------------------------------------ sampling

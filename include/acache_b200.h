@@ -173,6 +173,17 @@ ACACHE_API int acache_anchor_importance_static(const void* q, int64_t q_stride, 
  *   query side: additionally shared_kv_lens != NULL: the first shared_kv_lens[b] keys of
  *               request b are scored with q rotated by the inverse of table row
  *               affix_shifts[b]; the remaining keys with q as given.
+ * Two extensions over the reference, both neutral for a caller that does not use them:
+ *   holes:      an entry of -1 in read_slot_mapping is a key that takes no part (weight 0);
+ *               any other entry outside [0, num_slots) is reported through err_flag.  Since
+ *               attention does not depend on the order of the keys, a caller may list the
+ *               shared span as the consecutive slots it occupies, with -1 where a private
+ *               copy (an anchor) replaces the shared row, and append the private slots: all
+ *               requests then name the shared span the same way (acache_attention_grouped
+ *               builds on that);
+ *   run split:  shared_kv_lens != NULL with affix_shifts == NULL only splits the keys of
+ *               request b after the first shared_kv_lens[b] entries for tiling (the second
+ *               run starts a fresh tile); the result is the same as without it.
  * Output rows have the layout of q (rows o_stride apart).  Requests with kv_len <= 0
  * get zeros.  max_seqlen_q / max_seqlen_k are host-known upper bounds (no device
  * synchronisation is done to find them). */
@@ -183,6 +194,29 @@ ACACHE_API int acache_attention(const void* q, int64_t q_stride, void* out, int6
                      int shared_prefix_len, const int32_t* shared_kv_lens, const int32_t* affix_shifts,
                      const void* rope_cos, const void* rope_sin, int64_t rope_row_stride, int rope_rows,
                      int rope_dtype, int32_t* err_flag, void* stream);
+
+/* Block-decode form of acache_attention that stages the shared span once per group of four
+ * consecutive requests instead of once per request (no counterpart in the reference, which
+ * reads the span per request; same result up to the order of the floating-point sums).
+ * Contract on top of acache_attention's: shared_kv_lens != NULL; within each group of four
+ * consecutive requests shared_kv_lens[b] is the same and the first shared_kv_lens[b] entries of
+ * read_slot_mapping name the same slots, up to holes (-1); every request has at most
+ * 32 / (n_heads / n_kv_heads) queries; no key-side relocation.  A violated contract is reported
+ * through err_flag (code 7), never by a fault.  ACACHE_EUNSUPPORTED means "use acache_attention".
+ * scratch: acache_attention_grouped_scratch_bytes(...) bytes, 16-byte aligned, ZEROED ONCE by the
+ * caller and then left alone between calls (it holds tickets that every call returns to an even
+ * count); calls that share a scratch buffer must not overlap on the GPU; re-zero it after a call
+ * that reported an error.  total_q = number of query rows (cu_seqlens_q[batch]). */
+ACACHE_API int64_t acache_attention_grouped_scratch_bytes(int total_q, int n_heads, int head_dim, int batch,
+                                                          int n_kv_heads);
+ACACHE_API int acache_attention_grouped(const void* q, int64_t q_stride, void* out, int64_t o_stride,
+                             const void* k_cache, const void* v_cache, int64_t num_slots, int n_heads,
+                             int n_kv_heads, int head_dim, int dtype, const int32_t* cu_seqlens_q,
+                             const int32_t* cu_seqlens_k, int batch, int total_q, int max_seqlen_q,
+                             const int32_t* read_slot_mapping, float softmax_scale, int shared_prefix_len,
+                             const int32_t* shared_kv_lens, const int32_t* affix_shifts, const void* rope_cos,
+                             const void* rope_sin, int64_t rope_row_stride, int rope_rows, int rope_dtype,
+                             void* scratch, int64_t scratch_bytes, int32_t* err_flag, void* stream);
 
 /* ------------------------------------------------------------------ varlen attention, block tables
  * Replaces baseline_ragged_attention and baseline_decode_attention

@@ -57,6 +57,10 @@ def acache_attention(
             out[q0:q1] = 0
             continue
         slots = read_slot_mapping[k0:k1].long()
+        # extension over the reference: an entry of -1 is a hole, a key that takes no part
+        # (used to read the shared span as one contiguous run with the anchors punched out)
+        live = slots >= 0
+        slots = slots.clamp(min=0)
         k = flat_k[slots]
         v = flat_v[slots]
         qb = q[q0:q1]
@@ -84,7 +88,8 @@ def acache_attention(
             sf = torch.cat((s_sh, s_pr), dim=-1) * scale
         else:
             sf = (qb.float().permute(1, 0, 2) @ k.float().permute(1, 2, 0).repeat_interleave(g, dim=0)) * scale
-        w = torch.softmax(sf, dim=-1)
+        sf = sf.masked_fill(~live.view(1, 1, -1), float("-inf"))
+        w = torch.nan_to_num(torch.softmax(sf, dim=-1), nan=0.0)  # no live key: zeros
         o = w @ v.float().permute(1, 0, 2).repeat_interleave(g, dim=0)
         out[q0:q1] = o.permute(1, 0, 2).to(q.dtype)
     return out

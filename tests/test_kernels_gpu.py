@@ -502,6 +502,193 @@ def test_attention_tensor_core_growing_scores_and_block_tables():
     _lib.check_device_errors()
 
 
+def _runs_case(g, dt, nh, hkv, D, Bk, nb, A, q_lens, own_lens, hole_every=5, nan_fill=True):
+    """Shared span = slots 0..A-1; every request reads it as one run with holes (-1) where an
+    'anchor' has a private copy, then the private copies, then its own tokens, all private
+    slots being consecutive from a block boundary.  Returns the run layout and the same keys
+    without holes in logical order."""
+    kc = torch.randn(nb, Bk, hkv, D, generator=g).to(dt)
+    vc = torch.randn(nb, Bk, hkv, D, generator=g).to(dt)
+    q = torch.randn(sum(q_lens), nh, D, generator=g).to(dt)
+    runs, logical, n_span = [], [], []
+    next_block = -(-A // Bk)
+    for own in own_lens:
+        holes = list(range(2, A, hole_every)) if hole_every else []
+        k = len(holes)
+        base = next_block * Bk
+        next_block += -(-(k + own) // Bk)
+        assert next_block <= nb
+        span = list(range(A))
+        log = list(range(A))
+        for i, h in enumerate(holes):
+            span[h] = -1
+            log[h] = base + i
+        private = list(range(base, base + k + own))
+        runs += span + private
+        logical += log + private[k:]
+        n_span.append(A)
+    if nan_fill:  # rows a hole stands for and rows past the last used slot hold NaN: they must not leak
+        flat_k, flat_v = kc.view(-1, hkv, D), vc.view(-1, hkv, D)
+        for h in (range(2, A, hole_every) if hole_every else []):
+            flat_k[h], flat_v[h] = float("nan"), float("nan")
+        flat_k[next_block * Bk:], flat_v[next_block * Bk:] = float("nan"), float("nan")
+        used = torch.zeros(nb * Bk, dtype=torch.bool)
+        used[torch.tensor([x for x in runs if x >= 0])] = True
+        used[:A] = True
+        flat_k[~used], flat_v[~used] = float("nan"), float("nan")
+    ql = torch.tensor([0, *np.cumsum(q_lens)], dtype=torch.int32)
+    holes_n = len(range(2, A, hole_every)) if hole_every else 0
+    cu_runs = torch.tensor([0, *np.cumsum([A + holes_n + o for o in own_lens])], dtype=torch.int32)
+    cu_log = torch.tensor([0, *np.cumsum([A + o for o in own_lens])], dtype=torch.int32)
+    return q, kc, vc, ql, cu_runs, torch.tensor(runs, dtype=torch.int32), cu_log, \
+        torch.tensor(logical, dtype=torch.int32), torch.tensor(n_span, dtype=torch.int32)
+
+
+@pytest.mark.parametrize("dt,nh,hkv,D,A,q_lens,own_lens", [
+    (torch.bfloat16, 32, 32, 128, 800, [32, 32, 32], [96, 300, 511]),     # block decode, MHA, 800-token affix
+    (torch.bfloat16, 28, 4, 128, 600, [32, 32], [64, 257]),               # GQA 7
+    (torch.float16, 4, 2, 64, 130, [70, 3], [10, 200]),                    # head_dim 64, ragged queries
+    (torch.bfloat16, 4, 4, 128, 64, [5, 9], [0, 1]),                       # one full span tile, (almost) nothing else
+    (torch.float32, 4, 4, 32, 100, [7, 40], [30, 5]),                      # CUDA-core kernel, same contract
+])
+def test_attention_slot_runs_with_holes(dt, nh, hkv, D, A, q_lens, own_lens):
+    """The run layout (consecutive slots fetched by TMA, -1 = key that takes no part) gives
+    the same attention as the logical order; dead rows never leak, even when they hold NaN."""
+    from oracle import attention as oatt
+
+    _lib, ops, aa, att = _ops()
+    g = torch.Generator().manual_seed(21)
+    Bk = 256
+    nb = -(-A // Bk) + sum(-(-(A // 5 + 1 + o) // Bk) for o in own_lens) + 1
+    q, kc, vc, cu_q, cu_runs, runs, cu_log, logical, n_span = _runs_case(g, dt, nh, hkv, D, Bk, nb, A, q_lens, own_lens)
+    d = lambda x: x.to(DEV)
+    tol = _tol(dt)
+    ref = oatt.acache_attention(q, torch.nan_to_num(kc), torch.nan_to_num(vc), cu_q, cu_log, logical)
+    assert torch.isfinite(ref.float()).all()
+    # oracle agrees with itself across the two layouts (holes are handled the same way)
+    ref_runs = oatt.acache_attention(q, torch.nan_to_num(kc), torch.nan_to_num(vc), cu_q, cu_runs, runs)
+    assert (ref_runs.float() - ref.float()).abs().max() < tol
+    got = aa.acache_attention(d(q), d(kc), d(vc), d(cu_q), d(cu_runs), d(runs), max_seqlen_q=max(q_lens))
+    assert torch.isfinite(got.float()).all()
+    assert (got.cpu().float() - ref.float()).abs().max() < tol
+    # run split: the private part starts a fresh tile (all of its tiles are whole runs)
+    got2 = aa.acache_attention(d(q), d(kc), d(vc), d(cu_q), d(cu_runs), d(runs), None, 0, d(n_span),
+                               max_seqlen_q=max(q_lens))
+    assert torch.isfinite(got2.float()).all()
+    assert (got2.cpu().float() - ref.float()).abs().max() < tol
+    _lib.check_device_errors()
+
+
+def test_attention_slot_runs_query_side_and_edges():
+    """Query-side relocation over a run layout; a tile of holes only; a run that ends at the
+    last slot of the cache (the TMA box reaches past it); a run that starts at an odd slot."""
+    from oracle import attention as oatt
+
+    _lib, ops, aa, att = _ops()
+    g = torch.Generator().manual_seed(22)
+    dt, nh, hkv, D, Bk, A = torch.bfloat16, 8, 8, 128, 256, 300
+    q, kc, vc, cu_q, cu_runs, runs, cu_log, logical, n_span = _runs_case(
+        g, dt, nh, hkv, D, Bk, 6, A, [32, 40], [100, 37], nan_fill=False)
+    d = lambda x: x.to(DEV)
+    cos, sin = _rope(2048, D)
+    shifts = torch.tensor([11, 140], dtype=torch.int32)
+    ref = oatt.acache_attention(q, kc, vc, cu_q, cu_runs, runs, None, A, n_span, shifts, cos, sin)
+    got = aa.acache_attention(d(q), d(kc), d(vc), d(cu_q), d(cu_runs), d(runs), None, A, d(n_span), d(shifts), d(cos),
+                              d(sin), max_seqlen_q=40, max_seqlen_k=600)
+    assert (got.cpu().float() - ref.float()).abs().max() < 2e-2
+
+    # hand-made map, tile by tile: [64 holes] [run 7..70 (odd start)] [64 scattered rows]
+    # [the last 40 slots of the cache: a run whose TMA box reaches past the end]
+    nslots = 6 * Bk
+    m = [-1] * 64 + list(range(7, 71)) + [5, 900, 333] + list(range(100, 161)) + list(range(nslots - 40, nslots))
+    cu_k = torch.tensor([0, len(m)], dtype=torch.int32)
+    cu_q1 = torch.tensor([0, 32], dtype=torch.int32)
+    mm = torch.tensor(m, dtype=torch.int32)
+    ref = oatt.acache_attention(q[:32], kc, vc, cu_q1, cu_k, mm)
+    got = aa.acache_attention(d(q[:32]), d(kc), d(vc), d(cu_q1), d(cu_k), d(mm), max_seqlen_q=32)
+    assert (got.cpu().float() - ref.float()).abs().max() < 2e-2
+    # nothing but holes: zeros
+    mm = torch.full((130,), -1, dtype=torch.int32)
+    cu_k = torch.tensor([0, 130], dtype=torch.int32)
+    got = aa.acache_attention(d(q[:32]), d(kc), d(vc), d(cu_q1), d(cu_k), d(mm), max_seqlen_q=32)
+    assert torch.equal(got.cpu().float(), torch.zeros(32, nh, D))
+    _lib.check_device_errors()
+
+
+@pytest.mark.parametrize("dt,nh,hkv,D,A,q_lens,own_lens,shifts", [
+    (torch.bfloat16, 32, 32, 128, 800, [32] * 6, [96, 300, 511, 64, 130, 257], None),        # block decode, MHA; 6 = 4 + 2
+    (torch.bfloat16, 8, 8, 128, 200, [32, 7, 0, 32, 1, 32, 32, 32, 5], [50, 0, 9, 300, 1, 70, 64, 65, 2], None),
+    (torch.bfloat16, 28, 4, 128, 300, [4, 4, 3, 4, 4], [64, 257, 10, 0, 90], None),           # GQA 7: 4 x 7 = 28 rows
+    (torch.float16, 4, 2, 64, 130, [16, 16, 9], [10, 200, 33], [5, 77, 140]),                 # head_dim 64, query-side
+    (torch.bfloat16, 8, 8, 128, 100, [32, 32, 32, 32], [40, 41, 42, 43], [3, 3, 900, 0]),     # query-side, MHA
+])
+def test_attention_grouped_shared_span(dt, nh, hkv, D, A, q_lens, own_lens, shifts):
+    """The grouped block-decode kernel (shared span staged once per four requests, parts folded
+    by the second arrival) against the oracle and the per-request kernel."""
+    from oracle import attention as oatt
+
+    _lib, ops, aa, att = _ops()
+    g = torch.Generator().manual_seed(31)
+    Bk = 256
+    nb = -(-A // Bk) + sum(-(-(A // 5 + 1 + o) // Bk) for o in own_lens) + 1
+    q, kc, vc, cu_q, cu_runs, runs, cu_log, logical, n_span = _runs_case(g, dt, nh, hkv, D, Bk, nb, A, q_lens, own_lens)
+    d = lambda x: x.to(DEV)
+    tol = _tol(dt)
+    kw = {}
+    args = [None, 0, n_span]
+    if shifts is not None:
+        cos, sin = _rope(2048, D)
+        sh = torch.tensor(shifts, dtype=torch.int32)
+        args = [None, A, n_span, sh, cos, sin]
+        kw = dict(max_seqlen_k=1024)
+    ref = oatt.acache_attention(q, torch.nan_to_num(kc), torch.nan_to_num(vc), cu_q, cu_runs, runs, *args)
+    dargs = [d(x) if torch.is_tensor(x) else x for x in args]
+    plain = aa.acache_attention(d(q), d(kc), d(vc), d(cu_q), d(cu_runs), d(runs), *dargs, max_seqlen_q=max(q_lens), **kw)
+    launches = _lib.LAUNCHES
+    for _ in range(3):  # the scratch is reused as it was left
+        got = aa.acache_attention(d(q), d(kc), d(vc), d(cu_q), d(cu_runs), d(runs), *dargs, max_seqlen_q=max(q_lens),
+                                  group_shared_span=True, **kw)
+        assert torch.isfinite(got.float()).all()
+        assert (got.cpu().float() - ref.float()).abs().max() < tol
+        assert (got.float() - plain.float()).abs().max() < tol
+    assert _lib.LAUNCHES == launches + 3
+    _lib.check_device_errors()
+
+
+def test_attention_grouped_declines_and_reports():
+    """More than 32 rows per request: the plain kernel answers.  Requests of a group that name
+    different spans: reported through the error flag, nothing faults, and the next call works."""
+    from acache_b200._lib import AcacheError
+    from oracle import attention as oatt
+
+    _lib, ops, aa, att = _ops()
+    g = torch.Generator().manual_seed(32)
+    dt, nh, hkv, D, Bk, A = torch.bfloat16, 8, 8, 128, 256, 128
+    q, kc, vc, cu_q, cu_runs, runs, cu_log, logical, n_span = _runs_case(
+        g, dt, nh, hkv, D, Bk, 8, A, [40, 33], [20, 30], nan_fill=False)
+    d = lambda x: x.to(DEV)
+    ref = oatt.acache_attention(q, kc, vc, cu_q, cu_runs, runs)
+    got = aa.acache_attention(d(q), d(kc), d(vc), d(cu_q), d(cu_runs), d(runs), None, 0, d(n_span), max_seqlen_q=40,
+                              group_shared_span=True)
+    assert (got.cpu().float() - ref.float()).abs().max() < 2e-2
+    _lib.check_device_errors()
+
+    q, kc, vc, cu_q, cu_runs, runs, cu_log, logical, n_span = _runs_case(
+        g, dt, nh, hkv, D, Bk, 8, A, [32, 32], [20, 30], nan_fill=False)
+    bad = runs.clone()
+    second = int(cu_runs[1])
+    bad[second: second + A][bad[second: second + A] >= 0] += 256        # request 1 names another span
+    aa.acache_attention(d(q), d(kc), d(vc), d(cu_q), d(cu_runs), d(bad), None, 0, d(n_span), max_seqlen_q=32,
+                        group_shared_span=True)
+    with pytest.raises(AcacheError, match="same shared span"):
+        _lib.check_device_errors()
+    ref = oatt.acache_attention(q, kc, vc, cu_q, cu_runs, runs)
+    got = aa.acache_attention(d(q), d(kc), d(vc), d(cu_q), d(cu_runs), d(runs), None, 0, d(n_span), max_seqlen_q=32,
+                              group_shared_span=True)
+    assert (got.cpu().float() - ref.float()).abs().max() < 2e-2
+    _lib.check_device_errors()
+
+
 # ----------------------------------------------------------------------------- fused QKV GEMM
 @pytest.mark.parametrize("kind,n,hidden,nh,hkv", [("llada", 300, 512, 4, 4), ("dream", 77, 448, 7, 1),
                                                    ("llada", 512, 4096, 32, 32)])

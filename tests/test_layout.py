@@ -37,6 +37,39 @@ def test_layout_matches_reference_vectors(layout_cases):
         assert packed == out["packed_read"] and n_shared == out["packed_shared"]
 
 
+def test_read_runs_are_a_reordering_with_holes_at_the_anchors(layout_cases):
+    """attention_read_runs keeps exactly the keys of the logical read order: the affix span
+    as consecutive slots with -1 at the anchors, then the anchors' private slots, then the rest."""
+    import numpy as np
+
+    from acache_b200.model_runner import attention_read_runs
+
+    seen_holes = 0
+    for case in layout_cases:
+        seq, _ = _build(case)
+        layout, n_span, first = attention_read_runs(seq)
+        layout = np.asarray(layout)
+        logical = np.asarray(seq.read_slot_map)
+        assert n_span == seq.affix_len and layout.shape[0] == logical.shape[0] + int((layout == -1).sum())
+        assert sorted(layout[layout >= 0].tolist()) == sorted(logical.tolist())
+        span = layout[:n_span]
+        live = span >= 0
+        if live.any() and not live.all():
+            # live entries are one run of consecutive slots, holes sit exactly at the anchors
+            start = span[live][0] - np.flatnonzero(live)[0]
+            assert start == first
+            assert (span[live] == start + np.flatnonzero(live)).all()
+            holes = (np.flatnonzero(~live) + seq.affix_start).tolist()
+            assert holes == seq.anchor_positions
+            k = len(holes)
+            assert layout[n_span: n_span + k].tolist() == [seq.read_slot_map[p] for p in holes]
+            seen_holes += 1
+        # second call returns the cached arrays
+        again = attention_read_runs(seq)[0]
+        assert again is layout or (np.asarray(again) == layout).all()
+    assert seen_holes > 10
+
+
 def test_read_layout_known_answers():
     """reference: nano-vdllm/tests/test_model_runner_acache.py:26-47."""
     from types import SimpleNamespace
