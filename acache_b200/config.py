@@ -38,8 +38,9 @@ class Config:
     use_cuda_graphs: bool = False
     # block decode: hand attention every request's shared span as the same run of slots (with -1
     # where an anchor's private copy replaces the shared row) and stage it once per four requests
-    # (same result as the logical order up to the order of the floating-point sums)
-    group_shared_span: bool = True
+    # (same result as the logical order up to the order of the floating-point sums).
+    # None = decide per step from the span and request lengths, True / False = always / never
+    group_shared_span: bool | None = None
     # eos id and block size aliases read by the block scheduler
     eos: int = -1
 

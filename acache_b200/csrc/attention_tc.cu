@@ -33,6 +33,8 @@
 // writes the output, so there is no wait between CTAs and no second kernel.
 // Every mbarrier wait is bounded; on expiry the kernel raises the error flag, frees its
 // TMEM and returns.
+#include <type_traits>
+
 #include "common.cuh"
 #include "tcgen05.cuh"
 
@@ -56,7 +58,7 @@ struct SplitArgs {
   float* part_o;        // [2][total_rows][D]  unnormalised accumulator
 };
 
-template <typename T, typename TR, typename TC, int D, bool KEYSIDE, bool SPLIT>
+template <typename T, typename TR, typename TC, int D, bool KEYSIDE, bool SPLIT, int COPIES>
 __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
     const T* __restrict__ q, int64_t q_stride, T* __restrict__ out, int64_t o_stride, const T* __restrict__ k_cache,
     const T* __restrict__ v_cache, int64_t num_slots, int n_heads, int n_kv_heads, const int32_t* __restrict__ cu_q,
@@ -150,9 +152,17 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
   const int nt1 = (SPLIT && kind_a) ? 0 : (kv_len - n_shared + BN - 1) / BN;
   const int n_tiles = nt0 + nt1;
 
+  // COPIES = 4 (requests of at most 32 virtual rows, block decode): the 32 rows are staged four
+  // times, copy w in rows 32w..32w+31, and warp w runs the softmax of key columns 16w..16w+15 of
+  // every tile only (its P row is zero elsewhere), so each copy accumulates the attention over a
+  // quarter of the keys with its own reference maximum; the four slices are folded at the end.
+  // The tensor cores compute 128 rows either way; this spreads the softmax, the part that
+  // bounds block decode, over all four warps.  Items of kind A fill the rows with four requests
+  // instead and do not spread.
+  const bool spread = COPIES > 1 && !kind_a;
   // this thread's row: request slot ri of the item, virtual row vr
   const int ri = kind_a ? warp : 0;
-  const int vr = kind_a ? lane : m0 + tid;
+  const int vr = (kind_a || spread) ? lane : m0 + tid;
 
   const uint32_t bar_s = smem_u32(&bars[0]), bar_o = smem_u32(&bars[1]);
   if (tid == 0) {
@@ -196,7 +206,7 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
     for (int id = tid; id < BM * CH; id += NT) {
       const int r = id / CH, c = id % CH;
       const int rr = kind_a ? (r >> 5) : 0;             // request slot of the row
-      const int v = kind_a ? (r & 31) : m0 + r;
+      const int v = (kind_a || spread) ? (r & 31) : m0 + r;
       const bool ok = v < rq_vrows[rr];
       const int rq = ok ? v / g : 0, rh = kvh * g + (ok ? v % g : 0);
       const T* src = q + (int64_t)(rq_q0[rr] + rq) * q_stride + (int64_t)rh * D + c * (16 / sizeof(T));
@@ -351,7 +361,7 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
   const uint32_t idesc_o = make_idesc(Fmt<T>::id, 1, D, BM);
 
   // a warp is live when at least one of its 32 rows is a real (query, head) pair
-  const bool warp_live = kind_a ? my_vrows > 0 : m0 + warp * 32 < my_vrows;
+  const bool warp_live = (kind_a || spread) ? my_vrows > 0 : m0 + warp * 32 < my_vrows;
   float m_ref = -INFINITY, l_sum = 0.f;
   bool failed = false;
 
@@ -369,11 +379,64 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
       fetch_raw(1, raw);
       interpret(1, raw, e_nxt0, e_nxt1, dead_nxt_lo, dead_nxt_hi);
     }
-    if (!warp_live) {  // its rows of P are never written: keep them zero so the MMA reads no junk
+    if (!warp_live || spread) {  // rows (or, spread, column slices) of P that are never written stay zero
 #pragma unroll
       for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(sP + tid * 128 + (c << 4)) = make_uint4(0, 0, 0, 0);
     }
-    uint32_t s[64];
+    // online softmax of this thread's row over NC key columns of the tile starting at col0, exp2
+    // domain; raw scores are scaled inside the fma
+    auto softmax_tile = [&](auto nc_tag, const int col0, const int i) {
+      constexpr int NC = decltype(nc_tag)::value;
+      uint32_t s[NC];
+      if constexpr (NC == 64) {
+        tmem_ld32(t_lane + kColS, s);
+        tmem_ld32(t_lane + kColS + 32, s + 32);
+      } else {
+        static_assert(NC == 16, "column slices are 16 wide");
+        tmem_ld16(t_lane + kColS + col0, s);
+      }
+      tmem_wait_ld();
+      const uint64_t dead = ((((uint64_t)dead_hi) << 32) | dead_lo) >> col0;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        const float v = ((dead >> c) & 1ull) ? -INFINITY : __uint_as_float(s[c]);
+        s[c] = __float_as_uint(v);
+        mx = fmaxf(mx, v);
+      }
+      mx *= scale_log2;
+      const bool grow = mx > m_ref + 8.0f;  // also true on the first tile with a live key (m_ref = -inf)
+      if (__any_sync(0xFFFFFFFFu, grow) && i > 0) {
+        const float f = grow ? ex2(m_ref - mx) : 1.0f;
+        l_sum *= f;
+        uint32_t o[32];
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          tmem_ld32(t_lane + kColO + c0, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * f);
+          tmem_st32(t_lane + kColO + c0, o);
+        }
+        tmem_wait_st();
+      }
+      if (grow) m_ref = mx;
+      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;   // no live key so far: every p is 0
+      float rs = 0.f;
+#pragma unroll
+      for (int c = 0; c < NC; c += 8) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) {
+          const float p0 = ex2(fmaf(__uint_as_float(s[c + e]), scale_log2, -m_use));
+          const float p1 = ex2(fmaf(__uint_as_float(s[c + e + 1]), scale_log2, -m_use));
+          rs += p0 + p1;
+          w[e / 2] = pack2<T>(p0, p1);
+        }
+        *reinterpret_cast<uint4*>(sP + tid * 128 + ((((col0 + c) / 8) ^ (tid & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      l_sum += rs;
+    };
 
     for (int i = 0; i < n_tiles; ++i) {
       if (i + 2 < n_tiles) fetch_raw(i + 2, raw);   // looked at when the iteration ends
@@ -403,50 +466,12 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
       ok = mbar_wait(bar_s, (uint32_t)(i & 1)) && ok;
       tc_fence_after();
       if (warp_live) {  // warps whose 32 rows are all padding skip the softmax (their P rows stay zero)
-        tmem_ld32(t_lane + kColS, s);
-        tmem_ld32(t_lane + kColS + 32, s + 32);
-        tmem_wait_ld();
-        // online softmax of this thread's row, exp2 domain; raw scores are scaled inside the fma
-        float mx = -INFINITY;
-#pragma unroll
-        for (int c = 0; c < BN; ++c) {
-          const bool dead = ((c < 32 ? dead_lo : dead_hi) >> (c & 31)) & 1u;
-          const float v = dead ? -INFINITY : __uint_as_float(s[c]);
-          s[c] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
+        if constexpr (COPIES > 1) {
+          if (spread) softmax_tile(std::integral_constant<int, BN / COPIES>{}, warp * (BN / COPIES), i);
+          else softmax_tile(std::integral_constant<int, BN>{}, 0, i);
+        } else {
+          softmax_tile(std::integral_constant<int, BN>{}, 0, i);
         }
-        mx *= scale_log2;
-        const bool grow = mx > m_ref + 8.0f;  // also true on the first tile with a live key (m_ref = -inf)
-        if (__any_sync(0xFFFFFFFFu, grow) && i > 0) {
-          const float f = grow ? ex2(m_ref - mx) : 1.0f;
-          l_sum *= f;
-          uint32_t o[32];
-#pragma unroll 1
-          for (int c0 = 0; c0 < D; c0 += 32) {
-            tmem_ld32(t_lane + kColO + c0, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * f);
-            tmem_st32(t_lane + kColO + c0, o);
-          }
-          tmem_wait_st();
-        }
-        if (grow) m_ref = mx;
-        const float m_use = m_ref == -INFINITY ? 0.f : m_ref;   // no live key so far: every p is 0
-        float rs = 0.f;
-#pragma unroll
-        for (int c = 0; c < BN; c += 8) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 8; e += 2) {
-            const float p0 = ex2(fmaf(__uint_as_float(s[c + e]), scale_log2, -m_use));
-            const float p1 = ex2(fmaf(__uint_as_float(s[c + e + 1]), scale_log2, -m_use));
-            rs += p0 + p1;
-            w[e / 2] = pack2<T>(p0, p1);
-          }
-          *reinterpret_cast<uint4*>(sP + tid * 128 + (((c / 8) ^ (tid & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-        l_sum += rs;
       }
 
       // query tile swap at the partition boundary: every S product against the rotated
@@ -484,6 +509,121 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
 
   if (failed) {
     if (tid == 0 && err_flag) atomicExch(err_flag, 5);
+  } else if (COPIES > 1 && spread) {
+    // ---- fold the four column slices of every row, then write (or publish) the rows ----------
+    constexpr int F4 = D / 4;                       // float4 per row
+    cp_async_wait<0>();
+    float* xm = reinterpret_cast<float*>(sP);       // [128] reference maxima, [128] row sums
+    float4* part = reinterpret_cast<float4*>(sK);   // [4 slices][32 rows][F4], float4 index swizzled by the row
+    xm[tid] = m_ref;
+    xm[BM + tid] = l_sum;
+    __syncthreads();
+    auto fold_ml = [&](int row, float& m_all, float& l_all) {   // same order for every reader
+      m_all = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < COPIES; ++c) m_all = fmaxf(m_all, xm[c * 32 + row]);
+      l_all = 0.f;
+#pragma unroll
+      for (int c = 0; c < COPIES; ++c) {
+        const float mc = xm[c * 32 + row];
+        l_all += mc == -INFINITY ? 0.f : xm[BM + c * 32 + row] * ex2(mc - m_all);
+      }
+    };
+    float m_all, l_all;
+    fold_ml(lane, m_all, l_all);
+    const float w_own = m_ref == -INFINITY ? 0.f : ex2(m_ref - m_all);
+    const bool have = n_tiles > 0;                  // otherwise O was never written: it counts as 0
+    uint32_t o[32];
+#pragma unroll 1
+    for (int c0 = 0; c0 < D; c0 += 32) {
+      if (have) {
+        tmem_ld32(t_lane + kColO + c0, o);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) o[c] = 0u;
+      }
+#pragma unroll
+      for (int c = 0; c < 32; c += 4) {
+        const int idx = (c0 + c) / 4;
+        part[(warp * 32 + lane) * F4 + (idx ^ (lane & (F4 - 1)))] =
+            make_float4(__uint_as_float(o[c]) * w_own, __uint_as_float(o[c + 1]) * w_own,
+                        __uint_as_float(o[c + 2]) * w_own, __uint_as_float(o[c + 3]) * w_own);
+      }
+    }
+    __syncthreads();
+    // thread t: row t / 4, quarter t % 4 of its columns
+    const int r = tid >> 2, qd = tid & 3;
+    constexpr int QF4 = F4 / 4;                     // float4 per quarter row
+    float4 acc[QF4];
+#pragma unroll
+    for (int k = 0; k < QF4; ++k) {
+      const int idx = qd * QF4 + k;
+      float4 a4 = part[r * F4 + (idx ^ (r & (F4 - 1)))];
+#pragma unroll
+      for (int c = 1; c < COPIES; ++c) {
+        const float4 b4 = part[(c * 32 + r) * F4 + (idx ^ (r & (F4 - 1)))];
+        a4.x += b4.x; a4.y += b4.y; a4.z += b4.z; a4.w += b4.w;
+      }
+      acc[k] = a4;
+    }
+    fold_ml(r, m_all, l_all);
+    const bool r_ok = r < my_vrows;
+    const int r_qi = r_ok ? r / g : 0, r_head = kvh * g + (r_ok ? r % g : 0);
+    const int64_t r_qrow = (int64_t)rq_q0[0] + r_qi;
+    T* r_out = out + r_qrow * o_stride + (int64_t)r_head * D + qd * (D / 4);
+    float a_own = l_all > 0.f ? 1.0f / l_all : 0.f;
+    float a_oth = 0.f;
+    const float* ot_o = nullptr;
+    bool write_out = true;
+    if (SPLIT) {
+      // publish this part, take the ticket of (request, KV head); the second arrival folds both
+      const int64_t grow = r_qrow * n_heads + r_head;
+      float4* my_o = reinterpret_cast<float4*>(sp.part_o + ((int64_t)1 * sp.total_rows + grow) * D + qd * (D / 4));
+      if (r_ok) {
+#pragma unroll
+        for (int k = 0; k < QF4; ++k) __stcg(my_o + k, acc[k]);
+        if (qd == 0) __stcg(reinterpret_cast<float2*>(sp.part_ml + ((int64_t)1 * sp.total_rows + grow) * 2), make_float2(m_all, l_all));
+      }
+      __threadfence();
+      __syncthreads();
+      int* ticket_box = reinterpret_cast<int*>(xm);   // xm is no longer read
+      if (tid == 0) *ticket_box = atomicAdd(sp.tickets + (int64_t)b * n_kv_heads + kvh, 1);
+      __syncthreads();
+      write_out = (*ticket_box & 1) != 0;             // the other part is already in scratch
+      if (write_out) {
+        __threadfence();
+        ot_o = sp.part_o + ((int64_t)0 * sp.total_rows + grow) * D + qd * (D / 4);
+        float2 ml = make_float2(-INFINITY, 0.f);
+        if (r_ok) ml = __ldcg(reinterpret_cast<const float2*>(sp.part_ml + ((int64_t)0 * sp.total_rows + grow) * 2));
+        const float m_both = fmaxf(m_all, ml.x);
+        const float w1 = m_all == -INFINITY ? 0.f : ex2(m_all - m_both);
+        const float w0 = ml.x == -INFINITY ? 0.f : ex2(ml.x - m_both);
+        // rounded one by one, no fused multiply-add: the same whichever part arrives second
+        const float l_both = __fadd_rn(__fmul_rn(l_all, w1), __fmul_rn(ml.y, w0));
+        const float inv = l_both > 0.f ? 1.0f / l_both : 0.f;
+        a_own = w1 * inv;
+        a_oth = w0 * inv;
+      }
+    }
+    if (write_out && r_ok) {
+#pragma unroll
+      for (int k = 0; k < QF4; k += 2) {
+        float4 x0 = acc[k], x1 = acc[k + 1];
+        float4 y0 = make_float4(0.f, 0.f, 0.f, 0.f), y1 = y0;
+        if (SPLIT) {
+          y0 = __ldcg(reinterpret_cast<const float4*>(ot_o) + k);
+          y1 = __ldcg(reinterpret_cast<const float4*>(ot_o) + k + 1);
+        }
+        auto fold = [&](float own, float oth) { return __fadd_rn(__fmul_rn(own, a_own), __fmul_rn(oth, a_oth)); };
+        uint4 w;
+        w.x = pack2<T>(fold(x0.x, y0.x), fold(x0.y, y0.y));
+        w.y = pack2<T>(fold(x0.z, y0.z), fold(x0.w, y0.w));
+        w.z = pack2<T>(fold(x1.x, y1.x), fold(x1.y, y1.y));
+        w.w = pack2<T>(fold(x1.z, y1.z), fold(x1.w, y1.w));
+        *reinterpret_cast<uint4*>(r_out + k * 4) = w;
+      }
+    }
   } else if (!SPLIT) {
     const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
     uint32_t o[32];
@@ -609,9 +749,9 @@ static int launch(const AttnArgs& a, const SplitArgs* split) {
     sp = *split;
     grid = dim3(sp.n_items_a + a.batch * a.n_kv_heads, 1, 1);
   }
-#define ACACHE_TC_LAUNCH(KS, SPL)                                                                                     \
+#define ACACHE_TC_LAUNCH(KS, SPL, CP)                                                                                 \
   do {                                                                                                                \
-    auto kern = attention_tc_kernel<T, TR, TC, D, KS, SPL>;                                                           \
+    auto kern = attention_tc_kernel<T, TR, TC, D, KS, SPL, CP>;                                                       \
     ACACHE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));            \
     kern<<<grid, NT, smem, a.st>>>((const T*)a.q, a.q_stride, (T*)a.out, a.o_stride, (const T*)a.k_cache,             \
                                    (const T*)a.v_cache, a.num_slots, a.n_heads, a.n_kv_heads, a.cu_q, a.cu_k,         \
@@ -620,9 +760,12 @@ static int launch(const AttnArgs& a, const SplitArgs* split) {
                                    relocate ? a.affix_shifts : nullptr, (const TR*)a.rope_cos, (const TR*)a.rope_sin, \
                                    a.rope_stride, a.rope_rows, a.err_flag, sp);                                       \
   } while (0)
-  if (split) ACACHE_TC_LAUNCH(false, true);
-  else if (key_side) ACACHE_TC_LAUNCH(true, false);
-  else ACACHE_TC_LAUNCH(false, false);
+  // requests of at most 32 virtual rows (block decode): spread the softmax over the four warps
+  const bool small_rows = a.max_q * g <= 32;
+  if (split) ACACHE_TC_LAUNCH(false, true, 4);
+  else if (key_side) ACACHE_TC_LAUNCH(true, false, 1);
+  else if (small_rows) ACACHE_TC_LAUNCH(false, false, 4);
+  else ACACHE_TC_LAUNCH(false, false, 1);
 #undef ACACHE_TC_LAUNCH
   ACACHE_LAUNCH_CHECK();
   return ACACHE_OK;
