@@ -34,8 +34,6 @@ class Config:
     # --- additions of this implementation (all default to reference behaviour) ---
     # dtype of the paged KV cache; the reference hard-codes bfloat16
     kv_cache_dtype: str = "bfloat16"
-    # capture the block-decode step in a CUDA graph (same arithmetic, fewer launches)
-    use_cuda_graphs: bool = False
     # block decode: hand attention every request's shared span as the same run of slots (with -1
     # where an anchor's private copy replaces the shared row) and stage it once per four requests
     # (same result as the logical order up to the order of the floating-point sums).

@@ -370,14 +370,15 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
     const bool start_rotated = query_side && nt0 > 0;
     int32_t e_nxt0, e_nxt1, raw[NR][2];
     uint32_t dead_lo, dead_hi, dead_nxt_lo = 0, dead_nxt_hi = 0;
-    fetch_raw(0, raw);
-    interpret(0, raw, e_nxt0, e_nxt1, dead_lo, dead_hi);
-    load_q(start_rotated);
-    load_kv(0, e_nxt0, e_nxt1);
-    cp_async_commit();
-    if (n_tiles > 1) {
-      fetch_raw(1, raw);
-      interpret(1, raw, e_nxt0, e_nxt1, dead_nxt_lo, dead_nxt_hi);
+    {
+      int32_t raw0[NR][2];
+      fetch_raw(0, raw0);                        // the lookups of the first two tiles and the query
+      if (n_tiles > 1) fetch_raw(1, raw);        // tile are all in flight before anything is read
+      load_q(start_rotated);
+      interpret(0, raw0, e_nxt0, e_nxt1, dead_lo, dead_hi);
+      load_kv(0, e_nxt0, e_nxt1);
+      cp_async_commit();
+      if (n_tiles > 1) interpret(1, raw, e_nxt0, e_nxt1, dead_nxt_lo, dead_nxt_hi);
     }
     if (!warp_live || spread) {  // rows (or, spread, column slices) of P that are never written stay zero
 #pragma unroll
