@@ -32,6 +32,9 @@ sys.path.insert(0, str(ROOT))
 
 AFFIX_LEN, BATCH, GEN, BLOCK, THRESHOLD, RATIO = 800, 16, 256, 32, 0.9, 0.2
 REQ_LO, REQ_HI = 64, 256
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode-attention launch at this workload's
+# shape (profiler capture summarised in profiles/attention_tc_decode_llada.md)
+NCU_DECODE_ATTENTION_DRAM_BYTES = 171.0e6
 WORKLOAD = ("LLaDA-8B arch random-init bf16, prefix affix 800 tok + 16 ragged requests U[64,256], "
             "gen/steps/block 256/256/32, thr 0.9, anchor_ratio 0.2")
 
@@ -314,9 +317,13 @@ def run_ours(args):
             ms, n, work = timers[name]
             if name == "attention_decode":
                 achieved = work / (ms * 1e-3) / 1e9
+                # DRAM bytes per launch from the profiler capture of this shape (16 requests):
+                # profiles/attention_tc_decode_llada.md; below the algorithmic bytes because the
+                # shared affix is served by L2 after its first reader
+                traffic = NCU_DECODE_ATTENTION_DRAM_BYTES if args.batch == BATCH else None
                 roof = dict(kernel=name, bound="hbm", achieved=achieved, peak=peaks["hbm_gbs"], unit="GB/s",
-                            frac=achieved / peaks["hbm_gbs"], traffic=None, launches=n, avg_us=ms * 1e3 / n,
-                            peak_source=peaks["source"])
+                            frac=achieved / peaks["hbm_gbs"], traffic=traffic, launches=n, avg_us=ms * 1e3 / n,
+                            algorithmic_bytes_per_launch=work / n, peak_source=peaks["source"])
             else:
                 achieved = work / (ms * 1e-3) / 1e12
                 roof = dict(kernel=name, bound="tensor", achieved=achieved, peak=peaks["bf16_tflops_sustained"],
