@@ -44,7 +44,8 @@ namespace tc {
 
 constexpr int BM = 128;      // virtual rows per CTA
 constexpr int BN = 64;       // keys per tile
-constexpr int NT = 128;      // threads
+constexpr int NT = 128;      // threads that stage K/V and own the rows (warps 0-3)
+constexpr int NT_ALL = 160;  // + warp 4, whose first lane issues every tensor-core product
 constexpr int GROUP = 4;     // requests per shared-span work item (one per warp)
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kColS = 0, kColO = 128;
@@ -59,7 +60,7 @@ struct SplitArgs {
 };
 
 template <typename T, typename TR, typename TC, int D, bool KEYSIDE, bool SPLIT, int COPIES>
-__global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
+__global__ void __launch_bounds__(NT_ALL, 2) attention_tc_kernel(
     const T* __restrict__ q, int64_t q_stride, T* __restrict__ out, int64_t o_stride, const T* __restrict__ k_cache,
     const T* __restrict__ v_cache, int64_t num_slots, int n_heads, int n_kv_heads, const int32_t* __restrict__ cu_q,
     const int32_t* __restrict__ cu_k, const int32_t* __restrict__ slot_map, const int32_t* __restrict__ block_tables,
@@ -82,14 +83,17 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
   uint8_t* sK = sQ + Q_BYTES;            // 2 stages
   uint8_t* sV = sK + 2 * KV_BYTES;       // 2 stages
   uint8_t* sP = sV + 2 * KV_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);  // [0] = S done, [1] = O done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+  // mbarriers: [0],[1] K stage landed (128 arrivals); [2],[3] S buffer computed (tcgen05.commit);
+  // [4] P written and V landed (128 arrivals); [5] P V product done (tcgen05.commit)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
   // per request of the item (one unless this is a kind-A item): first query row, virtual
   // rows, first slot-map entry, rotation row
   int* rq_q0 = reinterpret_cast<int*>(tmem_slot + 1);
   int* rq_vrows = rq_q0 + GROUP;
   int* rq_kv0 = rq_vrows + GROUP;
   int* rq_shift = rq_kv0 + GROUP;
+  volatile int* give_up = rq_shift + GROUP;   // set by the first role whose bounded wait runs out
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = n_heads / n_kv_heads;
@@ -161,13 +165,19 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
   // instead and do not spread.
   const bool spread = COPIES > 1 && !kind_a;
   // this thread's row: request slot ri of the item, virtual row vr
-  const int ri = kind_a ? warp : 0;
+  const int ri = kind_a ? (warp & 3) : 0;
   const int vr = (kind_a || spread) ? lane : m0 + tid;
 
-  const uint32_t bar_s = smem_u32(&bars[0]), bar_o = smem_u32(&bars[1]);
+  const uint32_t bar_k = smem_u32(&bars[0]), bar_s = smem_u32(&bars[2]), bar_p = smem_u32(&bars[4]),
+                 bar_o = smem_u32(&bars[5]);
   if (tid == 0) {
+    mbar_init(bar_k, NT);
+    mbar_init(bar_k + 8, NT);
     mbar_init(bar_s, 1);
+    mbar_init(bar_s + 8, 1);
+    mbar_init(bar_p, NT);
     mbar_init(bar_o, 1);
+    *give_up = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -184,7 +194,7 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
   T* out_row = out + q_row * o_stride + (int64_t)head * D;
 
   if (!SPLIT && n_tiles == 0) {  // no keys: zeros
-    if (row_ok) {
+    if (row_ok && tid < NT) {
       for (int c = 0; c < CH; ++c) *reinterpret_cast<uint4*>(out_row + c * (16 / sizeof(T))) = make_uint4(0, 0, 0, 0);
     }
     return;
@@ -303,7 +313,7 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
       if (uni[0] == -2 || uni[1] == -2) atomicExch(err_flag, 3);
     }
   };
-  auto load_kv = [&](int i, int32_t e0, int32_t e1) {
+  auto load_rows = [&](int i, int32_t e0, int32_t e1, const bool want_k, const bool want_v) {
     const uint32_t kb = smem_u32(sK) + (i & 1) * KV_BYTES, vb = smem_u32(sV) + (i & 1) * KV_BYTES;
     int j0, j_end;
     tile_span(i, j0, j_end);
@@ -317,7 +327,8 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
       if (!ok) slot = 0;
       const int64_t off = slot * kv_row + (int64_t)kvh * D + c * (16 / sizeof(T));
       const uint32_t so = swz<D>(BN, r, c);
-      cp_async16(vb + so, v_cache + off, ok);
+      if (want_v) cp_async16(vb + so, v_cache + off, ok);
+      if (!want_k) continue;
       if (!KEYSIDE) {
         cp_async16(kb + so, k_cache + off, ok);
       } else if (c < CH / 2) {
@@ -365,40 +376,129 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
   float m_ref = -INFINITY, l_sum = 0.f;
   bool failed = false;
 
-  if (n_tiles > 0) {
+  // bounded wait that also ends when another role has given up
+  auto wait_bar = [&](uint32_t bar, uint32_t parity) -> bool {
+    const long long t0 = clock64();
+    for (uint32_t it = 0;; ++it) {
+      uint32_t done;
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+      if (done) return true;
+      if ((it & 63) == 63) {
+        if (*give_up) return false;
+        if (clock64() - t0 > kWaitCycles) {
+          *give_up = 1;
+          return false;
+        }
+        __nanosleep(32);
+      }
+    }
+  };
+  auto arrive = [&](uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); };
+  // barrier of the 128 row-owning threads only (warp 4 never takes part)
+  auto rows_sync = [&]() { asm volatile("bar.sync 1, 128;" ::: "memory"); };
+
+  // Roles.  Warp 4, one thread: issues S(i+1) as soon as K(i+1) has landed, i.e. one tile
+  // ahead of the softmax (two S buffers in TMEM), and P V(i) as soon as P(i) is written.
+  // Warps 0-3: stage K/V, run the softmax, never wait for one another inside the loop, only
+  // for the products they consume.  In iteration i a row-owning thread
+  //   publishes K(i+1) (its copies have landed)                        -> bar_k
+  //   waits for S(i); K(i+2) may then overwrite K(i)
+  //   waits for P V(i-1); V(i+1) may then overwrite V(i-1), O may be rescaled, P overwritten
+  //   writes P(i) and publishes it together with V(i) having landed     -> bar_p
+  // cp.async groups are committed in the fixed order K(i+2), V(i+1) per iteration (prologue:
+  // Q+K(0), K(1), V(0)), so "one group pending" means K(i+1) has landed at the top of an
+  // iteration and "two groups pending" means V(i) has landed at its end.
+  if (warp == 4) {
+    if (lane == 0 && n_tiles > 0) {
+      auto issue_s = [&](int i) {   // S(i) = Q K(i)^T into S buffer i & 1
+        const uint32_t kb = smem_u32(sK) + (i & 1) * KV_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t a_off = (ks / 4) * (BM * 128) + (ks % 4) * 32;
+          const uint32_t b_off = (ks / 4) * (BN * 128) + (ks % 4) * 32;
+          mma_ss(tmem_base + kColS + (i & 1) * BN, make_desc(smem_u32(sQ) + a_off, 16, 1024),
+                 make_desc(kb + b_off, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+        }
+        mma_commit(bar_s + (i & 1) * 8);
+      };
+      bool ok = wait_bar(bar_k, 0);
+      tc_fence_after();
+      if (ok) issue_s(0);
+      for (int i = 0; i < n_tiles && ok; ++i) {
+        if (i + 1 < n_tiles) {
+          // S buffer (i+1)&1 held S(i-1), read before P(i-1) was published, which was awaited
+          ok = wait_bar(bar_k + ((i + 1) & 1) * 8, (uint32_t)(((i + 1) >> 1) & 1));
+          tc_fence_after();
+          if (!ok) break;
+          issue_s(i + 1);
+        }
+        ok = wait_bar(bar_p, (uint32_t)(i & 1));
+        tc_fence_after();
+        if (!ok) break;
+        const uint32_t vb = smem_u32(sV) + (i & 1) * KV_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < BN / 16; ++ks) {
+          mma_ss(tmem_base + kColO, make_desc(smem_u32(sP) + ks * 32, 16, 1024),
+                 make_desc(vb + ks * 2048, BN * 128, 1024), idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
+        }
+        mma_commit(bar_o);
+      }
+    }
+  } else if (n_tiles > 0) {
     // ---- prologue ----------------------------------------------------------------------
     const bool start_rotated = query_side && nt0 > 0;
-    int32_t e_nxt0, e_nxt1, raw[NR][2];
-    uint32_t dead_lo, dead_hi, dead_nxt_lo = 0, dead_nxt_hi = 0;
+    int32_t raw[NR][2];
+    int32_t ev0 = -3, ev1 = -3, ek0 = -3, ek1 = -3;        // entries of tile i+1 (V load) / tile i+2 (K load)
+    uint32_t dead_lo, dead_hi, dead1_lo = 0, dead1_hi = 0, dead2_lo = 0, dead2_hi = 0;  // tiles i, i+1, i+2
     {
-      int32_t raw0[NR][2];
-      fetch_raw(0, raw0);                        // the lookups of the first two tiles and the query
-      if (n_tiles > 1) fetch_raw(1, raw);        // tile are all in flight before anything is read
+      int32_t raw0[NR][2], e0, e1;
+      fetch_raw(0, raw0);                        // the lookups of the first tiles and the query tile
+      if (n_tiles > 1) fetch_raw(1, raw);        // are all in flight before anything is read
       load_q(start_rotated);
-      interpret(0, raw0, e_nxt0, e_nxt1, dead_lo, dead_hi);
-      load_kv(0, e_nxt0, e_nxt1);
-      cp_async_commit();
-      if (n_tiles > 1) interpret(1, raw, e_nxt0, e_nxt1, dead_nxt_lo, dead_nxt_hi);
+      interpret(0, raw0, e0, e1, dead_lo, dead_hi);
+      load_rows(0, e0, e1, true, false);
+      cp_async_commit();                                   // Q + K(0)
+      if (n_tiles > 1) {
+        interpret(1, raw, ev0, ev1, dead1_lo, dead1_hi);
+        load_rows(1, ev0, ev1, true, false);
+      }
+      cp_async_commit();                                   // K(1)
+      load_rows(0, e0, e1, false, true);
+      cp_async_commit();                                   // V(0)
+      if (n_tiles > 2) {
+        fetch_raw(2, raw);
+        interpret(2, raw, ek0, ek1, dead2_lo, dead2_hi);
+      }
     }
     if (!warp_live || spread) {  // rows (or, spread, column slices) of P that are never written stay zero
 #pragma unroll
       for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(sP + tid * 128 + (c << 4)) = make_uint4(0, 0, 0, 0);
     }
+    cp_async_wait<2>();            // Q + K(0)
+    fence_proxy_async();
+    arrive(bar_k);
+
     // online softmax of this thread's row over NC key columns of the tile starting at col0, exp2
-    // domain; raw scores are scaled inside the fma
-    auto softmax_tile = [&](auto nc_tag, const int col0, const int i) {
+    // domain; raw scores are scaled inside the fma.  First half: scores and their maximum.
+    uint32_t s[BN];
+    float mx;
+    bool grow;
+    auto softmax_scores = [&](auto nc_tag, const int col0, const int i) {
       constexpr int NC = decltype(nc_tag)::value;
-      uint32_t s[NC];
       if constexpr (NC == 64) {
-        tmem_ld32(t_lane + kColS, s);
-        tmem_ld32(t_lane + kColS + 32, s + 32);
+        tmem_ld32(t_lane + kColS + (i & 1) * BN, s);
+        tmem_ld32(t_lane + kColS + (i & 1) * BN + 32, s + 32);
       } else {
         static_assert(NC == 16, "column slices are 16 wide");
-        tmem_ld16(t_lane + kColS + col0, s);
+        tmem_ld16(t_lane + kColS + (i & 1) * BN + col0, s);
       }
       tmem_wait_ld();
       const uint64_t dead = ((((uint64_t)dead_hi) << 32) | dead_lo) >> col0;
-      float mx = -INFINITY;
+      mx = -INFINITY;
 #pragma unroll
       for (int c = 0; c < NC; ++c) {
         const float v = ((dead >> c) & 1ull) ? -INFINITY : __uint_as_float(s[c]);
@@ -406,7 +506,11 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
         mx = fmaxf(mx, v);
       }
       mx *= scale_log2;
-      const bool grow = mx > m_ref + 8.0f;  // also true on the first tile with a live key (m_ref = -inf)
+      grow = mx > m_ref + 8.0f;  // also true on the first tile with a live key (m_ref = -inf)
+    };
+    // Second half, once the previous P V product is done: lazy rescale of O, P
+    auto softmax_weights = [&](auto nc_tag, const int col0, const int i) {
+      constexpr int NC = decltype(nc_tag)::value;
       if (__any_sync(0xFFFFFFFFu, grow) && i > 0) {
         const float f = grow ? ex2(m_ref - mx) : 1.0f;
         l_sum *= f;
@@ -438,77 +542,70 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
       }
       l_sum += rs;
     };
+    auto softmax_half = [&](const bool second, const int i) {
+      if (!warp_live) return;  // warps whose 32 rows are all padding skip the softmax (their P rows stay zero)
+      if constexpr (COPIES > 1) {
+        if (spread) {
+          if (!second) softmax_scores(std::integral_constant<int, BN / COPIES>{}, warp * (BN / COPIES), i);
+          else softmax_weights(std::integral_constant<int, BN / COPIES>{}, warp * (BN / COPIES), i);
+          return;
+        }
+      }
+      if (!second) softmax_scores(std::integral_constant<int, BN>{}, 0, i);
+      else softmax_weights(std::integral_constant<int, BN>{}, 0, i);
+    };
 
+    bool ok = true;
     for (int i = 0; i < n_tiles; ++i) {
-      if (i + 2 < n_tiles) fetch_raw(i + 2, raw);   // looked at when the iteration ends
-      cp_async_wait<0>();          // tile i (and the query tile) have landed for this thread
-      fence_proxy_async();
-      tc_fence_before();
-      __syncthreads();
-      tc_fence_after();
-
-      const uint32_t kb = smem_u32(sK) + (i & 1) * KV_BYTES, vb = smem_u32(sV) + (i & 1) * KV_BYTES;
-      if (tid == 0) {
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t a_off = (ks / 4) * (BM * 128) + (ks % 4) * 32;
-          const uint32_t b_off = (ks / 4) * (BN * 128) + (ks % 4) * 32;
-          mma_ss(tmem_base + kColS, make_desc(smem_u32(sQ) + a_off, 16, 1024), make_desc(kb + b_off, 16, 1024), idesc_s,
-                 ks > 0 ? 1u : 0u);
-        }
-        mma_commit(bar_s);
-      }
-      // the previous P V product must be done before its K/V stage is refilled, O is rescaled
-      // or P overwritten
-      bool ok = true;
-      if (i > 0) ok = mbar_wait(bar_o, (uint32_t)((i - 1) & 1));
-      if (i + 1 < n_tiles) load_kv(i + 1, e_nxt0, e_nxt1);
-      cp_async_commit();
-      ok = mbar_wait(bar_s, (uint32_t)(i & 1)) && ok;
-      tc_fence_after();
-      if (warp_live) {  // warps whose 32 rows are all padding skip the softmax (their P rows stay zero)
-        if constexpr (COPIES > 1) {
-          if (spread) softmax_tile(std::integral_constant<int, BN / COPIES>{}, warp * (BN / COPIES), i);
-          else softmax_tile(std::integral_constant<int, BN>{}, 0, i);
-        } else {
-          softmax_tile(std::integral_constant<int, BN>{}, 0, i);
-        }
-      }
-
-      // query tile swap at the partition boundary: every S product against the rotated
-      // queries has completed (bar_s of this tile was awaited)
-      const bool swap_q = start_rotated && i == nt0 - 1 && nt1 > 0;
-      if (swap_q) {
+      if (i + 3 < n_tiles) fetch_raw(i + 3, raw);   // looked at when the iteration ends
+      // query tile swap at the partition boundary: S(i) was the last product against the
+      // rotated queries; S(i+1) may only be issued after the plain ones are in place
+      if (start_rotated && i + 1 == nt0 && nt1 > 0) {
+        ok = wait_bar(bar_s + (i & 1) * 8, (uint32_t)((i >> 1) & 1)) && ok;
         load_q(false);
         cp_async_commit();
         cp_async_wait<0>();
       }
+      if (i + 1 < n_tiles) {
+        cp_async_wait<1>();                            // K(i+1) has landed for this thread
+        fence_proxy_async();
+        arrive(bar_k + ((i + 1) & 1) * 8);
+      }
+      ok = wait_bar(bar_s + (i & 1) * 8, (uint32_t)((i >> 1) & 1)) && ok;
+      tc_fence_after();
+      if (i + 2 < n_tiles) load_rows(i + 2, ek0, ek1, true, false);   // S(i) is done: K(i) may go
+      cp_async_commit();                               // K(i+2)
+      softmax_half(false, i);
+      // the previous P V product must be done before O is rescaled, P overwritten or its V
+      // stage refilled
+      if (i > 0) ok = wait_bar(bar_o, (uint32_t)((i - 1) & 1)) && ok;
+      tc_fence_after();
+      if (i + 1 < n_tiles) load_rows(i + 1, ev0, ev1, false, true);
+      cp_async_commit();                               // V(i+1)
+      softmax_half(true, i);
+      cp_async_wait<2>();                              // V(i) has landed for this thread
       fence_proxy_async();
       tc_fence_before();
-      if (__syncthreads_or(!ok)) { failed = true; break; }
-      tc_fence_after();
-
-      if (tid == 0) {
-#pragma unroll
-        for (int ks = 0; ks < BN / 16; ++ks) {
-          mma_ss(tmem_base + kColO, make_desc(smem_u32(sP) + ks * 32, 16, 1024),
-                 make_desc(vb + ks * 2048, BN * 128, 1024), idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
-        }
-        mma_commit(bar_o);
-      }
-      dead_lo = dead_nxt_lo;
-      dead_hi = dead_nxt_hi;
-      if (i + 2 < n_tiles) interpret(i + 2, raw, e_nxt0, e_nxt1, dead_nxt_lo, dead_nxt_hi);
+      arrive(bar_p);
+      dead_lo = dead1_lo;
+      dead_hi = dead1_hi;
+      dead1_lo = dead2_lo;
+      dead1_hi = dead2_hi;
+      ev0 = ek0;
+      ev1 = ek1;
+      if (i + 3 < n_tiles) interpret(i + 3, raw, ek0, ek1, dead2_lo, dead2_hi);
+      if (!ok) break;
     }
-
-    if (!failed) {
-      bool ok = mbar_wait(bar_o, (uint32_t)((n_tiles - 1) & 1));
-      tc_fence_after();
-      if (__syncthreads_or(!ok)) failed = true;
-    }
+    if (ok) ok = wait_bar(bar_o, (uint32_t)((n_tiles - 1) & 1));
+    tc_fence_after();
+    if (!ok) *give_up = 1;
+    rows_sync();
+    failed = *give_up != 0;
   }
 
-  if (failed) {
+  if (warp == 4) {
+    // nothing to write
+  } else if (failed) {
     if (tid == 0 && err_flag) atomicExch(err_flag, 5);
   } else if (COPIES > 1 && spread) {
     // ---- fold the four column slices of every row, then write (or publish) the rows ----------
@@ -518,7 +615,7 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
     float4* part = reinterpret_cast<float4*>(sK);   // [4 slices][32 rows][F4], float4 index swizzled by the row
     xm[tid] = m_ref;
     xm[BM + tid] = l_sum;
-    __syncthreads();
+    rows_sync();
     auto fold_ml = [&](int row, float& m_all, float& l_all) {   // same order for every reader
       m_all = -INFINITY;
 #pragma unroll
@@ -552,7 +649,7 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
                         __uint_as_float(o[c + 2]) * w_own, __uint_as_float(o[c + 3]) * w_own);
       }
     }
-    __syncthreads();
+    rows_sync();
     // thread t: row t / 4, quarter t % 4 of its columns
     const int r = tid >> 2, qd = tid & 3;
     constexpr int QF4 = F4 / 4;                     // float4 per quarter row
@@ -587,10 +684,10 @@ __global__ void __launch_bounds__(NT, 2) attention_tc_kernel(
         if (qd == 0) __stcg(reinterpret_cast<float2*>(sp.part_ml + ((int64_t)1 * sp.total_rows + grow) * 2), make_float2(m_all, l_all));
       }
       __threadfence();
-      __syncthreads();
+      rows_sync();
       int* ticket_box = reinterpret_cast<int*>(xm);   // xm is no longer read
       if (tid == 0) *ticket_box = atomicAdd(sp.tickets + (int64_t)b * n_kv_heads + kvh, 1);
-      __syncthreads();
+      rows_sync();
       write_out = (*ticket_box & 1) != 0;             // the other part is already in scratch
       if (write_out) {
         __threadfence();
@@ -754,7 +851,7 @@ static int launch(const AttnArgs& a, const SplitArgs* split) {
   do {                                                                                                                \
     auto kern = attention_tc_kernel<T, TR, TC, D, KS, SPL, CP>;                                                       \
     ACACHE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));            \
-    kern<<<grid, NT, smem, a.st>>>((const T*)a.q, a.q_stride, (T*)a.out, a.o_stride, (const T*)a.k_cache,             \
+    kern<<<grid, NT_ALL, smem, a.st>>>((const T*)a.q, a.q_stride, (T*)a.out, a.o_stride, (const T*)a.k_cache,             \
                                    (const T*)a.v_cache, a.num_slots, a.n_heads, a.n_kv_heads, a.cu_q, a.cu_k,         \
                                    a.slot_map, a.block_tables, a.table_stride, a.block_size,                          \
                                    a.scale * 1.4426950408889634f, a.shared_prefix_len, a.shared_kv_lens,              \
