@@ -46,6 +46,7 @@ constexpr int BM = 128;      // virtual rows per CTA
 constexpr int BN = 64;       // keys per tile
 constexpr int NT = 128;      // threads that stage K/V and own the rows (warps 0-3)
 constexpr int NT_ALL = 160;  // + warp 4, whose first lane issues every tensor-core product
+constexpr int NT_LOAD = 288; // + warps 5-8 that take the K/V staging over from the row-owning warps (LOADERS)
 constexpr int GROUP = 4;     // requests per shared-span work item (one per warp)
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kColS = 0, kColO = 128;
@@ -59,8 +60,8 @@ struct SplitArgs {
   float* part_o;        // [2][total_rows][D]  unnormalised accumulator
 };
 
-template <typename T, typename TR, typename TC, int D, bool KEYSIDE, bool SPLIT, int COPIES>
-__global__ void __launch_bounds__(NT_ALL, 2) attention_tc_kernel(
+template <typename T, typename TR, typename TC, int D, bool KEYSIDE, bool SPLIT, int COPIES, bool LOADERS>
+__global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_kernel(
     const T* __restrict__ q, int64_t q_stride, T* __restrict__ out, int64_t o_stride, const T* __restrict__ k_cache,
     const T* __restrict__ v_cache, int64_t num_slots, int n_heads, int n_kv_heads, const int32_t* __restrict__ cu_q,
     const int32_t* __restrict__ cu_k, const int32_t* __restrict__ slot_map, const int32_t* __restrict__ block_tables,
@@ -84,9 +85,10 @@ __global__ void __launch_bounds__(NT_ALL, 2) attention_tc_kernel(
   uint8_t* sV = sK + 2 * KV_BYTES;       // 2 stages
   uint8_t* sP = sV + 2 * KV_BYTES;
   // mbarriers: [0],[1] K stage landed (128 arrivals); [2],[3] S buffer computed (tcgen05.commit);
-  // [4] P written and V landed (128 arrivals); [5] P V product done (tcgen05.commit)
+  // [4] P written (and, without loader warps, V landed) (128 arrivals); [5] P V product done
+  // (tcgen05.commit); [6],[7] V stage landed (128 arrivals, loader warps only)
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
   // per request of the item (one unless this is a kind-A item): first query row, virtual
   // rows, first slot-map entry, rotation row
   int* rq_q0 = reinterpret_cast<int*>(tmem_slot + 1);
@@ -94,8 +96,12 @@ __global__ void __launch_bounds__(NT_ALL, 2) attention_tc_kernel(
   int* rq_kv0 = rq_vrows + GROUP;
   int* rq_shift = rq_kv0 + GROUP;
   volatile int* give_up = rq_shift + GROUP;   // set by the first role whose bounded wait runs out
+  // rows of a tile that take no part, published by the loader warps for the row-owning warps
+  volatile uint32_t* dead_ring = reinterpret_cast<volatile uint32_t*>(give_up + 1);   // [4 tiles][2]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool is_loader = LOADERS && warp >= 5;
+  const int ltid = is_loader ? tid - NT_ALL : tid;   // index among the 128 threads that stage K/V
   const int g = n_heads / n_kv_heads;
   const int kv_row = n_kv_heads * D;
   const bool query_side = shared_kv_lens != nullptr && affix_shifts != nullptr;
@@ -169,7 +175,7 @@ __global__ void __launch_bounds__(NT_ALL, 2) attention_tc_kernel(
   const int vr = (kind_a || spread) ? lane : m0 + tid;
 
   const uint32_t bar_k = smem_u32(&bars[0]), bar_s = smem_u32(&bars[2]), bar_p = smem_u32(&bars[4]),
-                 bar_o = smem_u32(&bars[5]);
+                 bar_o = smem_u32(&bars[5]), bar_v = smem_u32(&bars[6]);
   if (tid == 0) {
     mbar_init(bar_k, NT);
     mbar_init(bar_k + 8, NT);
@@ -177,6 +183,8 @@ __global__ void __launch_bounds__(NT_ALL, 2) attention_tc_kernel(
     mbar_init(bar_s + 8, 1);
     mbar_init(bar_p, NT);
     mbar_init(bar_o, 1);
+    mbar_init(bar_v, NT);
+    mbar_init(bar_v + 8, NT);
     *give_up = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -213,7 +221,7 @@ __global__ void __launch_bounds__(NT_ALL, 2) attention_tc_kernel(
   // ---- loaders -----------------------------------------------------------------------
   auto load_q = [&](bool rotated) {
     // chunk id = it*NT + tid: 16 consecutive threads cover one row
-    for (int id = tid; id < BM * CH; id += NT) {
+    for (int id = ltid; id < BM * CH; id += NT) {
       const int r = id / CH, c = id % CH;
       const int rr = kind_a ? (r >> 5) : 0;             // request slot of the row
       const int v = (kind_a || spread) ? (r & 31) : m0 + r;
@@ -257,7 +265,7 @@ __global__ void __launch_bounds__(NT_ALL, 2) attention_tc_kernel(
   // (reported), -3 past the end of the run.  Lane l holds rows l and l + 32 of the tile.
   constexpr int ITER = BN * CH / NT;   // rows gathered per thread and tile
   constexpr int RPI = NT / CH;         // rows covered per iteration
-  const int my_c = tid % CH, my_r = tid / CH;
+  const int my_c = ltid % CH, my_r = ltid / CH;
   // The words of the slot map (or block table) are only LOADED here, two tiles ahead, and not
   // looked at before the end of the iteration, so no warp waits for them.
   constexpr int NR = SPLIT ? GROUP : 1;   // requests whose entries a warp reads
@@ -401,6 +409,80 @@ __global__ void __launch_bounds__(NT_ALL, 2) attention_tc_kernel(
   // barrier of the 128 row-owning threads only (warp 4 never takes part)
   auto rows_sync = [&]() { asm volatile("bar.sync 1, 128;" ::: "memory"); };
 
+  uint32_t dead_lo = 0, dead_hi = 0;   // rows of the current tile that take no part
+  // online softmax of this thread's row over NC key columns of the tile starting at col0, exp2
+  // domain; raw scores are scaled inside the fma.  First half: scores and their maximum.
+  uint32_t s[BN];
+  float mx;
+  bool grow;
+  auto softmax_scores = [&](auto nc_tag, const int col0, const int i) {
+    constexpr int NC = decltype(nc_tag)::value;
+    if constexpr (NC == 64) {
+      tmem_ld32(t_lane + kColS + (i & 1) * BN, s);
+      tmem_ld32(t_lane + kColS + (i & 1) * BN + 32, s + 32);
+    } else {
+      static_assert(NC == 16, "column slices are 16 wide");
+      tmem_ld16(t_lane + kColS + (i & 1) * BN + col0, s);
+    }
+    tmem_wait_ld();
+    const uint64_t dead = ((((uint64_t)dead_hi) << 32) | dead_lo) >> col0;
+    mx = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      const float v = ((dead >> c) & 1ull) ? -INFINITY : __uint_as_float(s[c]);
+      s[c] = __float_as_uint(v);
+      mx = fmaxf(mx, v);
+    }
+    mx *= scale_log2;
+    grow = mx > m_ref + 8.0f;  // also true on the first tile with a live key (m_ref = -inf)
+  };
+  // Second half, once the previous P V product is done: lazy rescale of O, P
+  auto softmax_weights = [&](auto nc_tag, const int col0, const int i) {
+    constexpr int NC = decltype(nc_tag)::value;
+    if (__any_sync(0xFFFFFFFFu, grow) && i > 0) {
+      const float f = grow ? ex2(m_ref - mx) : 1.0f;
+      l_sum *= f;
+      uint32_t o[32];
+#pragma unroll 1
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        tmem_ld32(t_lane + kColO + c0, o);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * f);
+        tmem_st32(t_lane + kColO + c0, o);
+      }
+      tmem_wait_st();
+    }
+    if (grow) m_ref = mx;
+    const float m_use = m_ref == -INFINITY ? 0.f : m_ref;   // no live key so far: every p is 0
+    float rs = 0.f;
+#pragma unroll
+    for (int c = 0; c < NC; c += 8) {
+      uint32_t w[4];
+#pragma unroll
+      for (int e = 0; e < 8; e += 2) {
+        const float p0 = ex2(fmaf(__uint_as_float(s[c + e]), scale_log2, -m_use));
+        const float p1 = ex2(fmaf(__uint_as_float(s[c + e + 1]), scale_log2, -m_use));
+        rs += p0 + p1;
+        w[e / 2] = pack2<T>(p0, p1);
+      }
+      *reinterpret_cast<uint4*>(sP + tid * 128 + ((((col0 + c) / 8) ^ (tid & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    l_sum += rs;
+  };
+  auto softmax_half = [&](const bool second, const int i) {
+    if (!warp_live) return;  // warps whose 32 rows are all padding skip the softmax (their P rows stay zero)
+    if constexpr (COPIES > 1) {
+      if (spread) {
+        if (!second) softmax_scores(std::integral_constant<int, BN / COPIES>{}, warp * (BN / COPIES), i);
+        else softmax_weights(std::integral_constant<int, BN / COPIES>{}, warp * (BN / COPIES), i);
+        return;
+      }
+    }
+    if (!second) softmax_scores(std::integral_constant<int, BN>{}, 0, i);
+    else softmax_weights(std::integral_constant<int, BN>{}, 0, i);
+  };
+
   // Roles.  Warp 4, one thread: issues S(i+1) as soon as K(i+1) has landed, i.e. one tile
   // ahead of the softmax (two S buffers in TMEM), and P V(i) as soon as P(i) is written.
   // Warps 0-3: stage K/V, run the softmax, never wait for one another inside the loop, only
@@ -427,6 +509,7 @@ __global__ void __launch_bounds__(NT_ALL, 2) attention_tc_kernel(
       };
       bool ok = wait_bar(bar_k, 0);
       tc_fence_after();
+      if (LOADERS) __threadfence_block();
       if (ok) issue_s(0);
       for (int i = 0; i < n_tiles && ok; ++i) {
         if (i + 1 < n_tiles) {
@@ -434,9 +517,11 @@ __global__ void __launch_bounds__(NT_ALL, 2) attention_tc_kernel(
           ok = wait_bar(bar_k + ((i + 1) & 1) * 8, (uint32_t)(((i + 1) >> 1) & 1));
           tc_fence_after();
           if (!ok) break;
+          if (LOADERS) __threadfence_block();   // what the loaders wrote before K(i+1) (the tile's dead rows) is passed on
           issue_s(i + 1);
         }
         ok = wait_bar(bar_p, (uint32_t)(i & 1));
+        if (LOADERS) ok = wait_bar(bar_v + (i & 1) * 8, (uint32_t)((i >> 1) & 1)) && ok;
         tc_fence_after();
         if (!ok) break;
         const uint32_t vb = smem_u32(sV) + (i & 1) * KV_BYTES;
@@ -448,12 +533,18 @@ __global__ void __launch_bounds__(NT_ALL, 2) attention_tc_kernel(
         mma_commit(bar_o);
       }
     }
-  } else if (n_tiles > 0) {
-    // ---- prologue ----------------------------------------------------------------------
+  } else if (n_tiles > 0 && (!LOADERS || is_loader)) {
+    // ---- the threads that stage K/V (and, without loader warps, also own the rows) ---------
+    auto publish_dead = [&](int tile, uint32_t lo, uint32_t hi) {
+      if (LOADERS && ltid == 0) {
+        dead_ring[(tile & 3) * 2] = lo;
+        dead_ring[(tile & 3) * 2 + 1] = hi;
+      }
+    };
     const bool start_rotated = query_side && nt0 > 0;
     int32_t raw[NR][2];
     int32_t ev0 = -3, ev1 = -3, ek0 = -3, ek1 = -3;        // entries of tile i+1 (V load) / tile i+2 (K load)
-    uint32_t dead_lo, dead_hi, dead1_lo = 0, dead1_hi = 0, dead2_lo = 0, dead2_hi = 0;  // tiles i, i+1, i+2
+    uint32_t dead1_lo = 0, dead1_hi = 0, dead2_lo = 0, dead2_hi = 0;  // tiles i+1, i+2 (dead_lo/hi: tile i)
     {
       int32_t raw0[NR][2], e0, e1;
       fetch_raw(0, raw0);                        // the lookups of the first tiles and the query tile
@@ -473,87 +564,17 @@ __global__ void __launch_bounds__(NT_ALL, 2) attention_tc_kernel(
         fetch_raw(2, raw);
         interpret(2, raw, ek0, ek1, dead2_lo, dead2_hi);
       }
+      publish_dead(0, dead_lo, dead_hi);
+      publish_dead(1, dead1_lo, dead1_hi);
+      publish_dead(2, dead2_lo, dead2_hi);
     }
-    if (!warp_live || spread) {  // rows (or, spread, column slices) of P that are never written stay zero
+    if (!LOADERS && (!warp_live || spread)) {  // rows (or, spread, column slices) of P that are never written stay zero
 #pragma unroll
       for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(sP + tid * 128 + (c << 4)) = make_uint4(0, 0, 0, 0);
     }
     cp_async_wait<2>();            // Q + K(0)
     fence_proxy_async();
     arrive(bar_k);
-
-    // online softmax of this thread's row over NC key columns of the tile starting at col0, exp2
-    // domain; raw scores are scaled inside the fma.  First half: scores and their maximum.
-    uint32_t s[BN];
-    float mx;
-    bool grow;
-    auto softmax_scores = [&](auto nc_tag, const int col0, const int i) {
-      constexpr int NC = decltype(nc_tag)::value;
-      if constexpr (NC == 64) {
-        tmem_ld32(t_lane + kColS + (i & 1) * BN, s);
-        tmem_ld32(t_lane + kColS + (i & 1) * BN + 32, s + 32);
-      } else {
-        static_assert(NC == 16, "column slices are 16 wide");
-        tmem_ld16(t_lane + kColS + (i & 1) * BN + col0, s);
-      }
-      tmem_wait_ld();
-      const uint64_t dead = ((((uint64_t)dead_hi) << 32) | dead_lo) >> col0;
-      mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < NC; ++c) {
-        const float v = ((dead >> c) & 1ull) ? -INFINITY : __uint_as_float(s[c]);
-        s[c] = __float_as_uint(v);
-        mx = fmaxf(mx, v);
-      }
-      mx *= scale_log2;
-      grow = mx > m_ref + 8.0f;  // also true on the first tile with a live key (m_ref = -inf)
-    };
-    // Second half, once the previous P V product is done: lazy rescale of O, P
-    auto softmax_weights = [&](auto nc_tag, const int col0, const int i) {
-      constexpr int NC = decltype(nc_tag)::value;
-      if (__any_sync(0xFFFFFFFFu, grow) && i > 0) {
-        const float f = grow ? ex2(m_ref - mx) : 1.0f;
-        l_sum *= f;
-        uint32_t o[32];
-#pragma unroll 1
-        for (int c0 = 0; c0 < D; c0 += 32) {
-          tmem_ld32(t_lane + kColO + c0, o);
-          tmem_wait_ld();
-#pragma unroll
-          for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * f);
-          tmem_st32(t_lane + kColO + c0, o);
-        }
-        tmem_wait_st();
-      }
-      if (grow) m_ref = mx;
-      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;   // no live key so far: every p is 0
-      float rs = 0.f;
-#pragma unroll
-      for (int c = 0; c < NC; c += 8) {
-        uint32_t w[4];
-#pragma unroll
-        for (int e = 0; e < 8; e += 2) {
-          const float p0 = ex2(fmaf(__uint_as_float(s[c + e]), scale_log2, -m_use));
-          const float p1 = ex2(fmaf(__uint_as_float(s[c + e + 1]), scale_log2, -m_use));
-          rs += p0 + p1;
-          w[e / 2] = pack2<T>(p0, p1);
-        }
-        *reinterpret_cast<uint4*>(sP + tid * 128 + ((((col0 + c) / 8) ^ (tid & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-      l_sum += rs;
-    };
-    auto softmax_half = [&](const bool second, const int i) {
-      if (!warp_live) return;  // warps whose 32 rows are all padding skip the softmax (their P rows stay zero)
-      if constexpr (COPIES > 1) {
-        if (spread) {
-          if (!second) softmax_scores(std::integral_constant<int, BN / COPIES>{}, warp * (BN / COPIES), i);
-          else softmax_weights(std::integral_constant<int, BN / COPIES>{}, warp * (BN / COPIES), i);
-          return;
-        }
-      }
-      if (!second) softmax_scores(std::integral_constant<int, BN>{}, 0, i);
-      else softmax_weights(std::integral_constant<int, BN>{}, 0, i);
-    };
 
     bool ok = true;
     for (int i = 0; i < n_tiles; ++i) {
@@ -575,25 +596,61 @@ __global__ void __launch_bounds__(NT_ALL, 2) attention_tc_kernel(
       tc_fence_after();
       if (i + 2 < n_tiles) load_rows(i + 2, ek0, ek1, true, false);   // S(i) is done: K(i) may go
       cp_async_commit();                               // K(i+2)
-      softmax_half(false, i);
+      if (!LOADERS) softmax_half(false, i);
       // the previous P V product must be done before O is rescaled, P overwritten or its V
       // stage refilled
       if (i > 0) ok = wait_bar(bar_o, (uint32_t)((i - 1) & 1)) && ok;
       tc_fence_after();
       if (i + 1 < n_tiles) load_rows(i + 1, ev0, ev1, false, true);
       cp_async_commit();                               // V(i+1)
-      softmax_half(true, i);
+      if (!LOADERS) softmax_half(true, i);
       cp_async_wait<2>();                              // V(i) has landed for this thread
       fence_proxy_async();
       tc_fence_before();
-      arrive(bar_p);
+      if (LOADERS) arrive(bar_v + (i & 1) * 8);
+      else arrive(bar_p);
       dead_lo = dead1_lo;
       dead_hi = dead1_hi;
       dead1_lo = dead2_lo;
       dead1_hi = dead2_hi;
       ev0 = ek0;
       ev1 = ek1;
-      if (i + 3 < n_tiles) interpret(i + 3, raw, ek0, ek1, dead2_lo, dead2_hi);
+      if (i + 3 < n_tiles) {
+        interpret(i + 3, raw, ek0, ek1, dead2_lo, dead2_hi);
+        // ring slot (i+3)&3 held tile i-1, whose softmax ended before P V(i-1) was issued
+        publish_dead(i + 3, dead2_lo, dead2_hi);
+      }
+      if (!ok) break;
+    }
+    if (!LOADERS) {
+      if (ok) ok = wait_bar(bar_o, (uint32_t)((n_tiles - 1) & 1));
+      tc_fence_after();
+      if (!ok) *give_up = 1;
+      rows_sync();
+      failed = *give_up != 0;
+    } else if (!ok) {
+      *give_up = 1;
+    }
+  } else if (n_tiles > 0) {
+    // ---- row-owning warps when loader warps do the staging: softmax only ----------------------
+    if (!warp_live || spread) {  // rows (or, spread, column slices) of P that are never written stay zero
+#pragma unroll
+      for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(sP + tid * 128 + (c << 4)) = make_uint4(0, 0, 0, 0);
+    }
+    bool ok = true;
+    for (int i = 0; i < n_tiles; ++i) {
+      ok = wait_bar(bar_s + (i & 1) * 8, (uint32_t)((i >> 1) & 1)) && ok;   // also: the tile's dead rows are published
+      tc_fence_after();
+      dead_lo = dead_ring[(i & 3) * 2];
+      dead_hi = dead_ring[(i & 3) * 2 + 1];
+      softmax_half(false, i);
+      // the previous P V product must be done before O is rescaled or P overwritten
+      if (i > 0) ok = wait_bar(bar_o, (uint32_t)((i - 1) & 1)) && ok;
+      tc_fence_after();
+      softmax_half(true, i);
+      fence_proxy_async();
+      tc_fence_before();
+      arrive(bar_p);
       if (!ok) break;
     }
     if (ok) ok = wait_bar(bar_o, (uint32_t)((n_tiles - 1) & 1));
@@ -603,7 +660,7 @@ __global__ void __launch_bounds__(NT_ALL, 2) attention_tc_kernel(
     failed = *give_up != 0;
   }
 
-  if (warp == 4) {
+  if (warp >= 4) {
     // nothing to write
   } else if (failed) {
     if (tid == 0 && err_flag) atomicExch(err_flag, 5);
@@ -836,7 +893,7 @@ template <> struct PromoteT<__nv_bfloat16, __nv_bfloat16> { using type = __nv_bf
 template <typename T, typename TR, int D>
 static int launch(const AttnArgs& a, const SplitArgs* split) {
   using TC = typename PromoteT<T, TR>::type;
-  constexpr size_t smem = BM * D * sizeof(T) + 4 * BN * D * sizeof(T) + BM * BN * sizeof(T) + 128;
+  constexpr size_t smem = BM * D * sizeof(T) + 4 * BN * D * sizeof(T) + BM * BN * sizeof(T) + 256;
   const int g = a.n_heads / a.n_kv_heads;
   const bool relocate = a.shared_prefix_len > 0 && a.affix_shifts != nullptr;
   const bool query_side = relocate && a.shared_kv_lens != nullptr;
@@ -847,23 +904,23 @@ static int launch(const AttnArgs& a, const SplitArgs* split) {
     sp = *split;
     grid = dim3(sp.n_items_a + a.batch * a.n_kv_heads, 1, 1);
   }
-#define ACACHE_TC_LAUNCH(KS, SPL, CP)                                                                                 \
+#define ACACHE_TC_LAUNCH(KS, SPL, CP, LD)                                                                             \
   do {                                                                                                                \
-    auto kern = attention_tc_kernel<T, TR, TC, D, KS, SPL, CP>;                                                       \
+    auto kern = attention_tc_kernel<T, TR, TC, D, KS, SPL, CP, LD>;                                                   \
     ACACHE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));            \
-    kern<<<grid, NT_ALL, smem, a.st>>>((const T*)a.q, a.q_stride, (T*)a.out, a.o_stride, (const T*)a.k_cache,             \
-                                   (const T*)a.v_cache, a.num_slots, a.n_heads, a.n_kv_heads, a.cu_q, a.cu_k,         \
-                                   a.slot_map, a.block_tables, a.table_stride, a.block_size,                          \
-                                   a.scale * 1.4426950408889634f, a.shared_prefix_len, a.shared_kv_lens,              \
-                                   relocate ? a.affix_shifts : nullptr, (const TR*)a.rope_cos, (const TR*)a.rope_sin, \
-                                   a.rope_stride, a.rope_rows, a.err_flag, sp);                                       \
+    kern<<<grid, LD ? NT_LOAD : NT_ALL, smem, a.st>>>(                                                                \
+        (const T*)a.q, a.q_stride, (T*)a.out, a.o_stride, (const T*)a.k_cache, (const T*)a.v_cache, a.num_slots,      \
+        a.n_heads, a.n_kv_heads, a.cu_q, a.cu_k, a.slot_map, a.block_tables, a.table_stride, a.block_size,            \
+        a.scale * 1.4426950408889634f, a.shared_prefix_len, a.shared_kv_lens, relocate ? a.affix_shifts : nullptr,    \
+        (const TR*)a.rope_cos, (const TR*)a.rope_sin, a.rope_stride, a.rope_rows, a.err_flag, sp);                    \
   } while (0)
   // requests of at most 32 virtual rows (block decode): spread the softmax over the four warps
+  // and give the K/V staging to four more warps
   const bool small_rows = a.max_q * g <= 32;
-  if (split) ACACHE_TC_LAUNCH(false, true, 4);
-  else if (key_side) ACACHE_TC_LAUNCH(true, false, 1);
-  else if (small_rows) ACACHE_TC_LAUNCH(false, false, 4);
-  else ACACHE_TC_LAUNCH(false, false, 1);
+  if (split) ACACHE_TC_LAUNCH(false, true, 4, false);
+  else if (key_side) ACACHE_TC_LAUNCH(true, false, 1, false);
+  else if (small_rows) ACACHE_TC_LAUNCH(false, false, 4, true);
+  else ACACHE_TC_LAUNCH(false, false, 1, false);
 #undef ACACHE_TC_LAUNCH
   ACACHE_LAUNCH_CHECK();
   return ACACHE_OK;
