@@ -1,20 +1,28 @@
 // Bidirectional varlen attention over the slot-mapped paged cache on the 5th-generation
 // tensor cores (tcgen05) with TMEM accumulators, for bf16/fp16 and head_dim 64/128.
 //
-// One CTA (128 threads) = one (request, KV head, tile of 128 "virtual rows").  A virtual
-// row is a (query, head-of-the-GQA-group) pair, so all query heads that share a KV head
-// share one pass over its K/V.  Per tile of 64 keys:
-//   * every warp reads the tile's 64 slot-map entries (two per lane) two tiles ahead; an
-//     entry of -1 is a key that takes no part (its row is zero-filled and its score masked);
+// One CTA = one (request, KV head, tile of 128 "virtual rows").  A virtual row is a
+// (query, head-of-the-GQA-group) pair, so all query heads that share a KV head share one
+// pass over its K/V.  Roles inside the CTA, handing over through mbarriers only:
+//   warps 0-3  own the rows: thread t owns row t (TMEM lane t): tcgen05.ld of its scores,
+//              online softmax in the exp2 domain, P written to shared memory as an A operand;
+//              they also stage K/V, unless (block decode) warps 5-8 do that for them;
+//   warp 4     one thread issues every tcgen05.mma: S(i+1) = Q K(i+1)^T as soon as K(i+1)
+//              has landed, one tile ahead of the softmax, into one of two S buffers in TMEM,
+//              and O += P(i) V(i) as soon as P(i) is written;
+//   warps 5-8  (LOADERS, requests of at most 32 virtual rows) stage K/V and publish which
+//              rows of a tile take no part.
+// Per tile of 64 keys:
+//   * the tile's 64 slot-map entries (two per lane) are loaded three tiles ahead and looked
+//     at one iteration later, so nothing waits for a lookup; an entry of -1 is a key that
+//     takes no part (its row is zero-filled and its score masked);
 //   * K and V rows are gathered with 16-byte cp.async into shared memory in the
-//     128-byte-swizzled layout the MMA descriptors expect (double buffered, the next tile
-//     is in flight during the current one).  Loads of tile i+1 are issued after the S
-//     product of tile i has been queued and the P V product of tile i-1, the last reader of
-//     the stage they overwrite, has completed;
-//   * S = Q K^T      : tcgen05.mma, A = Q (K-major), B = K rows (K-major), fp32 in TMEM,
-//   * thread t owns row t (TMEM lane t): tcgen05.ld of its 64 scores, online softmax
-//     in the exp2 domain, P written back to shared memory as the A operand,
-//   * O += P V       : tcgen05.mma, B = V rows (MN-major), accumulated in TMEM.
+//     128-byte-swizzled layout the MMA descriptors expect (Q/K/P K-major, V MN-major), two
+//     stages each; a stage is refilled as soon as its last reader (the S product for K, the
+//     P V product for V) is done;
+//   * S and O are fp32 in TMEM (256 columns per CTA, two CTAs per SM).
+// Requests of at most 32 virtual rows (COPIES = 4): the rows are staged four times and warp w
+// runs the softmax of key columns 16w..16w+15 only; the four slices are folded at the end.
 // O is only rescaled when a row's running maximum grows by more than 2^8 (otherwise the
 // stale reference maximum is kept; the final division by the row sum makes it exact).
 // Query-side relocation: the first shared_kv_lens[b] keys are scored against queries

@@ -341,8 +341,7 @@ class ModelRunner:
         span (same first slot, same length); at most 32 (query, head-in-group) rows per request;
         no key-side relocation, which rotates a key by (its index - its slot) and so needs the
         logical order."""
-        want = getattr(self.config, "group_shared_span", None)
-        if want is False or len(seqs) < 2:
+        if not getattr(self.config, "group_shared_span", False) or len(seqs) < 2:
             return False
         if self._affix_relocation_enabled and not relocation_materialized and not use_query_relocation:
             return False
@@ -352,15 +351,7 @@ class ModelRunner:
         spans = {attention_read_runs(s)[1:] for s in seqs}
         if len(spans) != 1 or next(iter(spans))[0] <= 0:
             return False
-        if want is True:
-            return True
-        # measured on B200: the two-part kernel pays about 9 us per launch for publishing and
-        # folding the parts and runs more, shorter work items; it wins once the span is several
-        # times longer than what a request reads besides it (LLaDA-8B, 64 requests, 8192-token
-        # span: 1.59 ms against 1.90 ms), and loses at 800 shared against 560 other keys
-        span = next(iter(spans))[0]
-        private = max(len(s) - span + len(s.anchor_positions) for s in seqs)
-        return span >= 3 * private
+        return True
 
     def _use_query_side_affix_relocation(self, relocation_materialized: bool):
         return self._affix_relocation_enabled and not relocation_materialized and self.config.max_num_seqs != 1
