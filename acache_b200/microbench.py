@@ -170,6 +170,21 @@ def case_rope_store(n, nh, hkv, D):
     return fn, dict(bytes=n * D * 2 * (2 * nh + 2 * hkv + 2 * hkv + hkv))  # q,k rw; k,v cache w; v r
 
 
+def case_act_mul(n, ffn):
+    gate = torch.randn(n, ffn, device=DEV, dtype=torch.bfloat16)
+    up = torch.randn_like(gate)
+    fn = lambda: ops.act_mul(gate, up, "silu")
+    return fn, dict(bytes=3 * n * ffn * 2)
+
+
+def case_add_rmsnorm(n, hidden):
+    x = torch.randn(n, hidden, device=DEV, dtype=torch.bfloat16)
+    d = torch.randn_like(x)
+    w = torch.ones(hidden, device=DEV, dtype=torch.bfloat16)
+    fn = lambda: ops.add_rmsnorm(x, d, w, 1e-5)
+    return fn, dict(bytes=4 * n * hidden * 2)
+
+
 def case_qkv(n, hidden, nh, hkv, D, fused):
     import torch.nn.functional as F
 
@@ -219,6 +234,8 @@ CASES = {
     "qkv_cublas_refresh_llada": (lambda: case_qkv(2304, 4096, 32, 32, 128, False), "tensor"),
     "qkv_fused_decode_dream": (lambda: case_qkv(1024, 3584, 28, 4, 128, True), "tensor"),
     "qkv_cublas_decode_dream": (lambda: case_qkv(1024, 3584, 28, 4, 128, False), "tensor"),
+    "act_mul_decode_llada": (lambda: case_act_mul(512, 12288), "hbm"),
+    "add_rmsnorm_decode_llada": (lambda: case_add_rmsnorm(512, 4096), "hbm"),
     "topk_cfg1": (lambda: case_topk(4, 512, 103), "latency"),
     "topk_llada_bs16": (lambda: case_topk(16, 800, 160), "latency"),
     "topk_long_bs64": (lambda: case_topk(64, 8192, 820), "latency"),
