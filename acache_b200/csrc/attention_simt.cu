@@ -417,7 +417,8 @@ int attention_simt_dispatch(const AttnArgs& a, int dtype, int rope_dtype) {
 int importance_tc_dispatch(const void* q, int64_t q_stride, const int32_t* q_rows, int n_q, int n_heads, int n_kv_heads,
                            int head_dim, int dtype, const void* affix_k, int64_t k_slot_stride, int affix_len,
                            int affix_shift, const void* rope_cos, const void* rope_sin, int64_t rope_stride,
-                           int rope_dtype, float scale, float* partial, int* n_partials, cudaStream_t st);
+                           int rope_dtype, float scale, float* partial, int* n_partials, float* ml, cudaStream_t st);
+int64_t importance_tc_ml_floats(int n_q_rows, int n_heads, int affix_len);
 
 // implemented in attention_tc.cu: returns ACACHE_EUNSUPPORTED when it declines the shape
 int attention_tc_dispatch(const AttnArgs& a, int dtype, int rope_dtype);
@@ -501,10 +502,16 @@ extern "C" int acache_paged_attention(const void* q, int64_t q_stride, void* out
   return attention_common(a, dtype, ACACHE_F32);
 }
 
+// per-CTA partial column sums: one row of affix_len floats per (32-row tile, head)
+static int64_t importance_partial_floats(int n_q_rows, int n_heads, int affix_len) {
+  const int64_t tiles = (n_q_rows + kBM - 1) / kBM;
+  return tiles * n_heads * (int64_t)affix_len;
+}
+
 extern "C" int64_t acache_anchor_importance_scratch_bytes(int n_q_rows, int n_heads, int affix_len) {
   if (n_q_rows <= 0 || n_heads <= 0 || affix_len <= 0) return 0;
-  const int64_t tiles = (n_q_rows + kBM - 1) / kBM;
-  return tiles * n_heads * (int64_t)affix_len * (int64_t)sizeof(float);
+  return (importance_partial_floats(n_q_rows, n_heads, affix_len) +
+          importance_tc_ml_floats(n_q_rows, n_heads, affix_len)) * (int64_t)sizeof(float);
 }
 
 template <typename T, typename TR>
@@ -550,7 +557,8 @@ extern "C" int acache_anchor_importance(const void* q, int64_t q_stride, const i
     int n_partials = 0;
     const int rc = importance_tc_dispatch(q, q_stride, q_rows, n_q_rows, n_heads, n_kv_heads, head_dim, dtype, affix_k,
                                           k_slot_stride, affix_len, affix_shift, rope_cos, rope_sin, rope_row_stride,
-                                          rope_dtype, scale, (float*)scratch, &n_partials, st);
+                                          rope_dtype, scale, (float*)scratch, &n_partials,
+                                          (float*)scratch + importance_partial_floats(n_q_rows, n_heads, affix_len), st);
     if (rc == ACACHE_OK) {
       importance_reduce_kernel<<<(affix_len + 255) / 256, 256, 0, st>>>((const float*)scratch, n_partials, affix_len,
                                                                         importance);

@@ -11,14 +11,23 @@
 //           the 64 columns of the tile; the CTA writes its column sums to its own row of
 //           `partial`, which importance_reduce_kernel adds in a fixed order (deterministic).
 // Keys are staged through registers when they need the rotation, with cp.async otherwise.
+// Long affixes are cut into chunks of kChunkTiles tiles that separate CTAs walk (grid.z): a first
+// launch runs pass 1 per chunk and leaves every row's (maximum, denominator) per chunk in scratch,
+// a second launch folds them per row and runs pass 2 per chunk; each chunk writes its own columns
+// of the CTA's partial row, so the reduction that follows is unchanged.
 // Every mbarrier wait is bounded.
 #include "common.cuh"
 #include "tcgen05.cuh"
 
 namespace acache {
+int importance_tc_chunks(int affix_len);
+
 namespace tc {
 
 constexpr int IBM = 128, IBN = 64, INT = 128;
+constexpr int kChunkTiles = 16;        // 1024 keys per chunk
+constexpr int kChunkFrom = 2048;       // affixes longer than this are chunked
+enum { kBothPasses = 0, kPassOne = 1, kPassTwo = 2 };
 constexpr int kPsLd = 129;  // padded leading dimension of the transposed P tile
 
 template <typename T, typename TR, typename TC, int D>
@@ -26,7 +35,7 @@ __global__ void __launch_bounds__(INT) importance_tc_kernel(
     const T* __restrict__ q, int64_t q_stride, const int32_t* __restrict__ q_rows, int n_q, int n_heads, int n_kv_heads,
     const T* __restrict__ affix_k, int64_t k_slot_stride, int affix_len, int affix_shift,
     const TR* __restrict__ rope_cos, const TR* __restrict__ rope_sin, int64_t rope_stride, float scale_log2,
-    float* __restrict__ partial, int32_t* err_flag) {
+    float* __restrict__ partial, int32_t* err_flag, int mode, float* __restrict__ ml) {
   constexpr int CH = D * (int)sizeof(T) / 16;
   constexpr int Q_BYTES = IBM * D * (int)sizeof(T);
   constexpr int K_BYTES = IBN * D * (int)sizeof(T);
@@ -45,17 +54,22 @@ __global__ void __launch_bounds__(INT) importance_tc_kernel(
   const int m0 = blockIdx.x * IBM;
   const int vrows = n_q * g;
   float* my_partial = partial + ((int64_t)blockIdx.y * gridDim.x + blockIdx.x) * affix_len;
-  if (m0 >= vrows) {  // cannot happen with the launch grid; keep the reduce kernel's input defined
-    for (int a = tid; a < affix_len; a += INT) my_partial[a] = 0.f;
-    return;
-  }
-  if ((smem_u32(smem_raw) & 1023u) != 0) {
-    if (tid == 0 && err_flag) atomicExch(err_flag, 6);
-    for (int a = tid; a < affix_len; a += INT) my_partial[a] = 0.f;
+  if (m0 >= vrows || (smem_u32(smem_raw) & 1023u) != 0) {
+    // the first cannot happen with the launch grid, the second would be a launch error: keep the
+    // reduce kernel's input defined (every chunk writes the whole row: same zeros) and report
+    if (m0 < vrows && tid == 0 && err_flag) atomicExch(err_flag, 6);
+    if (mode != kPassOne)
+      for (int a = tid; a < affix_len; a += INT) my_partial[a] = 0.f;
     return;
   }
   const int rows_live = min(IBM, vrows - m0);
-  const int n_tiles = (affix_len + IBN - 1) / IBN;
+  // this CTA's tiles of the affix: all of them, or chunk blockIdx.z
+  const int tiles_all = (affix_len + IBN - 1) / IBN;
+  const int t0 = mode == kBothPasses ? 0 : (int)blockIdx.z * kChunkTiles;
+  const int n_tiles = mode == kBothPasses ? tiles_all : min(kChunkTiles, tiles_all - t0);
+  const int n_chunks = (int)gridDim.z;
+  // (maximum, denominator) of row `tid` for chunk c of this (KV head, row tile)
+  float* my_ml = ml + (((int64_t)blockIdx.y * gridDim.x + blockIdx.x) * n_chunks) * (IBM * 2);
 
   const uint32_t bar_s = smem_u32(&bars[0]);
   if (tid == 0) {
@@ -81,10 +95,13 @@ __global__ void __launch_bounds__(INT) importance_tc_kernel(
     const int head = kvh * g + (ok ? v % g : 0);
     cp_async16(smem_u32(sQ) + swz<D>(IBM, r, c), q + (int64_t)qrow * q_stride + (int64_t)head * D + c * (16 / sizeof(T)), ok);
   }
+  // iterations 0..n_tiles-1 are pass 1, n_tiles..2 n_tiles-1 pass 2
+  const int it_begin = mode == kPassTwo ? n_tiles : 0;
+  const int it_end = mode == kPassOne ? n_tiles : 2 * n_tiles;
   auto load_k = [&](int it) {
-    const int tile = it % n_tiles;
+    const int tile = t0 + it % n_tiles;
     const int j0 = tile * IBN;
-    uint8_t* kb = sK + (it & 1) * K_BYTES;
+    uint8_t* kb = sK + ((it - it_begin) & 1) * K_BYTES;
     for (int id = tid; id < IBN * CH; id += INT) {
       const int r = id / CH, c = id % CH;
       const int j = j0 + r;
@@ -119,25 +136,32 @@ __global__ void __launch_bounds__(INT) importance_tc_kernel(
   const uint32_t idesc = make_idesc(Fmt<T>::id, 0, IBN, IBM);
   const bool warp_live = warp * 32 < rows_live;
   const bool row_ok = tid < rows_live;
-  load_k(0);
+  load_k(it_begin);
   cp_async_commit();
 
   float m_run = -INFINITY, l_run = 0.f, inv_l = 0.f;
+  if (mode == kPassTwo) {   // fold what pass 1 left per chunk, in chunk order
+    for (int c = 0; c < n_chunks; ++c) m_run = fmaxf(m_run, my_ml[(c * IBM + tid) * 2]);
+    for (int c = 0; c < n_chunks; ++c) {
+      const float mc = my_ml[(c * IBM + tid) * 2];
+      l_run += mc == -INFINITY ? 0.f : my_ml[(c * IBM + tid) * 2 + 1] * ex2(mc - m_run);
+    }
+    inv_l = l_run > 0.f ? 1.0f / l_run : 0.f;
+  }
   bool failed = false;
   uint32_t s[64];
-  const int total = 2 * n_tiles;
-  for (int it = 0; it < total; ++it) {
-    if (it + 1 < total) load_k(it + 1);
+  for (int it = it_begin; it < it_end; ++it) {
+    if (it + 1 < it_end) load_k(it + 1);
     cp_async_commit();
     cp_async_wait<1>();
     fence_proxy_async();
     tc_fence_before();
     __syncthreads();   // also: every thread is done with the previous tile's sP and TMEM scores
     tc_fence_after();
-    const int tile = it % n_tiles;
+    const int tile = t0 + it % n_tiles;
     const int j0 = tile * IBN;
     const int valid = min(IBN, affix_len - j0);
-    const uint32_t kb = smem_u32(sK) + (it & 1) * K_BYTES;
+    const uint32_t kb = smem_u32(sK) + ((it - it_begin) & 1) * K_BYTES;
     if (tid == 0) {
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks) {
@@ -147,9 +171,9 @@ __global__ void __launch_bounds__(INT) importance_tc_kernel(
       }
       mma_commit(bar_s);
     }
-    const bool ok = mbar_wait(bar_s, (uint32_t)(it & 1));
+    const bool ok = mbar_wait(bar_s, (uint32_t)((it - it_begin) & 1));
     tc_fence_after();
-    if (it == n_tiles) inv_l = l_run > 0.f ? 1.0f / l_run : 0.f;   // pass 1 is complete for this row
+    if (mode == kBothPasses && it == n_tiles) inv_l = l_run > 0.f ? 1.0f / l_run : 0.f;   // pass 1 is complete for this row
     if (warp_live) {
       tmem_ld32(t_lane, s);
       tmem_ld32(t_lane + 32, s + 32);
@@ -190,9 +214,14 @@ __global__ void __launch_bounds__(INT) importance_tc_kernel(
       if (h == 0 && c < valid) my_partial[j0 + c] = acc + half_sum[c];
     }
   }
+  if (mode == kPassOne) {
+    my_ml[((int)blockIdx.z * IBM + tid) * 2] = failed ? -INFINITY : m_run;
+    my_ml[((int)blockIdx.z * IBM + tid) * 2 + 1] = failed ? 0.f : l_run;
+  }
   if (failed) {
     if (tid == 0 && err_flag) atomicExch(err_flag, 5);
-    for (int a = tid; a < affix_len; a += INT) my_partial[a] = 0.f;
+    if (mode != kPassOne)   // this CTA's columns of the partial row
+      for (int a = t0 * IBN + tid; a < min(affix_len, (t0 + n_tiles) * IBN); a += INT) my_partial[a] = 0.f;
   }
   cp_async_wait<0>();
   tc_fence_before();
@@ -210,16 +239,26 @@ template <typename T, typename TR, int D>
 static int launch_importance_tc(const void* q, int64_t q_stride, const int32_t* q_rows, int n_q, int n_heads,
                                 int n_kv_heads, const void* affix_k, int64_t k_slot_stride, int affix_len,
                                 int affix_shift, const void* rope_cos, const void* rope_sin, int64_t rope_stride,
-                                float scale, float* partial, int* n_partials, int32_t* err_flag, cudaStream_t st) {
+                                float scale, float* partial, int* n_partials, float* ml, int32_t* err_flag,
+                                cudaStream_t st) {
   using TC = typename PromoteI<T, TR>::type;
   constexpr size_t smem = IBM * D * sizeof(T) + 2 * IBN * D * sizeof(T) + IBN * kPsLd * sizeof(float) + 64;
   auto kern = importance_tc_kernel<T, TR, TC, D>;
   ACACHE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int g = n_heads / n_kv_heads;
   dim3 grid((n_q * g + IBM - 1) / IBM, n_kv_heads);
-  kern<<<grid, INT, smem, st>>>((const T*)q, q_stride, q_rows, n_q, n_heads, n_kv_heads, (const T*)affix_k, k_slot_stride,
-                                affix_len, affix_shift, (const TR*)rope_cos, (const TR*)rope_sin, rope_stride,
-                                scale * 1.4426950408889634f, partial, err_flag);
+  const int chunks = importance_tc_chunks(affix_len);
+  if (chunks <= 1 || ml == nullptr) {
+    kern<<<grid, INT, smem, st>>>((const T*)q, q_stride, q_rows, n_q, n_heads, n_kv_heads, (const T*)affix_k,
+                                  k_slot_stride, affix_len, affix_shift, (const TR*)rope_cos, (const TR*)rope_sin,
+                                  rope_stride, scale * 1.4426950408889634f, partial, err_flag, kBothPasses, partial);
+  } else {
+    dim3 grid3(grid.x, grid.y, chunks);
+    for (int mode = kPassOne; mode <= kPassTwo; ++mode)
+      kern<<<grid3, INT, smem, st>>>((const T*)q, q_stride, q_rows, n_q, n_heads, n_kv_heads, (const T*)affix_k,
+                                     k_slot_stride, affix_len, affix_shift, (const TR*)rope_cos, (const TR*)rope_sin,
+                                     rope_stride, scale * 1.4426950408889634f, partial, err_flag, mode, ml);
+  }
   ACACHE_LAUNCH_CHECK();
   *n_partials = (int)(grid.x * grid.y);
   return ACACHE_OK;
@@ -227,23 +266,37 @@ static int launch_importance_tc(const void* q, int64_t q_stride, const int32_t* 
 
 }  // namespace tc
 
+// chunks a long affix is cut into (1 = walked by one CTA per row tile and KV head)
+int importance_tc_chunks(int affix_len) {
+  if (affix_len <= tc::kChunkFrom) return 1;
+  const int tiles = (affix_len + tc::IBN - 1) / tc::IBN;
+  return (tiles + tc::kChunkTiles - 1) / tc::kChunkTiles;
+}
+// floats of scratch behind the partial rows for the per-chunk (maximum, denominator) pairs
+int64_t importance_tc_ml_floats(int n_q_rows, int n_heads, int affix_len) {
+  const int chunks = importance_tc_chunks(affix_len);
+  if (chunks <= 1) return 0;
+  // row tiles x KV heads <= (n_q_rows / 128 + 1) x n_heads (a KV head's rows are its group's)
+  return ((int64_t)n_q_rows / tc::IBM + 1) * n_heads * tc::IBM * 2 * (int64_t)chunks;
+}
+
 // Returns ACACHE_EUNSUPPORTED for what the tensor-core kernel does not cover (fp32, head sizes
 // other than 64/128); the caller then uses the general kernel.  On success *n_partials rows of
 // `partial` ([n_partials][affix_len]) hold per-CTA column sums.
 int importance_tc_dispatch(const void* q, int64_t q_stride, const int32_t* q_rows, int n_q, int n_heads, int n_kv_heads,
                            int head_dim, int dtype, const void* affix_k, int64_t k_slot_stride, int affix_len,
                            int affix_shift, const void* rope_cos, const void* rope_sin, int64_t rope_stride,
-                           int rope_dtype, float scale, float* partial, int* n_partials, cudaStream_t st) {
+                           int rope_dtype, float scale, float* partial, int* n_partials, float* ml, cudaStream_t st) {
   if (dtype == ACACHE_F32 || (head_dim != 64 && head_dim != 128)) return ACACHE_EUNSUPPORTED;
   if (!aligned16(q) || !aligned16(affix_k) || q_stride % 8 != 0 || k_slot_stride % 8 != 0) return ACACHE_EUNSUPPORTED;
 #define IMP_TC(T, TR)                                                                                                  \
   return head_dim == 128                                                                                               \
              ? tc::launch_importance_tc<T, TR, 128>(q, q_stride, q_rows, n_q, n_heads, n_kv_heads, affix_k,            \
                                                     k_slot_stride, affix_len, affix_shift, rope_cos, rope_sin,         \
-                                                    rope_stride, scale, partial, n_partials, nullptr, st)              \
+                                                    rope_stride, scale, partial, n_partials, ml, nullptr, st)              \
              : tc::launch_importance_tc<T, TR, 64>(q, q_stride, q_rows, n_q, n_heads, n_kv_heads, affix_k,             \
                                                    k_slot_stride, affix_len, affix_shift, rope_cos, rope_sin,          \
-                                                   rope_stride, scale, partial, n_partials, nullptr, st)
+                                                   rope_stride, scale, partial, n_partials, ml, nullptr, st)
   if (dtype == ACACHE_BF16) {
     if (rope_dtype == ACACHE_F32) { IMP_TC(__nv_bfloat16, float); }
     if (rope_dtype == ACACHE_BF16) { IMP_TC(__nv_bfloat16, __nv_bfloat16); }

@@ -226,7 +226,10 @@ def test_topk_golden_and_ties():
 # ----------------------------------------------------------------------------- importance
 @pytest.mark.parametrize("nh,hkv,D,A,nq,shift,dt", [
     (4, 4, 64, 37, 9, 0, torch.bfloat16), (8, 2, 128, 300, 70, 13, torch.bfloat16),
-    (4, 2, 32, 64, 5, 3, torch.float32), (32, 32, 128, 800, 256, 0, torch.bfloat16)])
+    (4, 2, 32, 64, 5, 3, torch.float32), (32, 32, 128, 800, 256, 0, torch.bfloat16),
+    # long affixes: cut into chunks walked by separate CTAs, two launches
+    (32, 32, 128, 5000, 8, 40, torch.bfloat16), (8, 2, 128, 2500, 200, 0, torch.bfloat16),
+    (4, 4, 64, 2049, 3, 5, torch.float16)])
 def test_anchor_importance_vs_oracle(nh, hkv, D, A, nq, shift, dt):
     from oracle.importance import layer_importance, relocate_keys
 
