@@ -1,8 +1,7 @@
 """Generates the golden fixtures in this directory from the reference itself.
 
-Runs only where a checkout of the reference is available (argument 1 or
-$ACACHE_REFERENCE; default /root/reference).  It imports the reference's own
-Python, read-only, on CPU:
+Runs only where a checkout of the reference is available (its root is argument 1
+or $ACACHE_REFERENCE).  It imports the reference's own Python, read-only, on CPU:
 
 * layout.json       - reference Sequence / BlockManager / _attention_read_layout
                       on seeded random prefix / infix / suffix requests
@@ -18,7 +17,7 @@ Python, read-only, on CPU:
                       tiny random LLaDA in fp32: importance scores, anchors, first
                       refresh logits, final tokens, nfe for prefix / infix / suffix
 
-Usage: TORCHDYNAMO_DISABLE=1 python tests/golden/make_golden.py [reference_root]
+Usage: TORCHDYNAMO_DISABLE=1 python tests/golden/make_golden.py <reference_root>
 """
 import importlib
 import importlib.util
@@ -36,7 +35,10 @@ import numpy as np
 import torch
 
 HERE = Path(__file__).resolve().parent
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("ACACHE_REFERENCE", "/root/reference"))
+_ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("ACACHE_REFERENCE")
+if not _ref_root:
+    sys.exit("usage: make_golden.py <reference_root>  (or set ACACHE_REFERENCE)")
+REF = Path(_ref_root)
 sys.path.insert(0, str(REF / "nano-vdllm"))
 sys.path.insert(0, str(HERE.parents[1]))
 
