@@ -105,8 +105,11 @@ def stream_ptr() -> int:
 # kernels launched through this binding since import (the benchmark reads the difference)
 LAUNCHES = 0
 
-# optional per-operator device timing: name -> [list of (start_event, end_event), work units]
+# optional per-operator device timing: name -> {"events": [(start, end), ...] of eager calls,
+# "ms"/"n": time and count harvested from graph replays, "work": work units of all of them}
 _TIMERS: dict | None = None
+# while a CUDA graph is being captured: the (name, start, end) event pairs recorded inside it
+_GRAPH_EVENTS: list | None = None
 
 
 def enable_kernel_timers(on: bool = True):
@@ -116,14 +119,47 @@ def enable_kernel_timers(on: bool = True):
     _TIMERS = {} if on else None
 
 
+def kernel_timers_enabled() -> bool:
+    return _TIMERS is not None
+
+
+def _timer_record(name: str) -> dict:
+    return _TIMERS.setdefault(name, {"events": [], "work": 0.0, "ms": 0.0, "n": 0})
+
+
 def kernel_timers() -> dict:
     """name -> (total_ms, launches, work) resolved from the recorded events."""
     out = {}
     if _TIMERS:
         torch.cuda.synchronize()
         for name, rec in _TIMERS.items():
-            out[name] = (sum(a.elapsed_time(b) for a, b in rec["events"]), len(rec["events"]), rec["work"])
+            out[name] = (sum(a.elapsed_time(b) for a, b in rec["events"]) + rec["ms"], len(rec["events"]) + rec["n"],
+                         rec["work"])
     return out
+
+
+def begin_graph_capture() -> list:
+    """Timed operators called until ``end_graph_capture`` record EXTERNAL events (event-record
+    nodes of the graph being captured) and list them in the returned list."""
+    global _GRAPH_EVENTS
+    _GRAPH_EVENTS = []
+    return _GRAPH_EVENTS
+
+
+def end_graph_capture():
+    global _GRAPH_EVENTS
+    _GRAPH_EVENTS = None
+
+
+def harvest_graph_timers(events: list, work: float):
+    """Adds the times between the event pairs of a graph whose last replay HAS COMPLETED."""
+    if _TIMERS is None:
+        return
+    for name, a, b in events:
+        rec = _timer_record(name)
+        rec["ms"] += a.elapsed_time(b)
+        rec["n"] += 1
+        rec["work"] += work
 
 
 class timed:
@@ -136,17 +172,20 @@ class timed:
 
     def __enter__(self):
         if _TIMERS is not None:
-            self.start = torch.cuda.Event(enable_timing=True)
+            self.start = torch.cuda.Event(enable_timing=True, external=_GRAPH_EVENTS is not None)
             self.start.record()
         return self
 
     def __exit__(self, *exc):
         if self.start is not None:
-            end = torch.cuda.Event(enable_timing=True)
+            end = torch.cuda.Event(enable_timing=True, external=_GRAPH_EVENTS is not None)
             end.record()
-            rec = _TIMERS.setdefault(self.name, {"events": [], "work": 0.0})
-            rec["events"].append((self.start, end))
-            rec["work"] += self.work
+            if _GRAPH_EVENTS is not None:
+                _GRAPH_EVENTS.append((self.name, self.start, end))
+            else:
+                rec = _timer_record(self.name)
+                rec["events"].append((self.start, end))
+                rec["work"] += self.work
         return False
 
 

@@ -34,6 +34,10 @@ class Config:
     # --- additions of this implementation (all default to reference behaviour) ---
     # dtype of the paged KV cache; the reference hard-codes bfloat16
     kv_cache_dtype: str = "bfloat16"
+    # replay the block-decode forward (all layers and the output head) from a CUDA graph with the
+    # step metadata in fixed buffers; the same kernels with the same arguments, without the host
+    # cost of about 330 launches per step
+    use_cuda_graphs: bool = True
     # block decode: hand attention every request's shared span as the same run of slots (with -1
     # where an anchor's private copy replaces the shared row) and stage it once per four requests
     # (same result as the logical order up to the order of the floating-point sums).  Off by

@@ -113,6 +113,111 @@ class _Staging:
         return out
 
 
+class _StaticStaging:
+    """Same interface as ``_Staging`` but with a fixed layout: every named array has a fixed
+    capacity and always lands at the same device address, so kernels captured in a CUDA graph
+    keep reading the step metadata from where they were captured.  One pinned host buffer, one
+    device buffer, one copy per ``ship``."""
+
+    def __init__(self, device, capacities: dict, counter: _Staging | None = None):
+        self.device = device
+        self.counter = counter
+        self.offsets, total = {}, 0
+        for name, (dtype, n) in sorted(capacities.items(), key=lambda kv: -np.dtype(kv[1][0]).itemsize):
+            total = -(-total // 16) * 16
+            self.offsets[name] = (total, np.dtype(dtype), int(n))
+            total += np.dtype(dtype).itemsize * int(n)
+        self.nbytes = max(total, 16)
+        self.host = torch.zeros(self.nbytes, dtype=torch.uint8, pin_memory=device.type == "cuda")
+        self.dev = torch.zeros(self.nbytes, dtype=torch.uint8, device=device)
+        self.copied = None   # event after the last copy: the pinned buffer is rewritten only after it
+
+    def fits(self, **arrays) -> bool:
+        return set(arrays) == set(self.offsets) and all(
+            np.dtype(a.dtype) == self.offsets[k][1] and a.size <= self.offsets[k][2] for k, a in arrays.items())
+
+    def ship(self, **arrays):
+        assert self.fits(**arrays), "step metadata does not fit the captured layout"
+        if self.copied is not None:
+            self.copied.synchronize()
+        hv = self.host.numpy()
+        out, moved = {}, 0
+        for k, a in arrays.items():
+            off, dt, _ = self.offsets[k]
+            a = np.ascontiguousarray(a)
+            hv[off: off + a.nbytes] = a.view(np.uint8).reshape(-1)
+            moved += a.nbytes
+            tdt = torch.int64 if dt == np.int64 else torch.int32
+            out[k] = self.dev[off: off + a.nbytes].view(tdt).view(a.shape)
+        self.dev.copy_(self.host, non_blocking=True)
+        if self.device.type == "cuda":
+            self.copied = torch.cuda.Event()
+            self.copied.record()
+        if self.counter is not None:
+            self.counter.h2d_bytes += moved
+        return out
+
+
+class _DecodeGraph:
+    """One block-decode forward (all layers and the output head) of ``n_rows`` requests captured
+    in a CUDA graph.  Inputs live at fixed addresses: the block's tokens, and the step metadata
+    in a ``_StaticStaging``; the logits come back in a tensor of the graph's memory pool.  The
+    graph is replayed for every decode step with this many rows, whatever the requests are."""
+
+    def __init__(self, runner, n_rows: int, names_and_dtypes: dict, read_capacity: int, max_pos: int):
+        T = runner.config.block_length
+        caps = {}
+        for name, dtype in names_and_dtypes.items():
+            n = {"positions": n_rows * T, "cu_q": n_rows + 1, "cu_k": n_rows + 1, "slots": n_rows * T,
+                 "read": read_capacity}.get(name, n_rows)
+            caps[name] = (dtype, n)
+        self.staging = _StaticStaging(runner.device, caps, runner._staging)
+        self.tokens = torch.zeros(n_rows, T, dtype=torch.int64, device=runner.device)
+        self.max_pos = max_pos
+        self.graph = None
+        self.logits = None
+        self.events: list = []
+        self.with_timers = False
+        self.launches = 0
+        self.pending_work = None   # work units of a replay whose event times were not read yet
+        self.stamp = None
+
+    def run(self, runner, block_tokens, positions):
+        self.tokens.copy_(block_tokens)
+        timers = _lib.kernel_timers_enabled()
+        for rope in runner._rope_caches:      # the table the capture will see (and later eager forwards keep)
+            rope.get(self.max_pos, runner.device)
+        if self.graph is None or (timers and not self.with_timers) or self.stamp != runner._graph_stamp():
+            self._capture(runner, positions, timers)
+        runner.harvest_graph_timers()
+        self.graph.replay()
+        _lib.LAUNCHES += self.launches
+        if self.events:
+            self.pending_work = aa.ATTENTION_WORK
+            runner._graph_with_pending_timers = self
+        return self.logits
+
+    def _capture(self, runner, positions, timers: bool):
+        def forward():
+            out = runner._forward_model(self.tokens, positions, max_pos=self.max_pos).logits
+            return runner._dream_decode_logits(out)
+
+        forward()   # eager once: tables, workspaces and library handles exist before the capture
+        torch.cuda.synchronize()
+        self.graph, self.logits = None, None
+        graph = torch.cuda.CUDAGraph()
+        self.events = _lib.begin_graph_capture()
+        launches0 = _lib.LAUNCHES
+        try:
+            with torch.cuda.graph(graph):
+                self.logits = forward()
+        finally:
+            _lib.end_graph_capture()
+        self.launches = _lib.LAUNCHES - launches0
+        _lib.LAUNCHES = launches0   # nothing ran during the capture
+        self.graph, self.with_timers, self.stamp = graph, timers, runner._graph_stamp()
+
+
 class _Probe:
     """State of one anchor-selection probe, read by the attention layers."""
 
@@ -142,6 +247,11 @@ class ModelRunner:
         self._staging = _Staging(self.device)
         self.d2h_bytes = 0
         self._attn_layers = [m for m in self.model.modules() if hasattr(m, "k_cache") and hasattr(m, "v_cache")]
+        # captured block-decode forwards, by (rows, layout of the step metadata)
+        self._decode_graphs: dict = {}
+        self._decode_graph = None
+        self._graph_with_pending_timers = None
+        self._rope_caches = [m.rope for m in self.model.modules() if hasattr(m, "rope") and hasattr(m.rope, "get")]
         self.allocate_kv_cache()
 
     # ------------------------------------------------------------------ model access
@@ -256,6 +366,8 @@ class ModelRunner:
         self._relocated_affix_slot_offset = None
 
     def _release_kv_cache(self):
+        self._decode_graphs.clear()   # they read the cache that goes away (and hold memory of their own)
+        self._decode_graph = self._graph_with_pending_timers = None
         for m in self._attn_layers:
             m.k_cache = m.v_cache = torch.tensor([])
         self.kv_cache = None
@@ -828,10 +940,12 @@ class ModelRunner:
                     dev["slots"], None, True, dev["read"], dev.get("shared_lens"), dev.get("shifts"))
         return dev["input_ids"], dev["positions"], dev["bqs"]
 
-    def prepare_decoding_acache(self, seqs, active_indices=None):
+    def prepare_decoding_acache(self, seqs, active_indices=None, graphs=None):
         """Block-decode metadata: ``[B, block_length]`` queries at the working block's
         positions, K/V written in place at the block's read slots
-        (reference: model_runner.py:1397-1471)."""
+        (reference: model_runner.py:1397-1471).  ``graphs``: a dict of captured decode forwards;
+        the metadata then goes to the fixed buffers of the matching one (made on demand), which
+        is left in ``self._decode_graph``."""
         ps = self._pick(seqs, active_indices)
         T = self.config.block_length
         self._configure_affix_relocation(ps)
@@ -857,12 +971,43 @@ class ModelRunner:
             arrays["shared_lens"] = np.asarray(shared_lens, dtype=np.int32)
         if not materialized:
             arrays["shifts"] = np.asarray(shifts, dtype=np.int32)
-        dev = self._staging.ship(**arrays)
+        staging = self._staging
+        self._decode_graph = None
+        if graphs is not None:
+            key = (len(ps), grouped, tuple(sorted(arrays)))
+            graph = graphs.get(key)
+            if graph is None or not graph.staging.fits(**arrays):
+                # read-map capacity and RoPE table length: powers of two with head-room
+                cap = 1 << int(2 * arrays["read"].size - 1).bit_length()
+                max_pos = 1 << int(2 * int(k_lens.max()) - 1).bit_length()
+                graph = graphs[key] = _DecodeGraph(self, len(ps), {k: a.dtype for k, a in arrays.items()}, cap, max_pos)
+            if int(k_lens.max()) <= graph.max_pos:
+                staging, self._decode_graph = graph.staging, graph
+        dev = staging.ship(**arrays)
         self._note_attention_work("decode", [T] * len(ps), k_lens)
         set_context(False, dev["cu_q"], dev["cu_k"], dev["kv_seqlens"], T, int(k_lens.max()), dev["slots"], None, True,
                     dev["read"], dev.get("shared_lens"), dev.get("shifts"))
         get_context().group_shared_span = grouped
         return dev["positions"]
+
+    def _graph_stamp(self):
+        """What a captured forward has baked in besides its own buffers: the cache, the RoPE
+        tables and the shared-span length.  A graph is captured again when any of them changed."""
+        a0 = self._attn_layers[0]
+        ptr_of = lambda t: t.data_ptr() if t is not None and t.numel() else 0
+        return (ptr_of(self.kv_cache), tuple(ptr_of(r.cos) for r in self._rope_caches), a0.shared_prefix_len,
+                ptr_of(a0.relocation_rope_cos), ptr_of(a0.relocation_rope_sin))
+
+    def harvest_graph_timers(self):
+        """Reads the event times of the last graph replay (it must have completed: call after a
+        host synchronisation or, as the next replay does, in stream order before re-recording)."""
+        graph = self._graph_with_pending_timers
+        if graph is not None and graph.pending_work is not None:
+            if _lib.kernel_timers_enabled():
+                torch.cuda.current_stream().synchronize()
+                _lib.harvest_graph_timers(graph.events, graph.pending_work)
+            graph.pending_work = None
+        self._graph_with_pending_timers = None
 
     # ------------------------------------------------------------------ sampling
     def get_transfer_index(self, logits, temperature, remasking, mask_index, x, threshold=0.9):
@@ -1033,6 +1178,8 @@ class ModelRunner:
             total_nfe += len(batched)
             decode_key = None
             decode_positions = None
+            decode_graph = None
+            use_graphs = bool(getattr(cfg, "use_cuda_graphs", True)) and dev.type == "cuda"
             # Every decode step commits at least one position per row, so a block needs at
             # most block_length steps unless the model keeps predicting the mask token itself
             # (the reference would then spin forever); stop with an error instead.
@@ -1106,14 +1253,19 @@ class ModelRunner:
                     t0 = self._start_timing()
                     decode_key = key
                     sel = [batched[r] for r in active]
-                    decode_positions = self.prepare_decoding_acache(sel) if reuse else self.prepare_decoding(sel)
+                    decode_positions = (self.prepare_decoding_acache(sel, graphs=self._decode_graphs if use_graphs else None)
+                                        if reuse else self.prepare_decoding(sel))
+                    decode_graph = self._decode_graph if reuse else None
                     decode_rows = torch.as_tensor(active, dtype=torch.int64, device=dev)
                     decode_max_pos = max(len(s) for s in sel)
                     self._finish_timing(timing, "decode_prepare", t0)
                 t0 = self._start_timing()
                 block_tokens = working.index_select(0, decode_rows) if len(active) != len(batched) else working
-                logits = self._forward_model(block_tokens, decode_positions, max_pos=decode_max_pos).logits
-                logits = self._dream_decode_logits(logits)
+                if decode_graph is not None:
+                    logits = decode_graph.run(self, block_tokens, decode_positions)
+                else:
+                    logits = self._forward_model(block_tokens, decode_positions, max_pos=decode_max_pos).logits
+                    logits = self._dream_decode_logits(logits)
                 self._finish_timing(timing, "decode_forward", t0)
                 self._add_timing_count(timing, "decode_forward_calls", 1)
                 self._add_timing_count(timing, "decode_forward_nfe", len(active))
@@ -1129,4 +1281,5 @@ class ModelRunner:
                 timing["total_nfe"] = int(total_nfe)
             self._active_timing = prev_timing
         _lib.check_device_errors(dev)
+        self.harvest_graph_timers()
         return outputs, total_nfe

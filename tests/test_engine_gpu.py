@@ -225,6 +225,52 @@ def test_engine_bf16_tensor_core_path_agrees_with_fp32_oracle(kind, nh, hkv, aff
     assert again == outs and anchors_again == anchors     # deterministic, whichever part arrives second
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_graph_replayed_decode_equals_eager_decode(dtype):
+    """The block-decode forward replayed from a CUDA graph (step metadata in fixed buffers, one
+    graph per number of active rows, reused across blocks and across calls) gives exactly the
+    tokens of the eager forward; batch composition changes while requests retire."""
+    from acache_b200 import _lib
+    from acache_b200.model_runner import ModelRunner
+    from acache_b200.sequence import Sequence
+    from oracle.models import ArchSpec, random_state_dict
+
+    rng = random.Random(29)
+    arch = ArchSpec("llada", n_layers=2, d_model=256, n_heads=2, n_kv_heads=2, ffn=192, vocab=180, rope_theta=10000.0,
+                    rms_eps=1e-5, act="silu", mask_id=179)
+    weights = random_state_dict(arch, seed=31, std=0.5)
+    A, T = 40, 4
+    affix = [rng.randint(1, 170) for _ in range(A)]
+    hf_cfg, model = _llada(arch, weights, dtype)
+
+    def run(graphs, runner=None):
+        outs = []
+        for G in (8, 12):   # two calls on one runner: graphs of the first call are reused by the second
+            reqs = _random_requests(random.Random(G), arch, 5, A, G, ["prefix", "infix", "suffix"], affix)
+            cfg = _serve_config(hf_cfg, arch, "llada", dtype, threshold=0.7, anchor_ratio=0.25, max_num_seqs=3,
+                                num_kvcache_blocks=48, cache_block_size=16, block_length=T, gen_length=G,
+                                use_cuda_graphs=graphs)
+            runner = runner or ModelRunner(model, cfg)
+            runner.config.gen_length = G
+            seqs = [Sequence(r["prompt"], block_length=T, gen_length=G, cache_block_size=16, mask_id=arch.mask_id,
+                             prompt_affix_start=r["affix_start"], prompt_affix_end=r["affix_end"],
+                             generation_start=r["generation_start"]) for r in reqs]
+            outs.append(runner.generate_with_acache(seqs))
+        return outs, runner
+
+    eager, _ = run(False)
+    _lib.enable_kernel_timers(True)     # timed operators inside the graph record external events
+    try:
+        replayed, runner = run(True)
+        timers = _lib.kernel_timers()
+    finally:
+        _lib.enable_kernel_timers(False)
+    assert replayed == eager
+    assert runner._decode_graphs and all(g.graph is not None for g in runner._decode_graphs.values())
+    assert timers["attention_decode"][1] > 0 and timers["attention_decode"][0] > 0.0
+    _lib.check_device_errors()
+
+
 def test_reuse_with_every_affix_token_an_anchor_equals_no_reuse_baseline(hf_llada):
     """reference: nano-vdllm/tests/test_model_runner_acache.py:597-687 (ratio 1.0 recomputes
     the whole affix, so the logits equal the full-recompute baseline)."""
