@@ -33,6 +33,7 @@ from .model import acache_attention as aa
 from .model.acache_attention import materialize_relocated_affix
 from .model.modeling_common import build_rope_table
 from .sequence import Sequence
+from .dkv import DkvMixin
 from .utils import add_gumbel_noise, get_context, reset_context, set_context
 
 _TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32}
@@ -224,7 +225,7 @@ class _Probe:
     __slots__ = ("q_rows", "affix_len", "affix_shift", "importance", "rope_cos", "rope_sin")
 
 
-class ModelRunner:
+class ModelRunner(DkvMixin):
     def __init__(self, model, config):
         self.config = config
         self.model = model

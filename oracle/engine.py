@@ -129,3 +129,82 @@ def generate_with_acache(model, requests, anchor_ratio, selection_mode="top", th
         anchors_all.append(anchors)
         nfe += n
     return outs, nfe, anchors_all
+
+
+# ------------------------------------------------------------------------------------------
+# dKV-Cache decoding, one request at a time (reference: nano-vdllm/model_runner.py:1724-2030).
+def dkv_transfer_schedule(block_length, steps_per_block):
+    base, rem = divmod(block_length, steps_per_block)
+    return [base + (s < rem) for s in range(steps_per_block)]
+
+
+def generate_request_dkv(model, tokens, generation_start, gen_length, block_length, steps, cache_interval,
+                         affix_kv=None, affix_start=0, affix_end=0, anchors=None):
+    """Denoise one request with delayed KV refresh.  ``affix_kv`` given: the shared affix is read
+    from the cache and only the anchors and the request's own tokens are dynamic.  Temperature 0,
+    low-confidence remasking (confidence in fp64).  Returns (tokens list, nfe)."""
+    spec = model.spec
+    mask_id, dream = spec.mask_id, spec.kind == "dream"
+    n = len(tokens)
+    x = list(tokens)
+    if affix_kv is not None:
+        kv = _request_kv(model, affix_kv, n, affix_start)
+        dynamic = sorted(set(anchors) | set(range(affix_start)) | set(range(affix_end, n)))
+    else:
+        kv = KVState(spec, n, model.dtype)
+        dynamic = list(range(n))
+    dyn = set(dynamic)
+    num_blocks = gen_length // block_length
+    schedule = dkv_transfer_schedule(block_length, steps // num_blocks)
+    generation_end = generation_start + gen_length
+    nfe = 0
+    for b in range(num_blocks):
+        start = generation_start + b * block_length
+        previous = delayed = None
+        for step, quota in enumerate(schedule):
+            if dream:
+                refresh = step % cache_interval == 0
+                pred = {(p - 1) % n for p, t in enumerate(x) if t == mask_id}
+                q = set(dyn if refresh else dyn & pred)
+                q |= {max(p - 1, 0) for p in range(start, start + block_length) if x[p] == mask_id}
+                positions = sorted(q)
+            else:
+                refresh = step <= 1 or step % cache_interval == 0
+                positions = list(dynamic) if refresh else list(delayed)
+            masked = [p for p in range(start, start + block_length) if x[p] == mask_id]
+            where = {p: i for i, p in enumerate(positions)}
+            rows = torch.tensor([where[max(p - 1, 0) if dream else p] for p in masked], dtype=torch.long)
+            pos_t = torch.tensor(positions, dtype=torch.long)
+            write = torch.tensor([p if p in dyn else -1 for p in positions], dtype=torch.long)
+            logits = model.forward_rows(torch.tensor([x[p] for p in positions], dtype=torch.long), pos_t, kv, write,
+                                        logits_rows=rows)
+            nfe += 1
+            x0 = torch.argmax(logits, dim=-1)
+            if quota:
+                l64 = logits.to(torch.float64)
+                conf = torch.gather(l64, -1, x0[:, None]).squeeze(-1) - torch.logsumexp(l64, dim=-1)
+                for idx in torch.topk(conf, k=quota).indices.tolist():
+                    x[masked[idx]] = int(x0[idx])
+            unresolved = [p for p in range(start, generation_end) if x[p] == mask_id]
+            delayed, previous = previous, unresolved
+    return x, nfe
+
+
+def generate_with_dkv(model, requests, block_length, steps, cache_interval, anchor_ratio=None, selection_mode="top"):
+    """``anchor_ratio`` None: dKV-Cache alone (every request keeps a full cache of its own);
+    otherwise dKV-Cache on top of affix reuse.  Returns (generated spans, total nfe)."""
+    affix_kv = None
+    if anchor_ratio is not None:
+        r0 = requests[0]
+        affix_kv = compute_affix_kv(model, r0["tokens"][r0["affix_start"]: r0["affix_end"]])
+    outs, nfe = [], 0
+    for r in requests:
+        anchors = None
+        if affix_kv is not None:
+            anchors, _ = select_anchors(model, affix_kv, r["tokens"], r["affix_start"], r["affix_end"], anchor_ratio,
+                                        selection_mode)
+        toks, n = generate_request_dkv(model, r["tokens"], r["generation_start"], r["gen_length"], block_length, steps,
+                                       cache_interval, affix_kv, r["affix_start"], r["affix_end"], anchors)
+        outs.append(toks[r["generation_start"]: r["generation_start"] + r["gen_length"]])
+        nfe += n
+    return outs, nfe

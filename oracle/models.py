@@ -104,7 +104,7 @@ class OracleModel:
     def forward_rows(self, tokens, positions, kv: KVState, write_idx, logits_rows=None, probe=None):
         """tokens/positions: int64 [n] (the query rows, logical positions);
         write_idx: int64 [n] rows of ``kv`` that receive this forward's K/V
-        (normally == positions).  Attention of every row is over ALL rows of
+        (normally == positions; -1 = do not store this row).  Attention of every row is over ALL rows of
         ``kv`` (bidirectional).  ``probe``: optional dict with 'mask_rows'
         (bool [n]), 'affix' (slice of kv rows) and 'acc' (fp32 [A]) to
         accumulate the anchor influence score of every layer
@@ -130,8 +130,9 @@ class OracleModel:
                 from .importance import layer_importance
                 probe["acc"] += layer_importance(q[probe["mask_rows"]], kv.k[l, probe["affix"]], scale,
                                                  exact=probe.get("exact", False))
-            kv.k[l, write_idx] = k
-            kv.v[l, write_idx] = v
+            keep = write_idx >= 0      # -1: the row is only queried, its cached K/V stays
+            kv.k[l, write_idx[keep]] = k[keep]
+            kv.v[l, write_idx[keep]] = v[keep]
             kf = kv.k[l].float().permute(1, 2, 0).repeat_interleave(g, dim=0)
             vf = kv.v[l].float().permute(1, 0, 2).repeat_interleave(g, dim=0)
             w = torch.softmax((q.float().permute(1, 0, 2) @ kf) * scale, dim=-1)

@@ -45,6 +45,24 @@ def hf_llada():
     return meta, weights, arrays
 
 
+def _hf_fixture(name):
+    raw = load_npz(name)
+    meta = json.loads(bytes(raw.pop("meta")).decode())
+    weights = {k[3:]: torch.from_numpy(v) for k, v in raw.items() if k.startswith("w::")}
+    arrays = {k: v for k, v in raw.items() if not k.startswith("w::")}
+    return meta, weights, arrays
+
+
+@pytest.fixture(scope="session")
+def hf_llada_dkv():
+    return _hf_fixture("hf_llada_dkv.npz")
+
+
+@pytest.fixture(scope="session")
+def hf_dream_dkv():
+    return _hf_fixture("hf_dream_dkv.npz")
+
+
 @pytest.fixture(scope="session")
 def layout_cases():
     return json.loads((GOLDEN / "layout.json").read_text())

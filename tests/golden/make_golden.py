@@ -16,6 +16,11 @@ or $ACACHE_REFERENCE).  It imports the reference's own Python, read-only, on CPU
 * hf_llada.npz      - the reference HF batch-1 path (llada/generate_ACache.py) on a
                       tiny random LLaDA in fp32: importance scores, anchors, first
                       refresh logits, final tokens, nfe for prefix / infix / suffix
+* hf_llada_dkv.npz  - the reference HF batch-1 dKV + affix-reuse path for LLaDA
+                      (llada/eval_dKV_ACache.py generate_with_dkv_anchor_attention), same grid
+* hf_dream_dkv.npz  - the reference HF batch-1 dKV + affix-reuse path
+                      (dream/generate_dKV_ACache.py) on a tiny random Dream in fp32: final
+                      tokens and nfe for prefix / infix / suffix, 3 anchor ratios, 3 intervals
 
 Usage: TORCHDYNAMO_DISABLE=1 python tests/golden/make_golden.py <reference_root>
 """
@@ -343,8 +348,178 @@ def make_hf_llada():
     print("hf_llada.npz", len(meta))
 
 
+def make_hf_llada_dkv():
+    """The reference HF batch-1 dKV + affix-reuse path for LLaDA
+    (llada/eval_dKV_ACache.py:75-277 ``generate_with_dkv_anchor_attention``) on the tiny random
+    LLaDA of ``make_hf_llada``.  The file's evaluation-harness imports (lm_eval, accelerate) are not
+    installed here, so only its three generation functions are compiled, from the file as it
+    lies, into a namespace that holds the helpers they import."""
+    import ast
+    from typing import Optional, Sequence, Tuple
+
+    root = REF
+    pkg = "acache_hf_llada_model"
+    if pkg not in sys.modules:
+        package = types.ModuleType(pkg)
+        package.__path__ = [str(root / "llada" / "model")]
+        sys.modules[pkg] = package
+    cfgm = importlib.import_module(f"{pkg}.configuration_llada")
+    mm = importlib.import_module(f"{pkg}.modeling_llada")
+    sys.path.insert(0, str(root / "llada"))
+
+    def load(name, filename):
+        spec = importlib.util.spec_from_file_location(name, root / "llada" / filename)
+        module = importlib.util.module_from_spec(spec)
+        sys.modules[name] = module
+        spec.loader.exec_module(module)
+        return module
+
+    gen_acache = load("acache_hf_generate", "generate_ACache.py")
+    gen_plain = load("acache_hf_generate_plain", "generate.py")
+    source = (root / "llada" / "eval_dKV_ACache.py").read_text()
+    wanted = {"_dkv_transfer_schedule", "_full_cache_with_static_affix", "generate_with_dkv_anchor_attention"}
+    tree = ast.parse(source)
+    tree.body = [n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name in wanted]
+    assert {n.name for n in tree.body} == wanted
+    ns = dict(torch=torch, Optional=Optional, Sequence=Sequence, Tuple=Tuple,
+              KVCache=Sequence[Tuple[torch.Tensor, torch.Tensor]], add_gumbel_noise=gen_plain.add_gumbel_noise,
+              ceil_to_int=gen_acache.ceil_to_int,
+              compute_attention_importance_cross_affix=gen_acache.compute_attention_importance_cross_affix,
+              select_anchor_tokens=gen_acache.select_anchor_tokens)
+    exec(compile(ast.fix_missing_locations(tree), str(root / "llada" / "eval_dKV_ACache.py"), "exec"), ns)
+    generate = ns["generate_with_dkv_anchor_attention"]
+
+    from oracle.models import ArchSpec, random_state_dict
+
+    arch = ArchSpec("llada", n_layers=2, d_model=64, n_heads=4, n_kv_heads=4, ffn=96, vocab=128,
+                    rope_theta=10000.0, rms_eps=1e-5, act="silu", mask_id=127)
+    cfg = cfgm.LLaDAConfig(
+        vocab_size=128, embedding_size=128, d_model=64, n_heads=4, n_kv_heads=4, n_layers=2, mlp_hidden_size=96,
+        activation_type="silu", block_type="llama", rope=True, rope_theta=10000.0, attention_dropout=0.0,
+        residual_dropout=0.0, embedding_dropout=0.0, eos_token_id=0, pad_token_id=0, mask_token_id=127,
+        layer_norm_type="rms", weight_tying=False, include_bias=False, flash_attention=False, init_device="cpu")
+    model = mm.LLaDAModelLM(cfg).eval()
+    sd = random_state_dict(arch, seed=9, std=0.35)
+    model.load_state_dict(sd, strict=True)
+
+    pyr = random.Random(35)
+    A, G, BL, STEPS = 7, 8, 4, 8
+    affix = [pyr.randint(1, 120) for _ in range(A)]
+    res = {f"w::{k}": v.numpy() for k, v in sd.items()}
+    meta = []
+    with torch.inference_mode():
+        cache = model(torch.tensor([affix]), use_cache=True).past_key_values
+        for mode, head, tail in (("prefix", 0, 5), ("infix", 3, 4), ("suffix", 4, 0)):
+            if mode == "prefix":
+                prompt = affix + [pyr.randint(1, 120) for _ in range(tail)]
+                kw = dict(affix_start=0, affix_end=A, generation_start=None)
+            elif mode == "infix":
+                prompt = [pyr.randint(1, 120) for _ in range(head)] + affix + [pyr.randint(1, 120) for _ in range(tail)]
+                kw = dict(affix_start=head, affix_end=head + A, generation_start=None)
+            else:
+                prompt = [pyr.randint(1, 120) for _ in range(head)] + [127] * G + affix
+                kw = dict(affix_start=head + G, affix_end=head + G + A, generation_start=head)
+            x = torch.tensor([prompt])
+            for ratio in (0.0, 0.3, 1.0):
+                for interval in (1, 2, 3):
+                    tokens, nfe = generate(model, x, steps=STEPS, gen_length=G, block_length=BL, temperature=0.,
+                                           remasking="low_confidence", mask_id=127, selection_mode="top",
+                                           drop_non_anchor=False, anchor_ratio=ratio, dkv_cache_interval=interval,
+                                           precomputed_affix_cache=cache, **kw)
+                    tag = f"{mode}_r{ratio}_i{interval}"
+                    res[f"{tag}::tokens"] = tokens[0].numpy()
+                    meta.append(dict(tag=tag, mode=mode, prompt=prompt, gen_length=G, block_length=BL, steps=STEPS,
+                                     anchor_ratio=ratio, interval=interval, nfe=int(nfe), **kw))
+    res["meta"] = np.frombuffer(json.dumps(dict(cases=meta, arch=arch.__dict__)).encode(), dtype=np.uint8)
+    np.savez_compressed(HERE / "hf_llada_dkv.npz", **res)
+    print("hf_llada_dkv.npz", len(meta))
+
+
+def make_hf_dream_dkv():
+    """The reference HF batch-1 dKV + affix-reuse path (dream/generate_dKV_ACache.py) on a tiny
+    random Dream in fp32: final tokens and NFE for prefix / infix / suffix placement, several
+    anchor ratios and cache intervals (the cases of the reference's own
+    nano-vdllm/tests/test_dream_dkv.py:60-111, run here on CPU in fp32)."""
+    root = REF / "dream"
+    pkg = "acache_hf_dream_model"
+    package = types.ModuleType(pkg)
+    package.__path__ = [str(root / "model")]
+    sys.modules[pkg] = package
+    # the installed transformers no longer ships the plain RoPE initialiser the reference's HF
+    # Dream model looks up by the name "default": inv_freq[j] = theta^(-2j/D), no scaling
+    from transformers import modeling_rope_utils as _mru
+
+    def _default_rope(config, device=None, **_):
+        dim = getattr(config, "head_dim", None) or config.hidden_size // config.num_attention_heads
+        inv = 1.0 / (config.rope_theta ** (torch.arange(0, dim, 2, dtype=torch.int64).float().to(device) / dim))
+        return inv, 1.0
+
+    _mru.ROPE_INIT_FUNCTIONS.setdefault("default", _default_rope)
+    cfgm = importlib.import_module(f"{pkg}.configuration_dream")
+    mm = importlib.import_module(f"{pkg}.modeling_dream")
+
+    def load(name, filename):
+        spec = importlib.util.spec_from_file_location(name, root / filename)
+        module = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(module)
+        return module
+
+    # the reference scripts import their model code as the top-level package ``model``
+    sys.modules["model.generation_utils_block"] = importlib.import_module(f"{pkg}.generation_utils_block")
+    sys.modules["model.modeling_dream"] = mm
+    sys.modules["generate_ACache"] = load("acache_hf_dream_generate", "generate_ACache.py")
+    gen = load("acache_hf_dream_dkv", "generate_dKV_ACache.py")
+
+    from oracle.models import ArchSpec, random_state_dict
+
+    arch = ArchSpec("dream", n_layers=2, d_model=64, n_heads=4, n_kv_heads=4, ffn=128, vocab=128,
+                    rope_theta=10000.0, rms_eps=1e-6, act="silu", mask_id=127)
+    cfg = cfgm.DreamConfig(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                           num_attention_heads=4, num_key_value_heads=4, max_position_embeddings=64,
+                           mask_token_id=127, pad_token_id=0, rope_theta=10000.0, rms_norm_eps=1e-6)
+    model = mm.DreamModel(cfg).eval()
+    sd = random_state_dict(arch, seed=5, std=0.35)
+    missing = model.load_state_dict(sd, strict=False)
+    assert not missing.unexpected_keys and all("rotary" in k or "inv_freq" in k for k in missing.missing_keys), missing
+
+    pyr = random.Random(33)
+    A, G, BL, STEPS = 6, 8, 4, 8
+    affix = [pyr.randint(1, 120) for _ in range(A)]
+    res = {f"w::{k}": v.numpy() for k, v in sd.items()}
+    meta = []
+    with torch.inference_mode():
+        for mode, head, tail in (("prefix", 0, 5), ("infix", 3, 4), ("suffix", 4, 0)):
+            if mode == "prefix":
+                prompt = affix + [pyr.randint(1, 120) for _ in range(tail)]
+                kw = dict(affix_start=0, affix_end=A, generation_start=None)
+            elif mode == "infix":
+                prompt = [pyr.randint(1, 120) for _ in range(head)] + affix + [pyr.randint(1, 120) for _ in range(tail)]
+                kw = dict(affix_start=head, affix_end=head + A, generation_start=None)
+            else:
+                prompt = [pyr.randint(1, 120) for _ in range(head)] + [127] * G + affix
+                kw = dict(affix_start=head + G, affix_end=head + G + A, generation_start=head)
+            x = torch.tensor([prompt])
+            cache = model(x[:, kw["affix_start"]: kw["affix_end"]], use_cache=True).past_key_values
+            for ratio in (0.0, 0.34, 1.0):
+                for interval in (1, 2, 3):
+                    tokens, nfe = gen.generate_with_dkv_anchor_attention(
+                        model, x, steps=STEPS, gen_length=G, block_length=BL, temperature=0., remasking="low_confidence",
+                        mask_id=127, selection_mode="top", drop_non_anchor=False, anchor_ratio=ratio,
+                        dkv_cache_interval=interval, precomputed_affix_cache=cache, **kw)
+                    tag = f"{mode}_r{ratio}_i{interval}"
+                    res[f"{tag}::tokens"] = tokens[0].numpy()
+                    meta.append(dict(tag=tag, mode=mode, prompt=prompt, gen_length=G, block_length=BL, steps=STEPS,
+                                     anchor_ratio=ratio, interval=interval, nfe=int(nfe), **kw))
+    res["meta"] = np.frombuffer(json.dumps(dict(cases=meta, arch=arch.__dict__)).encode(), dtype=np.uint8)
+    np.savez_compressed(HERE / "hf_dream_dkv.npz", **res)
+    print("hf_dream_dkv.npz", len(meta))
+
+
 if __name__ == "__main__":
-    which = sys.argv[2:] or ["layout", "triton", "sampling", "hf"]
+    which = sys.argv[2:] or ["layout", "triton", "sampling", "hf", "dkv"]
+    if "dkv" in which:
+        make_hf_llada_dkv()
+        make_hf_dream_dkv()
     if "layout" in which:
         make_layout()
     if "triton" in which:

@@ -271,6 +271,86 @@ def test_graph_replayed_decode_equals_eager_decode(dtype):
     _lib.check_device_errors()
 
 
+@pytest.mark.parametrize("which,kind", [("hf_llada_dkv", "llada"), ("hf_dream_dkv", "dream")])
+def test_dkv_engine_matches_hf_reference_fixtures(which, kind, request):
+    """dKV-Cache decoding on top of affix reuse, fp32: the tokens of the reference's HF batch-1
+    path for prefix / infix / suffix placement (batched here, three requests per run), anchor
+    ratios 0, ~1/3 and 1, cache intervals 1-3; with ratio 1 the plain dKV engine gives the same."""
+    from acache_b200.model_runner import ModelRunner
+    from oracle.models import ArchSpec
+
+    meta, weights, arrays = request.getfixturevalue(which)
+    arch = ArchSpec(**meta["arch"])
+    hf_cfg, model = (_llada if kind == "llada" else _dream)(arch, weights, torch.float32)
+    grid = sorted({(c["anchor_ratio"], c["interval"]) for c in meta["cases"]})
+    for ratio, interval in grid:
+        cases = [c for c in meta["cases"] if (c["anchor_ratio"], c["interval"]) == (ratio, interval)]
+        G, T, steps = cases[0]["gen_length"], cases[0]["block_length"], cases[0]["steps"]
+        cfg = _serve_config(hf_cfg, arch, kind, torch.float32, anchor_ratio=ratio, gen_length=G, block_length=T,
+                            dkv_steps=steps, dkv_cache_interval=interval, enable_dkv_cache=True, max_num_seqs=3)
+        runner = ModelRunner(model, cfg)
+        seqs = [_sequence(c, arch) for c in cases]
+        outs, nfe = runner.generate_with_dkv_acache(seqs)
+        assert nfe == steps * len(cases)
+        for c, seq, out in zip(cases, seqs, outs):
+            want = arrays[c["tag"] + "::tokens"].tolist()
+            assert seq.token_ids == want, c["tag"]
+            g0 = len(c["prompt"]) if c["generation_start"] is None else c["generation_start"]
+            assert out == want[g0: g0 + G], c["tag"]
+        if ratio == 1.0:   # every affix token recomputed = no reuse at all
+            cfg = _serve_config(hf_cfg, arch, kind, torch.float32, gen_length=G, block_length=T, dkv_steps=steps,
+                                dkv_cache_interval=interval, enable_dkv_cache=True, enable_acache=False, max_num_seqs=2)
+            plain = ModelRunner(model, cfg)
+            from acache_b200.sequence import Sequence
+
+            prompts = []
+            for c in cases:
+                toks = list(c["prompt"])
+                prompts.append(Sequence(toks, block_length=T, gen_length=G, cache_block_size=8, mask_id=arch.mask_id,
+                                        generation_start=c["generation_start"]))
+            outs2, nfe2 = plain.generate_with_dkv_cache(prompts)
+            assert outs2 == outs and nfe2 == nfe
+
+
+@pytest.mark.parametrize("kind,nh,hkv", [("llada", 4, 2), ("dream", 4, 2)])
+def test_dkv_engine_matches_cpu_oracle_fp32(kind, nh, hkv):
+    """Random tiny GQA models, five requests over mixed placements in static batches of three:
+    dKV alone and dKV on top of affix reuse against the request-at-a-time CPU restatement."""
+    from acache_b200.model_runner import ModelRunner
+    from acache_b200.sequence import Sequence
+    from oracle.engine import generate_with_dkv
+    from oracle.models import ArchSpec, OracleModel, random_state_dict
+
+    rng = random.Random(41)
+    arch = ArchSpec(kind, n_layers=2, d_model=64, n_heads=nh, n_kv_heads=hkv, ffn=96, vocab=160, rope_theta=10000.0,
+                    rms_eps=1e-5 if kind == "llada" else 1e-6, act="silu", mask_id=159)
+    weights = random_state_dict(arch, seed=13, std=0.3)
+    A, G, T, steps, interval = 11, 8, 4, 4, 2
+    affix = [rng.randint(1, 150) for _ in range(A)]
+    reqs = _random_requests(rng, arch, 5, A, G, ["infix", "prefix", "suffix"], affix)
+    oracle = OracleModel(arch, weights, torch.float32)
+    o_req = []
+    for r in reqs:
+        toks = list(r["prompt"]) + ([arch.mask_id] * G if r["generation_start"] is None else [])
+        o_req.append(dict(tokens=toks, affix_start=r["affix_start"], affix_end=r["affix_end"],
+                          generation_start=len(r["prompt"]) if r["generation_start"] is None else r["generation_start"],
+                          gen_length=G))
+    hf_cfg, model = (_llada if kind == "llada" else _dream)(arch, weights, torch.float32)
+    for ratio in (None, 0.3):
+        want, want_nfe = generate_with_dkv(oracle, o_req, T, steps, interval, ratio)
+        cfg = _serve_config(hf_cfg, arch, kind, torch.float32, anchor_ratio=ratio or 0.0, gen_length=G, block_length=T,
+                            dkv_steps=steps, dkv_cache_interval=interval, enable_dkv_cache=True,
+                            enable_acache=ratio is not None, max_num_seqs=3, num_kvcache_blocks=40)
+        runner = ModelRunner(model, cfg)
+        seqs = [Sequence(r["prompt"], block_length=T, gen_length=G, cache_block_size=8, mask_id=arch.mask_id,
+                         prompt_affix_start=r["affix_start"] if ratio is not None else None,
+                         prompt_affix_end=r["affix_end"] if ratio is not None else None,
+                         generation_start=r["generation_start"]) for r in reqs]
+        outs, nfe = (runner.generate_with_dkv_acache if ratio is not None else runner.generate_with_dkv_cache)(seqs)
+        assert outs == want, ratio
+        assert nfe == want_nfe
+
+
 def test_reuse_with_every_affix_token_an_anchor_equals_no_reuse_baseline(hf_llada):
     """reference: nano-vdllm/tests/test_model_runner_acache.py:597-687 (ratio 1.0 recomputes
     the whole affix, so the logits equal the full-recompute baseline)."""
