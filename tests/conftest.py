@@ -54,6 +54,11 @@ def _hf_fixture(name):
 
 
 @pytest.fixture(scope="session")
+def hf_dream():
+    return _hf_fixture("hf_dream.npz")
+
+
+@pytest.fixture(scope="session")
 def hf_llada_dkv():
     return _hf_fixture("hf_llada_dkv.npz")
 

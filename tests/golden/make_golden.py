@@ -16,6 +16,7 @@ or $ACACHE_REFERENCE).  It imports the reference's own Python, read-only, on CPU
 * hf_llada.npz      - the reference HF batch-1 path (llada/generate_ACache.py) on a
                       tiny random LLaDA in fp32: importance scores, anchors, first
                       refresh logits, final tokens, nfe for prefix / infix / suffix
+* hf_dream.npz      - the same for Dream (dream/generate_ACache.py), GQA
 * hf_llada_dkv.npz  - the reference HF batch-1 dKV + affix-reuse path for LLaDA
                       (llada/eval_dKV_ACache.py generate_with_dkv_anchor_attention), same grid
 * hf_dream_dkv.npz  - the reference HF batch-1 dKV + affix-reuse path
@@ -435,11 +436,9 @@ def make_hf_llada_dkv():
     print("hf_llada_dkv.npz", len(meta))
 
 
-def make_hf_dream_dkv():
-    """The reference HF batch-1 dKV + affix-reuse path (dream/generate_dKV_ACache.py) on a tiny
-    random Dream in fp32: final tokens and NFE for prefix / infix / suffix placement, several
-    anchor ratios and cache intervals (the cases of the reference's own
-    nano-vdllm/tests/test_dream_dkv.py:60-111, run here on CPU in fp32)."""
+def _hf_dream_modules():
+    """(configuration module, modeling module, generate_ACache module, loader) of the reference's
+    HF Dream path."""
     root = REF / "dream"
     pkg = "acache_hf_dream_model"
     package = types.ModuleType(pkg)
@@ -467,20 +466,76 @@ def make_hf_dream_dkv():
     # the reference scripts import their model code as the top-level package ``model``
     sys.modules["model.generation_utils_block"] = importlib.import_module(f"{pkg}.generation_utils_block")
     sys.modules["model.modeling_dream"] = mm
-    sys.modules["generate_ACache"] = load("acache_hf_dream_generate", "generate_ACache.py")
-    gen = load("acache_hf_dream_dkv", "generate_dKV_ACache.py")
+    if "generate_ACache" not in sys.modules or getattr(sys.modules["generate_ACache"], "__name__", "") != "acache_hf_dream_generate":
+        sys.modules["generate_ACache"] = load("acache_hf_dream_generate", "generate_ACache.py")
+    return cfgm, mm, sys.modules["generate_ACache"], load
 
+
+def _tiny_hf_dream(cfgm, mm, seed, n_kv_heads=4):
     from oracle.models import ArchSpec, random_state_dict
 
-    arch = ArchSpec("dream", n_layers=2, d_model=64, n_heads=4, n_kv_heads=4, ffn=128, vocab=128,
+    arch = ArchSpec("dream", n_layers=2, d_model=64, n_heads=4, n_kv_heads=n_kv_heads, ffn=128, vocab=128,
                     rope_theta=10000.0, rms_eps=1e-6, act="silu", mask_id=127)
     cfg = cfgm.DreamConfig(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
-                           num_attention_heads=4, num_key_value_heads=4, max_position_embeddings=64,
+                           num_attention_heads=4, num_key_value_heads=n_kv_heads, max_position_embeddings=64,
                            mask_token_id=127, pad_token_id=0, rope_theta=10000.0, rms_norm_eps=1e-6)
     model = mm.DreamModel(cfg).eval()
-    sd = random_state_dict(arch, seed=5, std=0.35)
+    sd = random_state_dict(arch, seed=seed, std=0.35)
     missing = model.load_state_dict(sd, strict=False)
     assert not missing.unexpected_keys and all("rotary" in k or "inv_freq" in k for k in missing.missing_keys), missing
+    return arch, model, sd
+
+
+def make_hf_dream():
+    """The reference HF batch-1 affix-reuse path for Dream (dream/generate_ACache.py) on a tiny
+    random GQA Dream in fp32: importance scores, anchors, final tokens, nfe."""
+    cfgm, mm, gen, _ = _hf_dream_modules()
+    arch, model, sd = _tiny_hf_dream(cfgm, mm, seed=7, n_kv_heads=2)
+    pyr = random.Random(23)
+    A, G, BL = 12, 8, 4
+    affix = [pyr.randint(1, 120) for _ in range(A)]
+    res = {f"w::{k}": v.numpy() for k, v in sd.items()}
+    meta = []
+    with torch.inference_mode():
+        affix_cache = model(torch.tensor([affix]), use_cache=True).past_key_values
+        for i, (mode, head, tail) in enumerate((("prefix", 0, 7), ("infix", 5, 6), ("suffix", 9, 0), ("infix", 2, 9))):
+            if mode == "prefix":
+                prompt = affix + [pyr.randint(1, 120) for _ in range(tail)]
+                kw = dict(affix_start=0, affix_end=A, generation_start=None)
+            elif mode == "infix":
+                prompt = [pyr.randint(1, 120) for _ in range(head)] + affix + [pyr.randint(1, 120) for _ in range(tail)]
+                kw = dict(affix_start=head, affix_end=head + A, generation_start=None)
+            else:
+                prompt = [pyr.randint(1, 120) for _ in range(head)] + [127] * G + affix
+                kw = dict(affix_start=head + G, affix_end=head + G + A, generation_start=head)
+            for thr in (0.9, 0.05):
+                p = torch.tensor([prompt])
+                x = torch.cat([p, torch.full((1, G), 127)], dim=1) if kw["generation_start"] is None else p.clone()
+                imp = gen.compute_attention_importance_cross_affix(model, x, affix_cache, mask_id=127,
+                                                                   affix_start=kw["affix_start"])
+                k = min(gen.ceil_to_int(0.25 * A), A)
+                anchors = (gen.select_anchor_tokens(imp, k, "top")[0] + kw["affix_start"]).tolist()
+                outx, nfe = gen.generate_with_anchor_attention(
+                    model, p, steps=G, gen_length=G, block_length=BL, mask_id=127, threshold=thr,
+                    anchor_ratio=0.25, selection_mode="top", precomputed_affix_cache=affix_cache, **kw)
+                tag = f"case{i}_thr{thr}"
+                res[f"{tag}::importance"] = imp[0].numpy()
+                res[f"{tag}::tokens"] = outx[0].numpy()
+                meta.append(dict(tag=tag, mode=mode, prompt=prompt, gen_length=G, block_length=BL, threshold=thr,
+                                 anchor_ratio=0.25, anchors=anchors, nfe_with_probe=int(nfe), **kw))
+    res["meta"] = np.frombuffer(json.dumps(dict(cases=meta, arch=arch.__dict__)).encode(), dtype=np.uint8)
+    np.savez_compressed(HERE / "hf_dream.npz", **res)
+    print("hf_dream.npz", len(meta))
+
+
+def make_hf_dream_dkv():
+    """The reference HF batch-1 dKV + affix-reuse path (dream/generate_dKV_ACache.py) on a tiny
+    random Dream in fp32: final tokens and NFE for prefix / infix / suffix placement, several
+    anchor ratios and cache intervals (the cases of the reference's own
+    nano-vdllm/tests/test_dream_dkv.py:60-111, run here on CPU in fp32)."""
+    cfgm, mm, _, load = _hf_dream_modules()
+    gen = load("acache_hf_dream_dkv", "generate_dKV_ACache.py")
+    arch, model, sd = _tiny_hf_dream(cfgm, mm, seed=5)
 
     pyr = random.Random(33)
     A, G, BL, STEPS = 6, 8, 4, 8
@@ -516,7 +571,9 @@ def make_hf_dream_dkv():
 
 
 if __name__ == "__main__":
-    which = sys.argv[2:] or ["layout", "triton", "sampling", "hf", "dkv"]
+    which = sys.argv[2:] or ["layout", "triton", "sampling", "hf", "dream", "dkv"]
+    if "dream" in which:
+        make_hf_dream()
     if "dkv" in which:
         make_hf_llada_dkv()
         make_hf_dream_dkv()

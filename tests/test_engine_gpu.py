@@ -57,18 +57,20 @@ def _sequence(case, arch, block=8):
                     prompt_affix_end=case["affix_end"], generation_start=case["generation_start"])
 
 
-def test_engine_matches_hf_reference_fixtures(hf_llada):
-    """fp32 end to end: anchors and greedy tokens of the reference's HF path for prefix,
-    infix and suffix placement, with the requests mixed in one continuously batched run."""
+@pytest.mark.parametrize("which,kind", [("hf_llada", "llada"), ("hf_dream", "dream")])
+def test_engine_matches_hf_reference_fixtures(which, kind, request):
+    """fp32 end to end: anchors and greedy tokens of the reference's HF paths (LLaDA; Dream with
+    GQA) for prefix, infix and suffix placement, with the requests mixed in one continuously
+    batched run."""
     from acache_b200.model_runner import ModelRunner
     from oracle.models import ArchSpec
 
-    meta, weights, arrays = hf_llada
+    meta, weights, arrays = request.getfixturevalue(which)
     arch = ArchSpec(**meta["arch"])
-    hf_cfg, model = _llada(arch, weights, torch.float32)
+    hf_cfg, model = (_llada if kind == "llada" else _dream)(arch, weights, torch.float32)
     for thr in (0.9, 0.05):
         cases = [c for c in meta["cases"] if c["threshold"] == thr]
-        runner = ModelRunner(model, _serve_config(hf_cfg, arch, "llada", torch.float32, threshold=thr))
+        runner = ModelRunner(model, _serve_config(hf_cfg, arch, kind, torch.float32, threshold=thr))
         seqs = [_sequence(c, arch) for c in cases]
         outs, nfe = runner.generate_with_acache(seqs)
         want_nfe = 0

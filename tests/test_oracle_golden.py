@@ -1,6 +1,7 @@
 """The CPU restatement (oracle/) against fixtures produced by the reference's
 own code (tests/golden/make_golden.py).  No GPU needed."""
 import numpy as np
+import pytest
 import torch
 
 from conftest import load_npz
@@ -74,10 +75,11 @@ def test_topk_tie_rule_is_lowest_index():
     assert topk.anchor_topk(z, 4, True).tolist() == [[0, 1, 2, 3]] * 2
 
 
-def test_engine_restatement_vs_hf_reference_path(hf_llada):
+@pytest.mark.parametrize("which", ["hf_llada", "hf_dream"])
+def test_engine_restatement_vs_hf_reference_path(which, request):
     """Anchors, importance scores and final tokens of the reference's HF batch-1
-    path (fp32, CPU) for prefix / infix / suffix placement."""
-    meta, weights, arrays = hf_llada
+    paths (LLaDA, Dream with GQA; fp32, CPU) for prefix / infix / suffix placement."""
+    meta, weights, arrays = request.getfixturevalue(which)
     arch = ArchSpec(**meta["arch"])
     model = OracleModel(arch, weights, torch.float32)
     affix_kv = None
