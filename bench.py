@@ -212,7 +212,14 @@ def run_ours(args):
                  gen_length=GEN, block_length=BLOCK, threshold=THRESHOLD, cache_block_size=256,
                  num_kvcache_blocks=shared_blocks + 3 * args.batch + 4, enable_acache=True, anchor_ratio=RATIO,
                  selection_mode="top", model_type="llada", profile_timing=True)
+    if args.mode == "dkv_acache":      # second serving mode of the engine: delayed KV refresh on top of affix reuse
+        cfg.enable_dkv_cache, cfg.dkv_steps, cfg.dkv_cache_interval = True, GEN, 8
+    if args.mode == "dual_cache":      # the no-reuse baseline: every request keeps its own copy of the affix
+        cfg.enable_acache = False
+        cfg.num_kvcache_blocks = args.batch * -(-(AFFIX_LEN + REQ_HI + GEN) // 256) + 4
     runner = ModelRunner(model, cfg)
+    generate = {"acache": runner.generate_with_acache, "dkv_acache": runner.generate_with_dkv_acache,
+                "dual_cache": runner.generate_with_dual_cache}[args.mode]
 
     def host_inputs(step):
         # every rank (replica) serves its own shard of requests; the affix is common
@@ -255,7 +262,7 @@ def run_ours(args):
 
     for w in range(args.warmup):
         a, t = host_inputs(10_000 + w)
-        runner.generate_with_acache(build(a, t))
+        generate(build(a, t))
 
     # ---- device-timed region: K steps, requests prebuilt
     prebuilt = [build(*host_inputs(s)) for s in range(args.steps)]
@@ -271,7 +278,7 @@ def run_ours(args):
     recompute_ms, recompute_calls = 0.0, 0
     sections = {}
     for seqs in prebuilt:
-        outs, n = runner.generate_with_acache(seqs)
+        outs, n = generate(seqs)
         nfe += n
         recompute_ms += runner.last_timing.get("cache_forward", 0.0) * 1e3
         recompute_calls += runner.last_timing.get("cache_forward_calls", 0)
@@ -293,7 +300,7 @@ def run_ours(args):
     t0 = time.perf_counter()
     for s in range(args.steps):
         a, t = host_inputs(5_000 + s)
-        outs, _ = runner.generate_with_acache(build(a, t))
+        outs, _ = generate(build(a, t))
         assert all(isinstance(o, list) and len(o) == GEN for o in outs)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
@@ -332,14 +339,19 @@ def run_ours(args):
             roof["share_of_step"] = ms / dev_ms
             roof["other_timed"] = {k: dict(ms=v[0], launches=v[1]) for k, v in timers.items() if k != name}
         cpu = None
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and args.mode == "acache":
             cpu = cpu_reference_sample()
             cpu.pop("seconds")
+        metric = "generated tok/s/box LLaDA-8B-arch bs16 affix reuse"
+        workload = WORKLOAD
+        if args.mode != "acache":   # not the benchmark: another serving mode of the engine on the same requests
+            metric += {"dkv_acache": " + dKV-Cache decoding", "dual_cache": " OFF (no-reuse baseline)"}[args.mode]
+            workload += {"dkv_acache": ", dKV steps 256, cache interval 8", "dual_cache": ", every request recomputes the affix"}[args.mode]
         line = dict(
-            metric="generated tok/s/box LLaDA-8B-arch bs16 affix reuse", value=tokens / (dev_ms * 1e-3), unit="tok/s",
+            metric=metric, value=tokens / (dev_ms * 1e-3), unit="tok/s",
             n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=dev_ms / args.steps, higher_is_better=True,
             scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
-            config={"workload": WORKLOAD, "batch_per_gpu": args.batch, "layers": hf.n_layers, "parallelism": f"dp{world}",
+            config={"workload": workload, "batch_per_gpu": args.batch, "layers": hf.n_layers, "parallelism": f"dp{world}",
                     "l2": "weights (16 GB) and K/V re-read every step exceed the 126 MB L2"},
             clocks=clocks,
             e2e={"value": tokens / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -360,6 +372,8 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH, help="requests per GPU (the workload is 16)")
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the architecture")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--mode", default="acache", choices=["acache", "dkv_acache", "dual_cache"],
+                    help="acache = the benchmark; the other serving modes of the engine on the same workload")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
