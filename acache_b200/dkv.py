@@ -139,7 +139,13 @@ class DkvMixin:
         cu_k = np.zeros(len(seqs) + 1, dtype=np.int32)
         for row, (seq, rp) in enumerate(zip(seqs, query_positions)):
             self._check_query_positions(seq, rp)
-            slot_of = dict(zip(seq.recompute_positions, seq.recompute_slot_mapping))
+            cached = getattr(seq, "_dkv_layout", None)    # per request, until its slot layout changes
+            if cached is None or cached[0] is not seq.recompute_slot_mapping or cached[1] != use_qr:
+                layout, n_shared = self._attention_read_layout(seq, use_qr)
+                cached = seq._dkv_layout = (seq.recompute_slot_mapping, use_qr,
+                                            dict(zip(seq.recompute_positions, seq.recompute_slot_mapping)),
+                                            np.asarray(layout, dtype=np.int32), n_shared)
+            slot_of = cached[2]
             try:
                 row_slots = [slot_of.get(p, -1) if dream else slot_of[p] for p in rp]
             except KeyError as exc:
@@ -149,9 +155,8 @@ class DkvMixin:
             ids.append(np.asarray(seq.token_ids, dtype=np.int64)[rp])
             pos.append(rp)
             slots.append(np.asarray(row_slots, dtype=np.int32))
-            layout, n_shared = self._attention_read_layout(seq, use_qr)
-            read.append(np.asarray(layout, dtype=np.int32))
-            shared_lens.append(n_shared)
+            read.append(cached[3])
+            shared_lens.append(cached[4])
             shifts.append(seq.affix_start if self._affix_relocation_enabled else 0)
             cu_q[row + 1] = cu_q[row] + rp.shape[0]
             cu_k[row + 1] = cu_k[row] + len(seq)
