@@ -353,6 +353,54 @@ def test_dkv_engine_matches_cpu_oracle_fp32(kind, nh, hkv):
         assert nfe == want_nfe
 
 
+def test_long_affix_at_real_head_dimensions_runs_clean_and_deterministic():
+    """Two layers of the LLaDA-8B architecture (32 heads x 128, hidden 4096) in bf16 with an
+    8192-token shared affix placed inside the prompts (query-side relocation), six requests in
+    batches of four: the chunked influence score, relocation, refresh and long block decode at the
+    sizes of the long-context workload.  No CPU restatement at this size; the check is that the
+    run completes, leaves no mask and no device-side error, and repeats exactly."""
+    from acache_b200 import _lib
+    from acache_b200.config import Config
+    from acache_b200.model.configuration import LLaDAConfig
+    from acache_b200.model.modeling_llada import LLaDAModelLM
+    from acache_b200.model_runner import ModelRunner
+    from acache_b200.sequence import Sequence
+
+    hf = LLaDAConfig.llada_8b()
+    hf.n_layers = 2
+    model = LLaDAModelLM(hf, device=DEV, dtype=torch.bfloat16, init_params=True, seed=77).eval()
+    with torch.no_grad():
+        w = model.model.transformer["ff_out"].weight
+        w[hf.mask_token_id] = w[0]          # the mask token is never the arg-max
+    model.fuse_projections()
+    rng = random.Random(3)
+    A, G, T = 8192, 64, 32
+    affix = [t if t != hf.mask_token_id else 1 for t in (rng.randrange(1, hf.vocab_size - 1) for _ in range(A))]
+    reqs = []
+    for i in range(6):
+        head = [1 + rng.randrange(1000) for _ in range(rng.randint(5, 300))]
+        tail = [1 + rng.randrange(1000) for _ in range(rng.randint(5, 300))]
+        reqs.append((head + affix + tail, len(head)))
+
+    def run():
+        cfg = Config(hf_config=hf, mask_id=hf.mask_token_id, recompute_batch_size=2, max_num_seqs=4, gen_length=G,
+                     block_length=T, threshold=0.9, cache_block_size=256, num_kvcache_blocks=32 + 4 * 12 + 8,
+                     enable_acache=True, anchor_ratio=0.1, selection_mode="top", model_type="llada")
+        runner = ModelRunner(model, cfg)
+        seqs = [Sequence(p, block_length=T, gen_length=G, cache_block_size=256, mask_id=hf.mask_token_id,
+                         prompt_affix_start=a0, prompt_affix_end=a0 + A) for p, a0 in reqs]
+        outs, nfe = runner.generate_with_acache(seqs)
+        return outs, nfe, [s.anchor_positions for s in seqs]
+
+    outs, nfe, anchors = run()
+    _lib.check_device_errors()
+    assert all(len(o) == G and hf.mask_token_id not in o and all(0 <= t < hf.vocab_size for t in o) for o in outs)
+    assert all(len(a) == 820 and a == sorted(set(a)) for a in anchors)
+    assert all(a0 <= a[0] and a[-1] < a0 + A for a, (_, a0) in zip(anchors, reqs))
+    again = run()
+    assert again == (outs, nfe, anchors)
+
+
 def test_reuse_with_every_affix_token_an_anchor_equals_no_reuse_baseline(hf_llada):
     """reference: nano-vdllm/tests/test_model_runner_acache.py:597-687 (ratio 1.0 recomputes
     the whole affix, so the logits equal the full-recompute baseline)."""
