@@ -209,8 +209,12 @@ class _DecodeGraph:
         graph = torch.cuda.CUDAGraph()
         self.events = _lib.begin_graph_capture()
         launches0 = _lib.LAUNCHES
+        if runner._graph_pool is None:
+            # one memory pool for all decode graphs: they never run at the same time and the
+            # logits of one replay are consumed before the next replay
+            runner._graph_pool = torch.cuda.graph_pool_handle()
         try:
-            with torch.cuda.graph(graph):
+            with torch.cuda.graph(graph, pool=runner._graph_pool):
                 self.logits = forward()
         finally:
             _lib.end_graph_capture()
@@ -250,6 +254,7 @@ class ModelRunner(DkvMixin):
         self._attn_layers = [m for m in self.model.modules() if hasattr(m, "k_cache") and hasattr(m, "v_cache")]
         # captured block-decode forwards, by (rows, layout of the step metadata)
         self._decode_graphs: dict = {}
+        self._graph_pool = None
         self._decode_graph = None
         self._graph_with_pending_timers = None
         self._rope_caches = [m.rope for m in self.model.modules() if hasattr(m, "rope") and hasattr(m.rope, "get")]

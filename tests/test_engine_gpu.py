@@ -401,6 +401,58 @@ def test_long_affix_at_real_head_dimensions_runs_clean_and_deterministic():
     assert again == (outs, nfe, anchors)
 
 
+def test_dream_at_real_head_dimensions_runs_clean_and_deterministic():
+    """Two layers of the Dream-7B architecture (28 query heads on 4 KV heads x 128, hidden 3584,
+    bf16 RoPE tables) with a 600-token shared affix in prefix / infix / suffix placement: GQA
+    row packing (7 heads share a K/V pass), Dream's shifted logits, both serving modes."""
+    from acache_b200 import _lib
+    from acache_b200.config import Config
+    from acache_b200.model.configuration import DreamConfig
+    from acache_b200.model.modeling_dream import DreamModel
+    from acache_b200.model_runner import ModelRunner
+    from acache_b200.sequence import Sequence
+
+    hf = DreamConfig.dream_7b()
+    hf.num_hidden_layers = 2
+    model = DreamModel(hf, device=DEV, dtype=torch.bfloat16, init_params=True, seed=78).eval()
+    with torch.no_grad():
+        model.lm_head.weight[hf.mask_token_id] = model.lm_head.weight[0]
+    model.fuse_projections()
+    rng = random.Random(4)
+    A, G, T = 600, 64, 32
+    affix = [1 + rng.randrange(5000) for _ in range(A)]
+    reqs = []
+    for i in range(5):
+        head = [1 + rng.randrange(5000) for _ in range(rng.randint(3, 120))]
+        tail = [1 + rng.randrange(5000) for _ in range(rng.randint(3, 120))]
+        if i % 3 == 0:
+            reqs.append(dict(prompt=affix + tail, a0=0, g0=None))
+        elif i % 3 == 1:
+            reqs.append(dict(prompt=head + affix + tail, a0=len(head), g0=None))
+        else:
+            reqs.append(dict(prompt=head + [hf.mask_token_id] * G + affix, a0=len(head) + G, g0=len(head)))
+
+    def run(dkv):
+        cfg = Config(hf_config=hf, mask_id=hf.mask_token_id, recompute_batch_size=2, max_num_seqs=3, gen_length=G,
+                     block_length=T, threshold=0.9, cache_block_size=256, num_kvcache_blocks=40, enable_acache=True,
+                     anchor_ratio=0.2, selection_mode="top", model_type="dream", enable_dkv_cache=dkv, dkv_steps=16,
+                     dkv_cache_interval=4)
+        runner = ModelRunner(model, cfg)
+        seqs = [Sequence(r["prompt"], block_length=T, gen_length=G, cache_block_size=256, mask_id=hf.mask_token_id,
+                         prompt_affix_start=r["a0"], prompt_affix_end=r["a0"] + A, generation_start=r["g0"]) for r in reqs]
+        outs, nfe = (runner.generate_with_dkv_acache if dkv else runner.generate_with_acache)(seqs)
+        return outs, nfe, [s.anchor_positions for s in seqs]
+
+    for dkv in (False, True):
+        outs, nfe, anchors = run(dkv)
+        _lib.check_device_errors()
+        assert all(len(o) == G and hf.mask_token_id not in o for o in outs)
+        assert all(len(a) == 120 and r["a0"] <= a[0] and a[-1] < r["a0"] + A for a, r in zip(anchors, reqs))
+        assert run(dkv) == (outs, nfe, anchors)
+        if dkv:
+            assert nfe == 16 * len(reqs)
+
+
 def test_reuse_with_every_affix_token_an_anchor_equals_no_reuse_baseline(hf_llada):
     """reference: nano-vdllm/tests/test_model_runner_acache.py:597-687 (ratio 1.0 recomputes
     the whole affix, so the logits equal the full-recompute baseline)."""
