@@ -182,14 +182,27 @@ class _DecodeGraph:
         self.launches = 0
         self.pending_work = None   # work units of a replay whose event times were not read yet
         self.stamp = None
+        self.eager = False         # set when a capture failed: this object then only forwards eagerly
 
     def run(self, runner, block_tokens, positions):
         self.tokens.copy_(block_tokens)
         timers = _lib.kernel_timers_enabled()
         for rope in runner._rope_caches:      # the table the capture will see (and later eager forwards keep)
             rope.get(self.max_pos, runner.device)
-        if self.graph is None or (timers and not self.with_timers) or self.stamp != runner._graph_stamp():
-            self._capture(runner, positions, timers)
+        if not self.eager and (self.graph is None or (timers and not self.with_timers)
+                               or self.stamp != runner._graph_stamp()):
+            try:
+                self._capture(runner, positions, timers)
+            except RuntimeError as exc:
+                # a capture that the installed stack refuses: keep serving, eagerly, and say so once
+                import warnings
+
+                warnings.warn(f"CUDA-graph capture of the decode forward failed ({exc}); continuing without graphs")
+                self.graph, self.eager = None, True
+                runner.config.use_cuda_graphs = False
+        if self.eager:
+            out = runner._forward_model(self.tokens, positions, max_pos=self.max_pos).logits
+            return runner._dream_decode_logits(out)
         runner.harvest_graph_timers()
         self.graph.replay()
         _lib.LAUNCHES += self.launches
