@@ -36,11 +36,11 @@ _SIGNATURES = {
     "acache_anchor_importance_scratch_bytes": (c_int64, [c_int, c_int, c_int]),
     "acache_anchor_importance": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                          c_int64, c_int, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_float,
-                                         c_void_p, c_void_p, c_int64, c_void_p]),
+                                         c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "acache_anchor_importance_static_scratch_bytes": (c_int64, []),
     "acache_anchor_importance_static": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                                 c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_int64, c_int,
-                                                c_int, c_float, c_void_p, c_void_p]),
+                                                c_int, c_float, c_void_p, c_void_p, c_void_p]),
     "acache_attention": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int,
                                  c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_int,
                                  c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
@@ -223,6 +223,13 @@ def err_flag(device: torch.device) -> torch.Tensor:
             flag = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
         _err_flags[idx] = flag
     return flag
+
+
+def existing_err_flag(device: torch.device):
+    """The device's error flag if some earlier call already made it, else None; for callers
+    that must not cause an allocation themselves."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    return _err_flags.get(idx)
 
 
 _ERR_TEXT = {1: "slot outside the cache", 2: "position outside the RoPE table", 3: "read slot outside the cache",

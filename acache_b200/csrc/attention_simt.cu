@@ -8,6 +8,8 @@
 // relocation) while being staged in shared memory as fp32.  Thread (i, g) with
 // i = tid/4, g = tid%4 owns score columns g*8..g*8+7 of query row i and output
 // dimensions g, g+4, g+8, ...
+#include <atomic>
+
 #include "common.cuh"
 
 namespace acache {
@@ -417,7 +419,8 @@ int attention_simt_dispatch(const AttnArgs& a, int dtype, int rope_dtype) {
 int importance_tc_dispatch(const void* q, int64_t q_stride, const int32_t* q_rows, int n_q, int n_heads, int n_kv_heads,
                            int head_dim, int dtype, const void* affix_k, int64_t k_slot_stride, int affix_len,
                            int affix_shift, const void* rope_cos, const void* rope_sin, int64_t rope_stride,
-                           int rope_dtype, float scale, float* partial, int* n_partials, float* ml, cudaStream_t st);
+                           int rope_dtype, float scale, float* partial, int* n_partials, float* ml, int32_t* err_flag,
+                           cudaStream_t st);
 int64_t importance_tc_ml_floats(int n_q_rows, int n_heads, int affix_len);
 
 // implemented in attention_tc.cu: returns ACACHE_EUNSUPPORTED when it declines the shape
@@ -539,7 +542,7 @@ extern "C" int acache_anchor_importance(const void* q, int64_t q_stride, const i
                                         int64_t k_slot_stride, int affix_len, int affix_shift, const void* rope_cos,
                                         const void* rope_sin, int64_t rope_row_stride, int rope_rows, int rope_dtype,
                                         float scale, float* importance, void* scratch, int64_t scratch_bytes,
-                                        void* stream) {
+                                        int32_t* err_flag, void* stream) {
   if (!dtype_ok(dtype) || !dtype_ok(rope_dtype)) return ACACHE_EINVAL;
   if (n_q_rows < 0 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || head_dim <= 0 || affix_len < 0)
     return ACACHE_EINVAL;
@@ -558,7 +561,8 @@ extern "C" int acache_anchor_importance(const void* q, int64_t q_stride, const i
     const int rc = importance_tc_dispatch(q, q_stride, q_rows, n_q_rows, n_heads, n_kv_heads, head_dim, dtype, affix_k,
                                           k_slot_stride, affix_len, affix_shift, rope_cos, rope_sin, rope_row_stride,
                                           rope_dtype, scale, (float*)scratch, &n_partials,
-                                          (float*)scratch + importance_partial_floats(n_q_rows, n_heads, affix_len), st);
+                                          (float*)scratch + importance_partial_floats(n_q_rows, n_heads, affix_len), err_flag,
+                                          st);
     if (rc == ACACHE_OK) {
       importance_reduce_kernel<<<(affix_len + 255) / 256, 256, 0, st>>>((const float*)scratch, n_partials, affix_len,
                                                                         importance);
@@ -597,8 +601,10 @@ static __device__ __align__(256) float g_importance_scratch[kStaticScratchFloats
 // In host code `g_importance_scratch` is only a handle for the runtime, not an address a
 // kernel can use; the device address is looked up once per device, with that device
 // current, and kept here.
+// The cache assumes that the device's primary context lives as long as the process (after a
+// cudaDeviceReset the array has a new address and this entry would be stale).
 constexpr int kMaxDevices = 64;
-static float* g_scratch_addr[kMaxDevices] = {};
+static std::atomic<float*> g_scratch_addr[kMaxDevices];
 }  // namespace acache
 
 extern "C" int64_t acache_anchor_importance_static_scratch_bytes(void) {
@@ -610,7 +616,7 @@ extern "C" int acache_anchor_importance_static(const void* q, int64_t q_stride, 
                                                const void* affix_k, int64_t k_slot_stride, int affix_len,
                                                int affix_shift, const void* rope_cos, const void* rope_sin,
                                                int64_t rope_row_stride, int rope_rows, int rope_dtype, float scale,
-                                               float* importance, void* stream) {
+                                               float* importance, int32_t* err_flag, void* stream) {
   // sizes first: a request that needs more partial-sum space than the fixed array holds is
   // refused here, before anything touches the device
   const int64_t need = acache_anchor_importance_scratch_bytes(n_q_rows, n_heads, affix_len);
@@ -618,15 +624,21 @@ extern "C" int acache_anchor_importance_static(const void* q, int64_t q_stride, 
   int dev = -1;
   ACACHE_CUDA_CHECK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return ACACHE_ELIMIT;
-  if (g_scratch_addr[dev] == nullptr) {
-    // first call on this device: resolve the array's device address (no allocation happens;
-    // do this first call outside of any stream capture)
+  float* addr = g_scratch_addr[dev].load(std::memory_order_acquire);
+  if (addr == nullptr) {
+    // first call on this device: resolve the array's device address (no allocation happens).
+    // The look-up is not a stream operation, so it is refused while the stream is capturing
+    // instead of invalidating the capture: make the first call on a device before capturing.
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    ACACHE_CUDA_CHECK(cudaStreamIsCapturing((cudaStream_t)stream, &capturing));
+    if (capturing != cudaStreamCaptureStatusNone) return ACACHE_EUNSUPPORTED;
     float* p = nullptr;
     ACACHE_CUDA_CHECK(cudaGetSymbolAddress((void**)&p, g_importance_scratch));
     if (p == nullptr) return ACACHE_ECUDA;
-    g_scratch_addr[dev] = p;
+    g_scratch_addr[dev].store(p, std::memory_order_release);   // every thread resolves the same address
+    addr = p;
   }
   return acache_anchor_importance(q, q_stride, q_rows, n_q_rows, n_heads, n_kv_heads, head_dim, dtype, affix_k,
                                   k_slot_stride, affix_len, affix_shift, rope_cos, rope_sin, rope_row_stride,
-                                  rope_rows, rope_dtype, scale, importance, g_scratch_addr[dev], need, stream);
+                                  rope_rows, rope_dtype, scale, importance, addr, need, err_flag, stream);
 }

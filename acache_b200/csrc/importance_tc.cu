@@ -286,17 +286,18 @@ int64_t importance_tc_ml_floats(int n_q_rows, int n_heads, int affix_len) {
 int importance_tc_dispatch(const void* q, int64_t q_stride, const int32_t* q_rows, int n_q, int n_heads, int n_kv_heads,
                            int head_dim, int dtype, const void* affix_k, int64_t k_slot_stride, int affix_len,
                            int affix_shift, const void* rope_cos, const void* rope_sin, int64_t rope_stride,
-                           int rope_dtype, float scale, float* partial, int* n_partials, float* ml, cudaStream_t st) {
+                           int rope_dtype, float scale, float* partial, int* n_partials, float* ml, int32_t* err_flag,
+                           cudaStream_t st) {
   if (dtype == ACACHE_F32 || (head_dim != 64 && head_dim != 128)) return ACACHE_EUNSUPPORTED;
   if (!aligned16(q) || !aligned16(affix_k) || q_stride % 8 != 0 || k_slot_stride % 8 != 0) return ACACHE_EUNSUPPORTED;
 #define IMP_TC(T, TR)                                                                                                  \
   return head_dim == 128                                                                                               \
              ? tc::launch_importance_tc<T, TR, 128>(q, q_stride, q_rows, n_q, n_heads, n_kv_heads, affix_k,            \
                                                     k_slot_stride, affix_len, affix_shift, rope_cos, rope_sin,         \
-                                                    rope_stride, scale, partial, n_partials, ml, nullptr, st)              \
+                                                    rope_stride, scale, partial, n_partials, ml, err_flag, st)             \
              : tc::launch_importance_tc<T, TR, 64>(q, q_stride, q_rows, n_q, n_heads, n_kv_heads, affix_k,             \
                                                    k_slot_stride, affix_len, affix_shift, rope_cos, rope_sin,          \
-                                                   rope_stride, scale, partial, n_partials, ml, nullptr, st)
+                                                   rope_stride, scale, partial, n_partials, ml, err_flag, st)
   if (dtype == ACACHE_BF16) {
     if (rope_dtype == ACACHE_F32) { IMP_TC(__nv_bfloat16, float); }
     if (rope_dtype == ACACHE_BF16) { IMP_TC(__nv_bfloat16, __nv_bfloat16); }

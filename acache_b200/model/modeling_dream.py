@@ -65,8 +65,8 @@ class DreamSdpaAttention(nn.Module):
         cos, sin = self.rotary_emb.get(max_pos, x.device)
         ctx = get_context()
         attn = self.attn
-        if self._qkv_w is None:
-            self.fuse_qkv()
+        if self._qkv_w is None or self._qkv_w.data_ptr() != self.q_proj.weight.data_ptr():
+            self.fuse_qkv()      # first use, or the parameters were replaced since (load, cast, move)
         q, k, v = project_qkv(x, self._qkv_w, self._qkv_b, nh, hkv, D, position_ids, cos, sin, attn, ctx)
         o = attn(q, k, v).reshape(n, nh * D)
         attn.kv_already_stored = False

@@ -23,6 +23,7 @@ from __future__ import annotations
 import gc
 import time
 from contextlib import contextmanager
+from itertools import islice
 
 import numpy as np
 import torch
@@ -32,6 +33,7 @@ from .block_manager import BlockManager
 from .model import acache_attention as aa
 from .model.acache_attention import materialize_relocated_affix
 from .model.modeling_common import build_rope_table
+from .scheduler import admissible_prefix
 from .sequence import Sequence
 from .dkv import DkvMixin
 from .utils import add_gumbel_noise, get_context, reset_context, set_context
@@ -529,6 +531,7 @@ class ModelRunner(DkvMixin):
         for local, pos in enumerate(range(seq.affix_start, seq.affix_end)):
             if lo <= rsm[pos] < hi:
                 rsm[pos] = base + local
+        seq._read_runs = None   # the map was edited in place: the cached run layout is stale
         seq.relocated_affix_materialized = True
         self._finish_timing(self._active_timing, "affix_materialize", t0)
 
@@ -818,16 +821,9 @@ class ModelRunner(DkvMixin):
     def _collect_admissible_sequences(self, prompts, next_prompt_idx, current_batch_size, max_num_seqs):
         """FIFO admission by free blocks and running-set size; stops at the first
         request that does not fit (reference: model_runner.py:960-976)."""
-        picked = []
-        budget = len(self.block_manager.free_block_ids)
-        while next_prompt_idx < len(prompts) and current_batch_size + len(picked) < max_num_seqs:
-            seq = prompts[next_prompt_idx]
-            if seq.num_cache_blocks > budget:
-                break
-            picked.append(seq)
-            budget -= seq.num_cache_blocks
-            next_prompt_idx += 1
-        return picked, next_prompt_idx
+        picked = admissible_prefix(islice(prompts, next_prompt_idx, None), current_batch_size, max_num_seqs,
+                                   len(self.block_manager.free_block_ids))
+        return picked, next_prompt_idx + len(picked)
 
     def _admit_sequences_with_acache(self, batched_prompts, new_prompts, prefix_token_ids, allow_kv_cache_resize):
         if not new_prompts:
@@ -999,7 +995,11 @@ class ModelRunner(DkvMixin):
                 # read-map capacity and RoPE table length: powers of two with head-room
                 cap = 1 << int(2 * arrays["read"].size - 1).bit_length()
                 max_pos = 1 << int(2 * int(k_lens.max()) - 1).bit_length()
+                graphs.pop(key, None)
                 graph = graphs[key] = _DecodeGraph(self, len(ps), {k: a.dtype for k, a in arrays.items()}, cap, max_pos)
+                self._evict_decode_graphs(graphs, keep=key)
+            else:
+                graphs[key] = graphs.pop(key)      # most recently used last
             if int(k_lens.max()) <= graph.max_pos:
                 staging, self._decode_graph = graph.staging, graph
         dev = staging.ship(**arrays)
@@ -1008,6 +1008,29 @@ class ModelRunner(DkvMixin):
                     dev["read"], dev.get("shared_lens"), dev.get("shifts"))
         get_context().group_shared_span = grouped
         return dev["positions"]
+
+    # Every captured decode forward keeps its own logits tensor ``[rows * block_length, vocab]`` alive
+    # (only intermediates are shared between graphs), so the set is bounded: at most this many
+    # graphs and this many bytes of logits; the least recently used ones are dropped and captured
+    # again if their row count comes back.  The bound stays inside ``acache_memory_reserve_gb``.
+    MAX_DECODE_GRAPHS = 8
+    MAX_DECODE_GRAPH_LOGITS_BYTES = 2 << 30
+
+    def _evict_decode_graphs(self, graphs, keep):
+        hf = self.config.hf_config
+        vocab = int(getattr(hf, "embedding_size", None) or getattr(hf, "vocab_size", 0) or 0)
+        row_bytes = self.config.block_length * vocab * self.kv_cache.element_size()
+        while len(graphs) > 1:
+            total = sum(g.tokens.shape[0] * row_bytes for g in graphs.values())
+            if len(graphs) <= self.MAX_DECODE_GRAPHS and total <= self.MAX_DECODE_GRAPH_LOGITS_BYTES:
+                break
+            oldest = next(k for k in graphs if k != keep)
+            victim = graphs.pop(oldest)
+            if self._graph_with_pending_timers is victim:
+                self.harvest_graph_timers()
+            if self._decode_graph is victim:
+                self._decode_graph = None
+            victim.graph = victim.logits = None
 
     def _graph_stamp(self):
         """What a captured forward has baked in besides its own buffers: the cache, the RoPE

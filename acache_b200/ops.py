@@ -61,7 +61,7 @@ def anchor_importance(q, q_rows, affix_k, affix_shift: int, rope_cos, rope_sin, 
     check(lib.acache_anchor_importance(
         ptr(q), q.stride(0), ptr(q_rows), n_q, nh, hkv, D, dtype_code(q.dtype), ptr(affix_k), affix_k.stride(0), A,
         int(affix_shift), rc, rs, rstride, rrows, rdt, float(scale), ptr(importance), ptr(scratch), scratch.numel(),
-        stream_ptr()), "anchor_importance", 2)
+        ptr(_lib.err_flag(q.device)), stream_ptr()), "anchor_importance", 2)
 
 
 def anchor_importance_noalloc(q, q_rows, affix_k, affix_shift: int, rope_cos, rope_sin, scale: float, importance):
@@ -72,7 +72,9 @@ def anchor_importance_noalloc(q, q_rows, affix_k, affix_shift: int, rope_cos, ro
     this wrapper itself creates no tensor.  Raises ``OverflowError`` when
     ``ceil(n_q / 32) * n_heads * affix_len`` floats do not fit that array.  Calls share the
     array: do not let two of them overlap on different streams.  The first call on a device
-    resolves the array's address and should be made before any stream capture."""
+    resolves the array's address and must be made before any stream capture (inside one it raises
+    ``NotImplementedError``).  A kernel-side failure is reported through the device's error flag
+    only if an earlier operator call has already created that flag."""
     assert q.is_cuda and q.dim() == 3 and q.stride(2) == 1 and q.stride(1) == q.shape[2]
     assert q_rows.dtype == torch.int32 and q_rows.is_cuda
     assert affix_k.dim() == 3 and affix_k.stride(2) == 1 and affix_k.stride(1) == affix_k.shape[2]
@@ -87,8 +89,8 @@ def anchor_importance_noalloc(q, q_rows, affix_k, affix_shift: int, rope_cos, ro
         rc, rs, rstride, rrows, rdt = None, None, 0, 0, _lib.F32
     check(_lib.load().acache_anchor_importance_static(
         ptr(q), q.stride(0), ptr(q_rows), n_q, nh, hkv, D, dtype_code(q.dtype), ptr(affix_k), affix_k.stride(0), A,
-        int(affix_shift), rc, rs, rstride, rrows, rdt, float(scale), ptr(importance), stream_ptr()),
-        "anchor_importance_static", 2)
+        int(affix_shift), rc, rs, rstride, rrows, rdt, float(scale), ptr(importance),
+        ptr(_lib.existing_err_flag(q.device)), stream_ptr()), "anchor_importance_static", 2)
 
 
 def rope_store(q, k, v, positions, rope_cos, rope_sin, k_cache=None, v_cache=None, slot_mapping=None):

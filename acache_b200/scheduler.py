@@ -5,7 +5,8 @@ autoregressive engine (reference: nano-vdllm/scheduler.py:8-71: ``add``,
 ``schedule``, ``is_finished``, ``preempt``, ``postprocess``); its engine does
 the actual admission inline (reference: nano-vdllm/model_runner.py:960-1003).
 This class keeps the interface and implements the engine's admission rule
-behind it, so both the class and the engine share one code path:
+behind it; the rule itself is ``admissible_prefix`` below, which the engine's own
+admission (``ModelRunner._collect_admissible_sequences``) calls too:
 
 * requests wait in FIFO order,
 * a request is admitted while the running set is below ``max_num_seqs``
@@ -21,6 +22,19 @@ from collections import deque
 from .block_manager import BlockManager
 from .config import Config
 from .sequence import Sequence, SequenceStatus
+
+
+def admissible_prefix(waiting, n_running: int, max_num_seqs: int, free_blocks: int) -> list[Sequence]:
+    """Longest FIFO prefix of ``waiting`` that fits: the running set stays below
+    ``max_num_seqs`` and every picked request finds ``num_cache_blocks`` free blocks; stops at
+    the first request that does not fit (reference: nano-vdllm/model_runner.py:960-976)."""
+    picked = []
+    for seq in waiting:
+        if n_running + len(picked) >= max_num_seqs or seq.num_cache_blocks > free_blocks:
+            break
+        picked.append(seq)
+        free_blocks -= seq.num_cache_blocks
+    return picked
 
 
 class Scheduler:
@@ -44,13 +58,7 @@ class Scheduler:
         the running-set limit; nothing is allocated or dequeued."""
         budget = len(self.block_manager.free_block_ids) if free_blocks is None else free_blocks
         limit = self.max_num_seqs if self.max_num_seqs > 0 else len(self.running) + len(self.waiting)
-        picked = []
-        for seq in self.waiting:
-            if len(self.running) + len(picked) >= limit or seq.num_cache_blocks > budget:
-                break
-            picked.append(seq)
-            budget -= seq.num_cache_blocks
-        return picked
+        return admissible_prefix(self.waiting, len(self.running), limit, budget)
 
     def schedule(self) -> tuple[list[Sequence], bool]:
         """Returns ``(seqs, is_refresh)``: newly admitted requests (they need a

@@ -240,8 +240,5 @@ class Sequence:
         first = self.generation_start + self.current_block_idx * self.block_length
         return self.recompute_positions.index(first)
 
-    def __getstate__(self):
-        return (self.num_tokens, self.num_prompt_tokens, self.block_table)
-
-    def __setstate__(self, state):
-        self.num_tokens, self.num_prompt_tokens, self.block_table, self.token_ids = state
+    # Pickling uses the default protocol (the whole attribute dict): a request that crosses a
+    # process boundary arrives with its tokens, spans and slot layout intact.

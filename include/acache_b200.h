@@ -130,13 +130,16 @@ ACACHE_API int acache_anchor_topk(const float* scores, int n_rows, int n_cols, i
  * q: [*, n_heads, head_dim] post-RoPE, rows q_stride apart; q_rows: device int32[n_q_rows]
  * row indices (the mask-token rows).  Deterministic: per-CTA partial sums go to `scratch`
  * and are reduced in a fixed order.  scratch must hold acache_anchor_importance_scratch_bytes()
- * bytes; contents on entry are irrelevant. */
+ * bytes; contents on entry are irrelevant.  err_flag (device int32, may be NULL) receives a
+ * non-zero code when a wait inside the tensor-core kernel ran out (5) or its shared memory
+ * was misplaced (6); the scores are then not valid. */
 ACACHE_API int64_t acache_anchor_importance_scratch_bytes(int n_q_rows, int n_heads, int affix_len);
 ACACHE_API int acache_anchor_importance(const void* q, int64_t q_stride, const int32_t* q_rows, int n_q_rows, int n_heads,
                              int n_kv_heads, int head_dim, int dtype, const void* affix_k, int64_t k_slot_stride,
                              int affix_len, int affix_shift, const void* rope_cos, const void* rope_sin,
                              int64_t rope_row_stride, int rope_rows, int rope_dtype, float scale,
-                             float* importance, void* scratch, int64_t scratch_bytes, void* stream);
+                             float* importance, void* scratch, int64_t scratch_bytes, int32_t* err_flag,
+                             void* stream);
 
 /* The same computation for callers that cannot provide scratch memory and must not cause an
  * allocation: hosts that have given the whole device to their own memory arena, plugins that
@@ -148,7 +151,9 @@ ACACHE_API int acache_anchor_importance(const void* q, int64_t q_stride, const i
  * acache_anchor_importance_scratch_bytes(n_q_rows, n_heads, affix_len) exceeds that returns
  * ACACHE_ELIMIT and does nothing.  Neither this call nor anything it calls allocates or frees
  * memory.  The first call on a device looks the array's device address up (once per device,
- * for the device current at that time); make that first call before any stream capture.
+ * for the device current at that time, assuming the device's primary context lives as long as
+ * the process); make that first call before any stream capture - a first call on a capturing
+ * stream returns ACACHE_EUNSUPPORTED and does nothing.
  * All calls on a device share the one array and it keeps whatever the last call left in it:
  * nothing in it needs clearing between calls (every entry that is read was written by the same
  * call), but two calls whose kernels overlap on the GPU (different streams) race on it -
@@ -159,7 +164,7 @@ ACACHE_API int acache_anchor_importance_static(const void* q, int64_t q_stride, 
                                                const void* affix_k, int64_t k_slot_stride, int affix_len,
                                                int affix_shift, const void* rope_cos, const void* rope_sin,
                                                int64_t rope_row_stride, int rope_rows, int rope_dtype, float scale,
-                                               float* importance, void* stream);
+                                               float* importance, int32_t* err_flag, void* stream);
 
 /* ------------------------------------------------------------------ varlen attention, slot map
  * Replaces acache_attention (nano-vdllm/model/acache_attention.py:338-514,643-738):

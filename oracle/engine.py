@@ -68,18 +68,24 @@ def select_anchors(model, affix_kv, tokens, affix_start, affix_end, anchor_ratio
     return (idx + affix_start).tolist(), acc
 
 
-def generate_request(model, affix_kv, tokens, affix_start, affix_end, generation_start, gen_length, block_length,
-                     anchors, threshold=0.9, trace=None):
-    """Denoise one request.  ``tokens`` already contains the mask span.
-    Returns (tokens list, nfe)."""
+def request_steps(model, affix_kv, tokens, affix_start, affix_end, generation_start, gen_length, block_length,
+                  anchors, threshold=0.9, kv_out=None):
+    """Generator over the forwards of one request, in order.  Yields
+    ``(phase, block index, logits [block_length, vocab], block tokens after the commit)`` with
+    phase 'refresh' (forward over anchors + own tokens, reference: model_runner.py:2091-2118) or
+    'decode' (forward over the working block, reference: model_runner.py:2196-2271).  The
+    logits are the ones unmasking sees (Dream's already shifted).  ``kv_out``: a list that
+    receives the request's dense logical cache and the row set of the refresh, for callers
+    that compare cache contents."""
     spec = model.spec
     n = len(tokens)
     x = torch.tensor(tokens, dtype=torch.long)
     kv = _request_kv(model, affix_kv, n, affix_start)
     anchors = sorted(anchors)
     rows = torch.tensor(sorted(set(anchors) | set(range(affix_start)) | set(range(affix_end, n))), dtype=torch.long)
+    if kv_out is not None:
+        kv_out.extend([kv, rows])
     row_of = {int(p): i for i, p in enumerate(rows.tolist())}
-    nfe = 0
     for b in range(-(-gen_length // block_length)):
         s = generation_start + b * block_length
         e = s + block_length
@@ -88,9 +94,6 @@ def generate_request(model, affix_kv, tokens, affix_start, affix_end, generation
         if spec.kind == "dream":
             keep = torch.clamp(keep, min=1) - 1  # logits of the preceding row (reference: model_runner.py:63-66)
         logits = model.forward_rows(x[rows], rows, kv, rows, logits_rows=keep)
-        nfe += 1
-        if trace is not None:
-            trace.append(("refresh", b, logits.clone()))
         blk = x[s:e].clone()
         if spec.kind == "dream":
             blk[0] = torch.argmax(logits[0])
@@ -98,18 +101,34 @@ def generate_request(model, affix_kv, tokens, affix_start, affix_end, generation
             x0, ti = get_transfer_index(logits[None], (blk == spec.mask_id)[None], blk[None], threshold)
             blk = torch.where(ti[0], x0[0], blk)
         x[s:e] = blk
+        yield "refresh", b, logits, x[s:e].clone()
         pos = torch.arange(s, e)
         while bool((x[s:e] == spec.mask_id).any()):
             logits = model.forward_rows(x[s:e], pos, kv, pos, logits_rows=torch.arange(block_length))
-            nfe += 1
             if spec.kind == "dream":
                 logits = torch.cat([logits[:1], logits[:-1]], dim=0)
-            if trace is not None:
-                trace.append(("decode", b, logits.clone()))
             blk = x[s:e].clone()
             x0, ti = get_transfer_index(logits[None], (blk == spec.mask_id)[None], blk[None], threshold)
             x[s:e] = torch.where(ti[0], x0[0], blk)
-    return x.tolist(), nfe
+            yield "decode", b, logits, x[s:e].clone()
+    if kv_out is not None:
+        kv_out.append(x.tolist())
+
+
+def generate_request(model, affix_kv, tokens, affix_start, affix_end, generation_start, gen_length, block_length,
+                     anchors, threshold=0.9, trace=None):
+    """Denoise one request.  ``tokens`` already contains the mask span.
+    Returns (tokens list, nfe)."""
+    x = list(tokens)
+    nfe = 0
+    for phase, b, logits, blk in request_steps(model, affix_kv, tokens, affix_start, affix_end, generation_start,
+                                               gen_length, block_length, anchors, threshold):
+        nfe += 1
+        if trace is not None:
+            trace.append((phase, b, logits.clone()))
+        s = generation_start + b * block_length
+        x[s: s + block_length] = blk.tolist()
+    return x, nfe
 
 
 def generate_with_acache(model, requests, anchor_ratio, selection_mode="top", threshold=0.9, block_length=32):

@@ -47,3 +47,32 @@ def test_static_staging_keeps_addresses_and_checks_capacity():
     assert not st.fits(**_arrays(3, 65))              # read map longer than the capacity
     assert not st.fits(**_arrays(3, 30, with_shifts=False))   # another set of arrays = another layout
     assert not st.fits(**_arrays(4, 40))              # more rows
+
+
+def test_decode_graph_cache_is_bounded():
+    """The set of captured decode forwards is bounded by count and by the bytes of logits they
+    keep alive; the least recently used ones go first and the newest always stays."""
+    from types import SimpleNamespace
+
+    import torch
+
+    from acache_b200.model_runner import ModelRunner
+
+    r = ModelRunner.__new__(ModelRunner)
+    r.config = SimpleNamespace(block_length=32, hf_config=SimpleNamespace(embedding_size=126464, vocab_size=126464))
+    r.kv_cache = torch.empty(1, dtype=torch.bfloat16)
+    r._graph_with_pending_timers = r._decode_graph = None
+    graph = lambda rows: SimpleNamespace(tokens=torch.empty(rows, 32), graph=object(), logits=object())
+    graphs = {}
+    for rows in range(1, 13):            # small graphs: the count bound applies
+        graphs[rows] = graph(rows)
+        r._evict_decode_graphs(graphs, keep=rows)
+    assert list(graphs) == list(range(5, 13))
+    big = {}
+    for rows in (64, 63, 62, 61, 60):    # 0.5 GB of logits each: the byte bound applies
+        big[rows] = graph(rows)
+        r._evict_decode_graphs(big, keep=rows)
+    assert list(big) == [63, 62, 61, 60]
+    lone = {64: graph(6400)}             # one oversized graph is still kept (it is the one in use)
+    r._evict_decode_graphs(lone, keep=64)
+    assert list(lone) == [64]

@@ -39,8 +39,8 @@ def test_static_scratch_variant_matches_the_allocating_entry_point_twice():
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
         args = (ptr(q), q.stride(0), ptr(rows), nq, nh, hkv, D, dtype_code(q.dtype), ptr(kc), kc.stride(0), A, shift,
                 ptr(cos), ptr(sin), cos.stride(0), cos.shape[0], dtype_code(cos.dtype), D ** -0.5)
-        check(lib.acache_anchor_importance(*args, ptr(want), ptr(scratch), nbytes, stream_ptr()), "importance")
-        check(lib.acache_anchor_importance_static(*args, ptr(got), stream_ptr()), "importance_static")
+        check(lib.acache_anchor_importance(*args, ptr(want), ptr(scratch), nbytes, None, stream_ptr()), "importance")
+        check(lib.acache_anchor_importance_static(*args, ptr(got), None, stream_ptr()), "importance_static")
         torch.cuda.synchronize()
         # same kernels, same summation order: the tolerance of the score tests is more than enough
         assert torch.allclose(got, want, rtol=2e-3, atol=1e-4)
@@ -61,7 +61,7 @@ def test_static_scratch_variant_refuses_oversized_requests():
     imp = torch.zeros(A, device=DEV)
     dummy = torch.zeros(16, device=DEV)
     rc = lib.acache_anchor_importance_static(ptr(dummy), 0, ptr(dummy), nq, nh, nh, 128, 2, ptr(dummy), 0, A, 0, None,
-                                             None, 0, 0, 0, 1.0, ptr(imp), None)
+                                             None, 0, 0, 0, 1.0, ptr(imp), None, None)
     assert rc == -4
     assert lib.acache_status_string(rc) == b"size beyond a fixed limit"
     assert float(imp.abs().sum()) == 0.0
