@@ -32,6 +32,17 @@ _SIGNATURES = {
     "acache_qkv_rope_scatter": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                         c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_int64,
                                         c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+    "acache_linear": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int64, c_int,
+                              c_int, c_void_p, c_void_p]),
+    "acache_linear_swiglu": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int64,
+                                     c_int, c_int, c_void_p, c_void_p]),
+    "acache_linear_qkv_rope_scatter": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                                               c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
+                                               c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
+                                               c_void_p]),
+    "acache_linear_argmax_scratch_bytes": (c_int64, [c_int, c_int]),
+    "acache_linear_argmax": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                     c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "acache_anchor_topk": (c_int, [c_void_p, c_int, c_int, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "acache_anchor_importance_scratch_bytes": (c_int64, [c_int, c_int, c_int]),
     "acache_anchor_importance": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
@@ -56,6 +67,7 @@ _SIGNATURES = {
     "acache_add_rmsnorm": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int,
                                    c_float, c_int, c_void_p]),
     "acache_act_mul": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "acache_apply_transfer": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_float, c_void_p]),
     "acache_transfer_tokens": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_int, c_int64, c_float,
                                        c_void_p, c_void_p, c_void_p]),
 }

@@ -1,0 +1,644 @@
+// Dense projections of the served models as tcgen05 GEMMs on CTA pairs, with the work that
+// follows each projection in the reference model fused into the epilogue:
+//
+//   acc[M, N] = X[M, K] . W[N, K]^T        (bf16 / fp16 in, fp32 accumulation in TMEM)
+//
+//   plain    out = acc (+ bias)                               output / down projections
+//   swiglu   out[:, j] = act(gate_j) * up_j                   gate and up projections in one GEMM
+//   qkv      bias, RoPE at the row's position, q to its buffer, k / v into the paged cache
+//   argmax   per row: arg-max, maximum and sum of exponentials over the N columns (output
+//            head + greedy unmasking statistics; the logits never reach global memory)
+//
+// Two CTAs of a cluster work as one: `tcgen05.mma.cta_group::2` multiplies a 256-row block of X
+// (128 rows staged by each CTA) with a BN-column block of W (BN/2 rows staged by each CTA), so a
+// W tile crosses L2 -> shared memory once per 256 rows, or once per 512 rows when a pair keeps
+// two row blocks (MB = 2).  Every CTA loads its own halves with plain TMA tile loads whose
+// completion is counted on the leader's mbarrier; nothing is multicast.  Per CTA (192 threads):
+//   warp 0      one thread issues the TMA loads of every k block into a ring of stages;
+//   warp 1      (leader CTA only) one thread issues the products of the pair into TMEM and
+//               commits them to the `stage free` barriers of both CTAs / the `accumulator ready`
+//               barriers of both CTAs;
+//   warps 2-5   epilogue: thread = accumulator row; reads TMEM 16 columns at a time.
+// The pair walks the tile list (row block fastest, so pairs that run together share W tiles in
+// L2); BN is chosen per launch so that the tiles fill whole waves of the 74 pairs, and with two
+// accumulator stages (when they fit the 512 TMEM columns) the epilogue of a tile overlaps the
+// products of the next.  All waits are bounded; a wait that runs out raises error code 5.
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace acache {
+namespace gemm {
+
+using namespace tc;
+
+constexpr int BK = 64, NT = 192;
+constexpr int A_SUB = 128 * BK * 2;      // one 128-row block of X for one k block: 16 KB
+constexpr int kPairs = kNumSMs / 2;
+constexpr int kMaxStages = 8;
+constexpr uint32_t kTmemCols = 512;
+
+enum { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_QKV = 2, EPI_ARGMAX = 3 };
+
+struct Params {
+  int M, N, K, MB, BN, stages, acc_stages;
+  // plain / swiglu
+  void* out; int64_t ldo; const void* bias; int act;
+  // qkv
+  int n_heads, n_kv_heads; const int64_t* positions; const void* rope_cos; const void* rope_sin; int64_t rope_stride;
+  int rope_rows; void* out_q; int64_t q_stride; void* k_cache; void* v_cache; const int32_t* slots; int64_t num_slots;
+  // argmax: per (column tile, row) partial maximum, its column and the sum of exp(x - maximum)
+  float* part_max; int32_t* part_arg; float* part_sum;
+  int32_t* err_flag;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load of this CTA's half of a pair's operand; the bytes are counted on `bar`, which
+// may be the mbarrier of the pair's other CTA
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void mma_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives (once the pair's earlier products have completed) on the mbarrier at this offset in
+// both CTAs of the pair
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+  const uint16_t both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(both) : "memory");
+}
+
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort) {
+  const long long t0 = clock64();
+  for (uint32_t it = 0;; ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+    if ((it & 63) == 63) {
+      if (*abort) return false;
+      if (clock64() - t0 > kWaitCycles) {
+        *abort = 1;
+        return false;
+      }
+      __nanosleep(32);
+    }
+  }
+}
+
+__device__ __forceinline__ float act_fn(float x, int act) {
+  if (act == 0) return x / (1.0f + __expf(-x));                 // silu
+  if (act == 1) return x > 0.f ? x : 0.f;                       // relu
+  return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));    // gelu (erf form)
+}
+
+template <typename TR> __device__ __forceinline__ void load8(const TR* p, float* o);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float* o) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<__half>(const __half* p, float* o) {
+  Vec16<__half> v;
+  v.u = *reinterpret_cast<const uint4*>(p);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i] = __half2float(v.e[i]);
+}
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float* o) {
+  Vec16<__nv_bfloat16> v;
+  v.u = *reinterpret_cast<const uint4*>(p);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i] = __bfloat162float(v.e[i]);
+}
+
+template <typename T>
+__device__ __forceinline__ uint4 pack8(const float* o) {
+  return make_uint4(pack2<T>(o[0], o[1]), pack2<T>(o[2], o[3]), pack2<T>(o[4], o[5]), pack2<T>(o[6], o[7]));
+}
+
+// ---- epilogues: one accumulator row (global row m, live = inside the matrix), 16 columns
+// starting at global column n, values v[0..15] --------------------------------------------
+template <typename T>
+__device__ __forceinline__ void epi_plain(const Params& p, int m, int n, const float* v) {
+  float o[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) o[i] = v[i];
+  if (p.bias) {
+    float b[16];
+    load8<T>((const T*)p.bias + n, b);
+    load8<T>((const T*)p.bias + n + 8, b + 8);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) o[i] += b[i];
+  }
+  T* dst = (T*)p.out + (int64_t)m * p.ldo + n;
+  *reinterpret_cast<uint4*>(dst) = pack8<T>(o);
+  *reinterpret_cast<uint4*>(dst + 8) = pack8<T>(o + 8);
+}
+
+// W rows are interleaved in groups of 8: columns n..n+7 are gate features n/2..n/2+7 and columns
+// n+8..n+15 the up features of the same indices; both projections are rounded to T first, the
+// activation is rounded to T, then the product, as the separate kernels do
+template <typename T>
+__device__ __forceinline__ void epi_swiglu(const Params& p, int m, int n, const float* v) {
+  float o[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float g = round_to<T>(v[i]), u = round_to<T>(v[8 + i]);
+    o[i] = round_to<T>(act_fn(g, p.act)) * u;
+  }
+  *reinterpret_cast<uint4*>((T*)p.out + (int64_t)m * p.ldo + (n >> 1)) = pack8<T>(o);
+}
+
+// W rows are interleaved inside every head in groups of 8: columns n..n+7 are features
+// d..d+7 and columns n+8..n+15 features d+64..d+71 of head n/128, d = (n % 128) / 2, so both
+// halves of a rotation pair sit in one thread
+template <typename T, typename TR, typename TC>
+__device__ __forceinline__ void epi_qkv(const Params& p, int m, int n, const float* v, int64_t pos, int slot) {
+  constexpr int D = 128;
+  const int head = n / D, d = (n % D) >> 1;
+  const int kind = head < p.n_heads ? 0 : (head < p.n_heads + p.n_kv_heads ? 1 : 2);
+  float x1[8], x2[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    x1[i] = v[i];
+    x2[i] = v[8 + i];
+  }
+  if (p.bias) {
+    float b[16];
+    load8<T>((const T*)p.bias + n, b);
+    load8<T>((const T*)p.bias + n + 8, b + 8);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      x1[i] += b[i];
+      x2[i] += b[8 + i];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {   // the projection's output in T, as an unfused GEMM leaves it
+    x1[i] = round_to<T>(x1[i]);
+    x2[i] = round_to<T>(x2[i]);
+  }
+  T* dst;
+  if (kind == 0) {
+    dst = (T*)p.out_q + (int64_t)m * p.q_stride + (int64_t)head * D + d;
+  } else {
+    if (slot < 0) return;
+    const int h = kind == 1 ? head - p.n_heads : head - p.n_heads - p.n_kv_heads;
+    dst = (T*)(kind == 1 ? p.k_cache : p.v_cache) + (int64_t)slot * p.n_kv_heads * D + (int64_t)h * D + d;
+  }
+  if (kind < 2) {
+    if (pos < 0) return;
+    const TR* cr = (const TR*)p.rope_cos + pos * p.rope_stride;
+    const TR* sr = (const TR*)p.rope_sin + pos * p.rope_stride;
+    float c1[8], s1[8], c2[8], s2[8], o1[8], o2[8];
+    load8<TR>(cr + d, c1);
+    load8<TR>(sr + d, s1);
+    load8<TR>(cr + d + 64, c2);
+    load8<TR>(sr + d + 64, s2);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      o1[i] = rot_lo<TC>(x1[i], x2[i], c1[i], s1[i]);
+      o2[i] = rot_hi<TC>(x1[i], x2[i], c2[i], s2[i]);
+    }
+    *reinterpret_cast<uint4*>(dst) = pack8<T>(o1);
+    *reinterpret_cast<uint4*>(dst + 64) = pack8<T>(o2);
+  } else {
+    *reinterpret_cast<uint4*>(dst) = pack8<T>(x1);
+    *reinterpret_cast<uint4*>(dst + 64) = pack8<T>(x2);
+  }
+}
+
+template <typename T, typename TR, typename TC, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NT, 1)
+linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                 const __grid_constant__ Params p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const int MB = p.MB, BN = p.BN, S = p.stages, AS = p.acc_stages;
+  const int b_bytes = (BN / 2) * BK * 2;
+  const int stage_bytes = MB * A_SUB + b_bytes;
+  uint8_t* ring = smem_raw;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)S * stage_bytes);
+  // [0, S) full (leader's are used), [S, 2S) empty, [2S, 2S+2) accumulator full, [2S+2, 2S+4) accumulator empty
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  auto bar = [&](int i) { return smem_u32(&bars[i]); };
+  const int FULL = 0, EMPTY = kMaxStages, ACC_FULL = 2 * kMaxStages, ACC_EMPTY = 2 * kMaxStages + 2;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const bool misplaced = (smem_u32(smem_raw) & 1023u) != 0;
+
+  const int rows_per_tile = 256 * MB;
+  const int m_tiles = (p.M + rows_per_tile - 1) / rows_per_tile;
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int total = m_tiles * n_tiles;
+  const int k_blocks = (p.K + BK - 1) / BK;
+  const int acc_cols = (BN + 31) & ~31;       // TMEM columns reserved per accumulator
+
+  if (tid == 0) {
+    for (int i = 0; i < S; ++i) {
+      mbar_init(bar(FULL + i), 1);
+      mbar_init(bar(EMPTY + i), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar(ACC_FULL + a), 1);
+      mbar_init(bar(ACC_EMPTY + a), 8);   // one arrival per epilogue warp of both CTAs
+    }
+    *abort_flag = misplaced ? 1 : 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();          // both CTAs' barriers exist before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (tid == 0 && (tmem_base & 0xFFFFu) != 0) *abort_flag = 1;   // the pair needs the same columns in both CTAs
+  __syncthreads();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0 && !*abort_flag) {
+      int it = 0;
+      bool ok = true;
+      for (int t = pair; t < total && ok; t += n_pairs) {
+        const int mt = t % m_tiles, nt = t / m_tiles;
+        const int m0 = mt * rows_per_tile + (int)rank * 128, n0 = nt * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
+          const int s = it % S;
+          if (it >= S) ok = wait_or_abort(bar(EMPTY + s), (uint32_t)(((it / S) - 1) & 1), abort_flag);
+          if (!ok) break;
+          if (rank == 0) mbar_expect_tx(bar(FULL + s), (uint32_t)(2 * stage_bytes));   // both CTAs' bytes
+          const uint32_t full = map_to_cta(bar(FULL + s), 0);
+          const uint32_t dst = smem_u32(ring) + s * stage_bytes;
+          for (int r = 0; r < MB; ++r) tma_load_2d_pair(dst + r * A_SUB, &tmap_x, full, kb * BK, m0 + r * 256);
+          tma_load_2d_pair(dst + MB * A_SUB, &tmap_w, full, kb * BK, n0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ product issuer (leader CTA)
+    if (lane == 0 && rank == 0 && !*abort_flag) {
+      const uint32_t idesc = make_idesc(Fmt<T>::id, 0, (uint32_t)BN, 256);
+      int it = 0, n = 0;
+      bool ok = true;
+      for (int t = pair; t < total && ok; t += n_pairs, ++n) {
+        const int acc = n % AS;
+        if (n >= AS) ok = wait_or_abort(bar(ACC_EMPTY + acc), (uint32_t)(((n / AS) - 1) & 1), abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
+          const int s = it % S;
+          ok = wait_or_abort(bar(FULL + s), (uint32_t)((it / S) & 1), abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a = smem_u32(ring) + s * stage_bytes, b = a + MB * A_SUB;
+#pragma unroll
+          for (int ks = 0; ks < BK / 16; ++ks) {
+            const uint64_t bd = make_desc(b + ks * 32, 16, 1024);
+            for (int r = 0; r < MB; ++r)
+              mma_ss_pair(tmem_base + (uint32_t)((acc * MB + r) * acc_cols), make_desc(a + r * A_SUB + ks * 32, 16, 1024),
+                          bd, idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+          }
+          mma_commit_pair(bar(EMPTY + s));              // the stage is free in both CTAs once these have read it
+        }
+        if (ok) mma_commit_pair(bar(ACC_FULL + acc));   // accumulator complete, in both CTAs
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (both CTAs)
+    const int quad = warp & 3;                    // TMEM lane quadrant this warp may access
+    const int row = quad * 32 + lane;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const uint32_t acc_empty0 = map_to_cta(bar(ACC_EMPTY), 0);
+    int n = 0;
+    bool ok = !*abort_flag;
+    for (int t = pair; t < total && ok; t += n_pairs, ++n) {
+      const int mt = t % m_tiles, nt = t / m_tiles;
+      const int acc = n % AS;
+      ok = wait_or_abort(bar(ACC_FULL + acc), (uint32_t)((n / AS) & 1), abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const int n0 = nt * BN;
+      const int cols = min(BN, p.N - n0);          // a multiple of 16
+      for (int r = 0; r < MB; ++r) {
+        const int m = mt * rows_per_tile + r * 256 + (int)rank * 128 + row;
+        const bool live = m < p.M;
+        const uint32_t t_acc = t_lane + (uint32_t)((acc * MB + r) * acc_cols);
+        int64_t pos = -1;
+        int slot = -1;
+        if (EPI == EPI_QKV && live) {
+          pos = p.positions[m];
+          if (pos < 0 || pos >= p.rope_rows) {
+            if (p.err_flag) atomicExch(p.err_flag, 2);
+            pos = -1;
+          }
+          slot = p.slots[m];
+          if (slot < -1 || slot >= p.num_slots) {
+            if (p.err_flag) atomicExch(p.err_flag, 1);
+            slot = -1;
+          }
+        }
+        float run_max = -INFINITY, run_sum = 0.f;
+        int run_arg = 0;
+#pragma unroll 1
+        for (int c = 0; c < cols; c += 32) {
+          uint32_t v0[16], v1[16];
+          const bool two = c + 16 < cols;
+          tmem_ld16(t_acc + c, v0);
+          if (two) tmem_ld16(t_acc + c + 16, v1);
+          tmem_wait_ld();
+          if (!live) continue;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            if (half == 1 && !two) break;
+            const float* v = reinterpret_cast<const float*>(half == 0 ? v0 : v1);
+            const int nn = n0 + c + half * 16;
+            if (EPI == EPI_PLAIN) epi_plain<T>(p, m, nn, v);
+            if (EPI == EPI_SWIGLU) epi_swiglu<T>(p, m, nn, v);
+            if (EPI == EPI_QKV) epi_qkv<T, TR, TC>(p, m, nn, v, pos, slot);
+            if (EPI == EPI_ARGMAX) {
+              // logits as the unfused projection leaves them (rounded to T); first maximum wins
+              float x[16], mx = -INFINITY;
+              int am = 0;
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                x[i] = round_to<T>(v[i]);
+                if (x[i] > mx) {
+                  mx = x[i];
+                  am = i;
+                }
+              }
+              if (mx > run_max) {
+                run_sum *= __expf(run_max - mx);
+                run_max = mx;
+                run_arg = nn + am;
+              }
+#pragma unroll
+              for (int i = 0; i < 16; ++i) run_sum += __expf(x[i] - run_max);
+            }
+          }
+        }
+        if (EPI == EPI_ARGMAX && live) {
+          const int64_t idx = (int64_t)nt * p.M + m;
+          p.part_max[idx] = run_max;
+          p.part_arg[idx] = run_arg;
+          p.part_sum[idx] = run_sum;
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty0 + (uint32_t)acc * 8u);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();          // the other CTA no longer reads this CTA's shared memory or barriers
+  if (tid == 0 && *abort_flag && p.err_flag) atomicExch(p.err_flag, misplaced ? 6 : 5);
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---- the second step of the fused output head: fold the per-tile statistics of every row and
+// apply threshold unmasking to the working blocks in place (same rule as the sampling kernel:
+// confidence = exp(max - logsumexp); commit where confidence >= threshold; a row of the block
+// that still has masks but committed nothing commits its most confident position) ------------
+__global__ void __launch_bounds__(128) argmax_fold_kernel(const float* __restrict__ part_max,
+                                                          const int32_t* __restrict__ part_arg,
+                                                          const float* __restrict__ part_sum, int n_tiles, int M,
+                                                          int64_t* __restrict__ x0, float* __restrict__ conf) {
+  const int m = blockIdx.x * blockDim.x + threadIdx.x;
+  if (m >= M) return;
+  float mx = -INFINITY, sum = 0.f;
+  int arg = 0;
+  for (int t = 0; t < n_tiles; ++t) {
+    const float pm = part_max[(int64_t)t * M + m], ps = part_sum[(int64_t)t * M + m];
+    if (pm > mx) {
+      sum = sum * __expf(mx - pm) + ps;
+      mx = pm;
+      arg = part_arg[(int64_t)t * M + m];
+    } else {
+      sum += ps * __expf(pm - mx);
+    }
+  }
+  x0[m] = arg;
+  conf[m] = 1.0f / sum;      // exp(max - logsumexp) = 1 / sum exp(x - max)
+}
+
+// ---------------------------------------------------------------------------------------- host
+struct Tile { int mb, bn, stages, acc_stages; size_t smem; };
+
+static Tile pick_tile(int M, int N, int want_mb, int want_bn, int bn_multiple) {
+  double best = 1e30;
+  Tile out{1, 128, 4, 2, 0};
+  for (int mb = 1; mb <= 2; ++mb) {
+    if (want_mb && mb != want_mb) continue;
+    if (!want_mb && mb == 2 && M <= 256) continue;
+    const int m_tiles = (M + 256 * mb - 1) / (256 * mb);
+    for (int bn = 256; bn >= 64; bn -= 16) {
+      if (want_bn && bn != want_bn) continue;
+      if (bn % bn_multiple != 0) continue;
+      const int acc_cols = (bn + 31) & ~31;
+      if (mb * acc_cols > 512) continue;
+      const int n_tiles = (N + bn - 1) / bn;
+      const long tiles = (long)m_tiles * n_tiles;
+      const long waves = (tiles + kPairs - 1) / kPairs;
+      const int acc_stages = 2 * mb * acc_cols <= 512 ? 2 : 1;
+      // time ~ waves x tile area; a tile whose epilogue is not hidden pays a little extra, and among
+      // equal costs fewer, larger tiles move fewer bytes from L2
+      double cost = (double)waves * mb * bn * (acc_stages == 1 ? 1.04 : 1.0) - 1e-3 * bn - 1e-2 * mb;
+      if (cost < best) {
+        best = cost;
+        const int stage_bytes = mb * A_SUB + (bn / 2) * BK * 2;
+        int stages = (int)((200 * 1024) / stage_bytes);
+        if (stages > kMaxStages) stages = kMaxStages;
+        out = Tile{mb, bn, stages, acc_stages, (size_t)stages * stage_bytes + 512};
+      }
+    }
+  }
+  return out;
+}
+
+template <typename T, typename TR, typename TC, int EPI>
+static int launch(const CUtensorMap& mx, const CUtensorMap& mw, const Params& p, const Tile& tile, cudaStream_t st) {
+  auto kern = linear_tc_kernel<T, TR, TC, EPI>;
+  ACACHE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile.smem));
+  const int m_tiles = (p.M + 256 * p.MB - 1) / (256 * p.MB), n_tiles = (p.N + p.BN - 1) / p.BN;
+  const long total = (long)m_tiles * n_tiles;
+  const int pairs = total < kPairs ? (int)total : kPairs;
+  kern<<<2 * pairs, NT, tile.smem, st>>>(mx, mw, p);
+  ACACHE_LAUNCH_CHECK();
+  return ACACHE_OK;
+}
+
+template <typename T, typename TR> struct PromoteG { using type = float; };
+template <> struct PromoteG<__half, __half> { using type = __half; };
+template <> struct PromoteG<__nv_bfloat16, __nv_bfloat16> { using type = __nv_bfloat16; };
+
+static int prepare(const void* x, int64_t ldx, const void* w, int M, int N, int K, int dtype, int tile_mb, int tile_bn,
+                   int bn_multiple, Params* p, Tile* tile, CUtensorMap* mx, CUtensorMap* mw) {
+  if (dtype != ACACHE_BF16 && dtype != ACACHE_F16) return ACACHE_EUNSUPPORTED;
+  if (M <= 0 || N <= 0 || K <= 0 || N % 16 != 0 || K % 8 != 0 || ldx % 8 != 0) return ACACHE_EUNSUPPORTED;
+  if (!aligned16(x) || !aligned16(w)) return ACACHE_EUNSUPPORTED;
+  if ((tile_mb != 0 && tile_mb != 1 && tile_mb != 2) || (tile_bn != 0 && (tile_bn % 16 != 0 || tile_bn < 32 || tile_bn > 256)))
+    return ACACHE_EINVAL;
+  *tile = pick_tile(M, N, tile_mb, tile_bn, bn_multiple);
+  if (tile->smem == 0) return ACACHE_EUNSUPPORTED;
+  p->M = M; p->N = N; p->K = K; p->MB = tile->mb; p->BN = tile->bn; p->stages = tile->stages;
+  p->acc_stages = tile->acc_stages;
+  if (!make_tensor_map_2d(mx, x, M, K, ldx, 128, dtype) || !make_tensor_map_2d(mw, w, N, K, K, tile->bn / 2, dtype))
+    return ACACHE_EUNSUPPORTED;
+  return ACACHE_OK;
+}
+
+}  // namespace gemm
+}  // namespace acache
+
+using namespace acache;
+
+extern "C" int acache_linear(const void* x, int64_t x_stride, int n_rows, int in_features, const void* weight,
+                             int out_features, const void* bias, int dtype, void* out, int64_t out_stride,
+                             int tile_mb, int tile_bn, int32_t* err_flag, void* stream) {
+  if (n_rows == 0) return ACACHE_OK;
+  if (!x || !weight || !out) return ACACHE_EINVAL;
+  gemm::Params p{};
+  gemm::Tile tile;
+  CUtensorMap mx, mw;
+  const int rc = gemm::prepare(x, x_stride, weight, n_rows, out_features, in_features, dtype, tile_mb, tile_bn, 16, &p,
+                               &tile, &mx, &mw);
+  if (rc != ACACHE_OK) return rc;
+  if (!aligned16(out) || out_stride % 8 != 0 || (bias && !aligned16(bias))) return ACACHE_EUNSUPPORTED;
+  p.out = out; p.ldo = out_stride; p.bias = bias; p.err_flag = err_flag;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == ACACHE_BF16) return gemm::launch<__nv_bfloat16, float, float, gemm::EPI_PLAIN>(mx, mw, p, tile, st);
+  return gemm::launch<__half, float, float, gemm::EPI_PLAIN>(mx, mw, p, tile, st);
+}
+
+extern "C" int acache_linear_swiglu(const void* x, int64_t x_stride, int n_rows, int in_features,
+                                    const void* weight_gate_up, int ffn_features, int act, int dtype, void* out,
+                                    int64_t out_stride, int tile_mb, int tile_bn, int32_t* err_flag, void* stream) {
+  if (n_rows == 0) return ACACHE_OK;
+  if (!x || !weight_gate_up || !out || act < 0 || act > 2) return ACACHE_EINVAL;
+  if (ffn_features % 8 != 0) return ACACHE_EUNSUPPORTED;
+  gemm::Params p{};
+  gemm::Tile tile;
+  CUtensorMap mx, mw;
+  const int rc = gemm::prepare(x, x_stride, weight_gate_up, n_rows, 2 * ffn_features, in_features, dtype, tile_mb,
+                               tile_bn, 16, &p, &tile, &mx, &mw);
+  if (rc != ACACHE_OK) return rc;
+  if (!aligned16(out) || out_stride % 8 != 0) return ACACHE_EUNSUPPORTED;
+  p.out = out; p.ldo = out_stride; p.act = act; p.err_flag = err_flag;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == ACACHE_BF16) return gemm::launch<__nv_bfloat16, float, float, gemm::EPI_SWIGLU>(mx, mw, p, tile, st);
+  return gemm::launch<__half, float, float, gemm::EPI_SWIGLU>(mx, mw, p, tile, st);
+}
+
+extern "C" int acache_linear_qkv_rope_scatter(const void* x, int64_t x_stride, int n_rows, int hidden,
+                                              const void* w_qkv_interleaved, const void* bias_interleaved, int n_heads,
+                                              int n_kv_heads, int head_dim, int dtype, const int64_t* positions,
+                                              const void* rope_cos, const void* rope_sin, int64_t rope_row_stride,
+                                              int rope_rows, int rope_dtype, void* out_q, int64_t q_stride,
+                                              void* k_cache, void* v_cache, const int32_t* slot_mapping,
+                                              int64_t num_slots, int tile_mb, int tile_bn, int32_t* err_flag,
+                                              void* stream) {
+  if (!dtype_ok(dtype) || !dtype_ok(rope_dtype) || n_rows < 0 || hidden <= 0 || n_heads <= 0 || n_kv_heads <= 0)
+    return ACACHE_EINVAL;
+  if (n_rows == 0) return ACACHE_OK;
+  if (!x || !w_qkv_interleaved || !positions || !rope_cos || !rope_sin || !out_q || !k_cache || !v_cache ||
+      !slot_mapping)
+    return ACACHE_EINVAL;
+  if (head_dim != 128) return ACACHE_EUNSUPPORTED;
+  gemm::Params p{};
+  gemm::Tile tile;
+  CUtensorMap mx, mw;
+  const int N = (n_heads + 2 * n_kv_heads) * head_dim;
+  const int rc = gemm::prepare(x, x_stride, w_qkv_interleaved, n_rows, N, hidden, dtype, tile_mb, tile_bn, 16, &p, &tile,
+                               &mx, &mw);
+  if (rc != ACACHE_OK) return rc;
+  const int re = dtype_bytes(rope_dtype);
+  if (!aligned16(out_q) || q_stride % 8 != 0 || !aligned16(k_cache) || !aligned16(v_cache) ||
+      (bias_interleaved && !aligned16(bias_interleaved)) || !aligned16(rope_cos) || !aligned16(rope_sin) ||
+      (rope_row_stride * re) % 16 != 0)
+    return ACACHE_EUNSUPPORTED;
+  p.bias = bias_interleaved; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.positions = positions;
+  p.rope_cos = rope_cos; p.rope_sin = rope_sin; p.rope_stride = rope_row_stride; p.rope_rows = rope_rows;
+  p.out_q = out_q; p.q_stride = q_stride; p.k_cache = k_cache; p.v_cache = v_cache; p.slots = slot_mapping;
+  p.num_slots = num_slots; p.err_flag = err_flag;
+  cudaStream_t st = (cudaStream_t)stream;
+#define QKV(T, TR) \
+  return gemm::launch<T, TR, typename gemm::PromoteG<T, TR>::type, gemm::EPI_QKV>(mx, mw, p, tile, st)
+  if (dtype == ACACHE_BF16) {
+    if (rope_dtype == ACACHE_F32) { QKV(__nv_bfloat16, float); }
+    if (rope_dtype == ACACHE_BF16) { QKV(__nv_bfloat16, __nv_bfloat16); }
+    QKV(__nv_bfloat16, __half);
+  }
+  if (rope_dtype == ACACHE_F32) { QKV(__half, float); }
+  if (rope_dtype == ACACHE_F16) { QKV(__half, __half); }
+  QKV(__half, __nv_bfloat16);
+#undef QKV
+}
+
+extern "C" int64_t acache_linear_argmax_scratch_bytes(int n_rows, int out_features) {
+  if (n_rows <= 0 || out_features <= 0) return 0;
+  const int64_t tiles = (out_features + 63) / 64;      // the smallest column tile bounds the tile count
+  return tiles * n_rows * 12;
+}
+
+extern "C" int acache_linear_argmax(const void* x, int64_t x_stride, int n_rows, int in_features, const void* weight,
+                                    int out_features, int dtype, int64_t* x0, float* confidence, void* scratch,
+                                    int64_t scratch_bytes, int tile_mb, int tile_bn, int32_t* err_flag, void* stream) {
+  if (n_rows == 0) return ACACHE_OK;
+  if (!x || !weight || !x0 || !confidence || !scratch) return ACACHE_EINVAL;
+  gemm::Params p{};
+  gemm::Tile tile;
+  CUtensorMap mx, mw;
+  const int rc = gemm::prepare(x, x_stride, weight, n_rows, out_features, in_features, dtype, tile_mb, tile_bn, 16, &p,
+                               &tile, &mx, &mw);
+  if (rc != ACACHE_OK) return rc;
+  const int64_t n_tiles = (out_features + tile.bn - 1) / tile.bn;
+  if (scratch_bytes < n_tiles * n_rows * 12) return ACACHE_EINVAL;
+  p.part_max = (float*)scratch;
+  p.part_arg = (int32_t*)((float*)scratch + n_tiles * n_rows);
+  p.part_sum = (float*)scratch + 2 * n_tiles * n_rows;
+  p.err_flag = err_flag;
+  cudaStream_t st = (cudaStream_t)stream;
+  int lrc;
+  if (dtype == ACACHE_BF16) lrc = gemm::launch<__nv_bfloat16, float, float, gemm::EPI_ARGMAX>(mx, mw, p, tile, st);
+  else lrc = gemm::launch<__half, float, float, gemm::EPI_ARGMAX>(mx, mw, p, tile, st);
+  if (lrc != ACACHE_OK) return lrc;
+  gemm::argmax_fold_kernel<<<(n_rows + 127) / 128, 128, 0, st>>>(p.part_max, p.part_arg, p.part_sum, (int)n_tiles,
+                                                                 n_rows, x0, confidence);
+  ACACHE_LAUNCH_CHECK();
+  return ACACHE_OK;
+}

@@ -133,3 +133,14 @@ extern "C" int acache_transfer_tokens(const void* logits, int64_t logits_stride,
   ACACHE_LAUNCH_CHECK();
   return ACACHE_OK;
 }
+
+extern "C" int acache_apply_transfer(int64_t* blocks, const int64_t* x0, const float* confidence, int n_rows,
+                                     int block_len, int64_t mask_id, float threshold, void* stream) {
+  if (n_rows < 0 || block_len <= 0) return ACACHE_EINVAL;
+  if (n_rows == 0) return ACACHE_OK;
+  if (!blocks || !x0 || !confidence) return ACACHE_EINVAL;
+  apply_transfer_kernel<<<(n_rows + 3) / 4, 128, 0, (cudaStream_t)stream>>>(blocks, x0, confidence, n_rows, block_len,
+                                                                             mask_id, threshold);
+  ACACHE_LAUNCH_CHECK();
+  return ACACHE_OK;
+}

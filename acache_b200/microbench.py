@@ -207,6 +207,55 @@ def case_qkv(n, hidden, nh, hkv, D, fused):
     return fn, dict(flops=2.0 * n * hidden * (nh + 2 * hkv) * D, bytes=2.0 * (nh + 2 * hkv) * D * hidden)
 
 
+def gemm_sweep(iters=10, shapes=None, tiles=None):
+    """Projection shapes of the served models: this package's CTA-pair GEMM at several tile
+    shapes against the library GEMM.  Back-to-back launches over 8 rotating weight copies (so the
+    weights come from HBM, as in a model), one event pair around ``8 * iters`` launches."""
+    import torch.nn.functional as F
+
+    shapes = shapes or [("qkv/gate/up decode", 512, 4096, 12288), ("attn_out decode", 512, 4096, 4096),
+                        ("ff_out decode", 512, 12288, 4096), ("gate+up decode", 512, 4096, 24576),
+                        ("qkv refresh", 2304, 4096, 12288), ("ff_out refresh", 2304, 12288, 4096),
+                        ("head decode", 512, 4096, 126464), ("qkv dream decode", 1024, 3584, 4608),
+                        ("ff_out dream decode", 1024, 18944, 3584)]
+    tiles = tiles or [(0, 0), (1, 256), (1, 176), (1, 128), (1, 112), (2, 256), (2, 176), (2, 128), (2, 112)]
+    _, tf, src = peaks()
+    for name, M, K, N in shapes:
+        copies = max(2, min(8, int((1 << 30) // (N * K * 2))))
+        x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+        ws = [torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * K ** -0.5 for _ in range(copies)]
+        flops = 2.0 * M * N * K
+
+        def timeit(fn):
+            for w in ws[:2]:
+                fn(w)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                for w in ws:
+                    fn(w)
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) * 1e-3 / (iters * copies)
+
+        t_lib = timeit(lambda w: F.linear(x, w))
+        print(f"{name:22s} M={M} K={K} N={N}  library {t_lib * 1e6:8.1f} us {flops / t_lib / 1e12:7.1f} TFLOP/s", flush=True)
+        for tile in tiles:
+            ops.GEMM_TILE = tile
+            try:
+                t = timeit(lambda w: ops.linear(x, w))
+                print(f"    tile {tile}: {t * 1e6:8.1f} us {flops / t / 1e12:7.1f} TFLOP/s  {t_lib / t:5.2f}x library"
+                      f"  {flops / t / 1e12 / tf:5.2f} of {src} burst peak", flush=True)
+            except (NotImplementedError, _lib.AcacheError) as exc:
+                print(f"    tile {tile}: {exc}", flush=True)
+            finally:
+                ops.GEMM_TILE = (0, 0)
+        del ws, x
+        torch.cuda.empty_cache()
+    _lib.check_device_errors()
+
+
 CASES = {
     # name: (builder, bound)
     "relocate_cfg1_fp32": (lambda: case_relocate(2, 512, 8, 128, 4, torch.float32, 1024), "hbm"),
@@ -278,7 +327,11 @@ def main(argv=None):
     ap.add_argument("names", nargs="*")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--gemm-sweep", action="store_true", help="projection GEMMs at several tile shapes against the library")
     args = ap.parse_args(argv)
+    if args.gemm_sweep:
+        gemm_sweep(args.iters)
+        return
     names = args.names or list(CASES)
     for n in names:
         if n not in CASES:

@@ -18,28 +18,79 @@ def build_rope_table(length: int, head_dim: int, theta: float, dtype: torch.dtyp
     return emb.cos().to(dtype).to(device), emb.sin().to(dtype).to(device)
 
 
-# The projection of q/k/v, the rotary embedding and the K/V scatter can run as one tcgen05 GEMM
-# with a fused epilogue (16-bit, head_dim 128).  Measured on B200 it is slower than the library
-# GEMM followed by the RoPE + scatter kernel (84 us against 54 us for 512 x 4096 x 12288: with
-# 128 x 128 tiles it is bound by L2 -> SM traffic), so it is off unless switched on here.
+# The dense projections of the model blocks run on this package's CTA-pair tcgen05 GEMMs
+# (``ops.linear*``: fused QKV + RoPE + cache scatter, output projection, gate/up projection with the
+# gated activation in the epilogue, down projection, output head) for 16-bit models whose shapes
+# the kernels take; False sends every projection to the library GEMM instead.
+OWN_GEMM = True
+
+# The older single-CTA form of the fused QKV projection (128 x 128 tiles); kept for comparison,
+# slower than both the CTA-pair kernel and the library GEMM + RoPE/scatter kernel.
 FUSED_QKV = False
 
 
-def project_qkv(h, w_qkv, b_qkv, n_heads, n_kv_heads, head_dim, position_ids, cos, sin, attn, ctx):
+def dense(x, weight, bias=None):
+    """An ``nn.Linear`` of the model blocks on 2-D activations."""
+    if OWN_GEMM and ops._gemm_ok(x, weight):
+        return ops.linear(x, weight, bias)
+    return torch.nn.functional.linear(x, weight, bias)
+
+
+class FusedProjections:
+    """Weights of one block in the layouts the fused projection kernels read: q/k/v rows
+    interleaved inside every head (``ops.interleave_heads``), gate and up rows interleaved with
+    each other (``ops.interleave_rows``).  These are copies (the parameters keep their natural
+    layout for state dicts); ``stale()`` tells when the parameters were replaced since."""
+
+    def __init__(self):
+        self.qkv_w = self.qkv_b = self.gate_up_w = None
+        self._stamp = None
+
+    @staticmethod
+    def _stamp_of(params):
+        return tuple((p.data_ptr(), p._version) for p in params if p is not None)
+
+    def stale(self, params):
+        return self._stamp != self._stamp_of(params)
+
+    def build(self, w_qkv, b_qkv, gate, up, head_dim, params):
+        usable = w_qkv.dtype in (torch.bfloat16, torch.float16) and w_qkv.is_cuda
+        self.qkv_w = self.qkv_b = self.gate_up_w = None
+        if usable and head_dim == 128:
+            self.qkv_w = ops.interleave_heads(w_qkv)
+            self.qkv_b = ops.interleave_heads(b_qkv) if b_qkv is not None else None
+        if usable and gate.shape[0] % 8 == 0:
+            self.gate_up_w = ops.interleave_rows(gate, up)
+        self._stamp = self._stamp_of(params)
+
+
+def gated_mlp_input(h, fused: FusedProjections, gate_proj, up_proj, act: str):
+    """``act(gate_proj(h)) * up_proj(h)``: one GEMM with the activation in its epilogue when the
+    interleaved weight exists, else two projections and the activation kernel."""
+    if OWN_GEMM and fused.gate_up_w is not None and gate_proj.bias is None and ops._gemm_ok(h, fused.gate_up_w):
+        return ops.linear_swiglu(h, fused.gate_up_w, act)
+    return ops.act_mul(dense(h, gate_proj.weight, gate_proj.bias), dense(h, up_proj.weight, up_proj.bias), act)
+
+
+def project_qkv(h, w_qkv, b_qkv, n_heads, n_kv_heads, head_dim, position_ids, cos, sin, attn, ctx, fused=None):
     """Returns ``(q, k, v)`` views for the attention call; with the fused path ``k``/``v`` are
     ``None`` because they only exist in the paged cache."""
-    import torch.nn.functional as F
-
     n = h.shape[0]
     D, nh, hkv = head_dim, n_heads, n_kv_heads
     caching = attn.k_cache.numel() > 0 and ctx.slot_mapping is not None
+    if (OWN_GEMM and caching and fused is not None and fused.qkv_w is not None and ops._gemm_ok(h, fused.qkv_w)
+            and cos.stride(0) * cos.element_size() % 16 == 0):
+        q = ops.linear_qkv_rope_scatter(h, fused.qkv_w, fused.qkv_b, nh, hkv, D, position_ids, cos, sin, attn.k_cache,
+                                        attn.v_cache, ctx.slot_mapping)
+        attn.kv_already_stored = True
+        return q, None, None
     if (FUSED_QKV and caching and D == 128 and h.dtype in (torch.bfloat16, torch.float16) and h.shape[1] % 64 == 0
             and h.stride(0) % 8 == 0):
         q = ops.qkv_rope_scatter(h, w_qkv, b_qkv, nh, hkv, D, position_ids, cos, sin, attn.k_cache, attn.v_cache,
                                  ctx.slot_mapping)
         attn.kv_already_stored = True
         return q, None, None
-    qkv = F.linear(h, w_qkv, b_qkv)
+    qkv = dense(h, w_qkv, b_qkv)
     q, k, v = qkv[:, : nh * D], qkv[:, nh * D: (nh + hkv) * D], qkv[:, (nh + hkv) * D:]
     q, k, v = q.view(n, nh, D), k.view(n, hkv, D), v.view(n, hkv, D)
     if caching:

@@ -17,7 +17,8 @@ from .. import ops
 from ..utils import get_context
 from .attention import Attention
 from .configuration import DreamConfig
-from .modeling_common import RMSNorm, RopeCache, project_qkv
+from . import modeling_common as mc
+from .modeling_common import FusedProjections, RMSNorm, RopeCache, dense, gated_mlp_input, project_qkv
 
 
 class DreamMLP(nn.Module):
@@ -28,9 +29,16 @@ class DreamMLP(nn.Module):
         self.up_proj = nn.Linear(config.hidden_size, config.intermediate_size, bias=False, **kw)
         self.down_proj = nn.Linear(config.intermediate_size, config.hidden_size, bias=False, **kw)
         self.act = config.hidden_act
+        self._fused = FusedProjections()
+
+    def _params(self):
+        return (self.gate_proj.weight, self.up_proj.weight)
 
     def forward(self, x):
-        return self.down_proj(ops.act_mul(self.gate_proj(x), self.up_proj(x), self.act))
+        if self._fused.stale(self._params()):
+            w = self.gate_proj.weight.data
+            self._fused.build(w, None, w, self.up_proj.weight.data, 0, self._params())
+        return dense(gated_mlp_input(x, self._fused, self.gate_proj, self.up_proj, self.act), self.down_proj.weight)
 
 
 class DreamSdpaAttention(nn.Module):
@@ -50,6 +58,11 @@ class DreamSdpaAttention(nn.Module):
         self.rotary_emb = rope
         self.attn = Attention(num_heads=self.num_heads, head_dim=self.head_dim, num_kv_heads=self.num_key_value_heads)
         self._qkv_w = self._qkv_b = None
+        self._fused = FusedProjections()
+
+    def _projection_params(self):
+        return (self.q_proj.weight, self.k_proj.weight, self.v_proj.weight, self.q_proj.bias, self.k_proj.bias,
+                self.v_proj.bias)
 
     def fuse_qkv(self):
         w = torch.cat([self.q_proj.weight.data, self.k_proj.weight.data, self.v_proj.weight.data], dim=0)
@@ -58,6 +71,11 @@ class DreamSdpaAttention(nn.Module):
         self.q_proj.weight.data, self.k_proj.weight.data, self.v_proj.weight.data = w[:d], w[d:d + kvd], w[d + kvd:]
         self.q_proj.bias.data, self.k_proj.bias.data, self.v_proj.bias.data = b[:d], b[d:d + kvd], b[d + kvd:]
         self._qkv_w, self._qkv_b = w, b
+        if w.dtype in (torch.bfloat16, torch.float16) and w.is_cuda and self.head_dim == 128:
+            self._fused.qkv_w, self._fused.qkv_b = ops.interleave_heads(w), ops.interleave_heads(b)
+        else:
+            self._fused.qkv_w = self._fused.qkv_b = None
+        self._fused._stamp = self._fused._stamp_of(self._projection_params())
 
     def forward(self, x, position_ids, max_pos):
         n = x.shape[0]
@@ -65,12 +83,13 @@ class DreamSdpaAttention(nn.Module):
         cos, sin = self.rotary_emb.get(max_pos, x.device)
         ctx = get_context()
         attn = self.attn
-        if self._qkv_w is None or self._qkv_w.data_ptr() != self.q_proj.weight.data_ptr():
+        if (self._qkv_w is None or self._qkv_w.data_ptr() != self.q_proj.weight.data_ptr()
+                or self._fused.stale(self._projection_params())):
             self.fuse_qkv()      # first use, or the parameters were replaced since (load, cast, move)
-        q, k, v = project_qkv(x, self._qkv_w, self._qkv_b, nh, hkv, D, position_ids, cos, sin, attn, ctx)
+        q, k, v = project_qkv(x, self._qkv_w, self._qkv_b, nh, hkv, D, position_ids, cos, sin, attn, ctx, self._fused)
         o = attn(q, k, v).reshape(n, nh * D)
         attn.kv_already_stored = False
-        return self.o_proj(o)
+        return dense(o, self.o_proj.weight)
 
 
 class DreamDecoderLayer(nn.Module):
@@ -138,7 +157,8 @@ class DreamModel(nn.Module):
         return self
 
     def forward(self, input_ids=None, position_ids=None, compute_logits=True, logits_keep_indices=None, max_pos=None,
-                **_unused):
+                greedy_stats=False, **_unused):
+        """``greedy_stats``: see ``LLaDAModel.forward``."""
         shape = input_ids.shape
         ids = input_ids.reshape(-1)
         if position_ids is None:
@@ -155,7 +175,10 @@ class DreamModel(nn.Module):
             if logits_keep_indices is not None:
                 x = x.index_select(0, logits_keep_indices)
                 delta = delta.index_select(0, logits_keep_indices) if delta is not None else None
-            logits = self.lm_head(self.model.norm(x, delta))
+            x = self.model.norm(x, delta)
+            if greedy_stats and mc.OWN_GEMM and ops._gemm_ok(x, self.lm_head.weight):
+                return SimpleNamespace(logits=None, stats=ops.linear_argmax(x, self.lm_head.weight), hidden_states=None)
+            logits = dense(x, self.lm_head.weight)
             if logits_keep_indices is None:
                 logits = logits.view(*shape, -1)
-        return SimpleNamespace(logits=logits, hidden_states=None)
+        return SimpleNamespace(logits=logits, stats=None, hidden_states=None)

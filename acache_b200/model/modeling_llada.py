@@ -4,8 +4,9 @@ Llama-style pre-norm block with separate q/k/v projections, RoPE computed in fp3
 SiLU-gated FFN and an untied output head; ragged ``[n]`` and batched ``[B, T]`` inputs
 (reference: nano-vdllm/model/modeling_llada.py:593-767 block, :889-982 model,
 :999-1064 wrapper).  Parameter names equal the reference's, so its checkpoints load
-with ``load_state_dict``.  The GEMMs are library calls; normalisation, RoPE + K/V
-scatter, attention and the gated activation are this package's kernels.
+with ``load_state_dict``.  Projections, normalisation, RoPE + K/V scatter, attention and the
+gated activation are this package's kernels (``modeling_common.OWN_GEMM`` sends the
+projections to the library GEMM instead).
 """
 from __future__ import annotations
 
@@ -19,7 +20,8 @@ from .. import ops
 from ..utils import get_context
 from .attention import Attention
 from .configuration import LLaDAConfig
-from .modeling_common import RMSNorm, RopeCache, project_qkv
+from . import modeling_common as mc
+from .modeling_common import FusedProjections, RMSNorm, RopeCache, dense, gated_mlp_input, project_qkv
 
 
 class LLaDALlamaBlock(nn.Module):
@@ -43,6 +45,11 @@ class LLaDALlamaBlock(nn.Module):
         self.attn = Attention(num_heads=config.n_heads, head_dim=d // config.n_heads,
                               num_kv_heads=config.effective_n_kv_heads)
         self._qkv_w = self._qkv_b = None
+        self._fused = FusedProjections()
+
+    def _projection_params(self):
+        return (self.q_proj.weight, self.k_proj.weight, self.v_proj.weight, self.q_proj.bias, self.ff_proj.weight,
+                self.up_proj.weight)
 
     def fuse_qkv(self):
         """One projection GEMM for q, k and v: the three weights become views of one
@@ -55,6 +62,9 @@ class LLaDALlamaBlock(nn.Module):
             b = torch.cat([self.q_proj.bias.data, self.k_proj.bias.data, self.v_proj.bias.data])
             self.q_proj.bias.data, self.k_proj.bias.data, self.v_proj.bias.data = b[:d], b[d:d + kvd], b[d + kvd:]
             self._qkv_b = b
+        D = self.config.d_model // self.config.n_heads
+        self._fused.build(self._qkv_w, self._qkv_b, self.ff_proj.weight.data, self.up_proj.weight.data, D,
+                          self._projection_params())
 
     def forward(self, x: torch.Tensor, position_ids: torch.Tensor, max_pos: int, delta=None):
         """``x [n, d]`` rows of the ragged batch (updated in place), ``position_ids [n]`` int64;
@@ -68,13 +78,15 @@ class LLaDALlamaBlock(nn.Module):
         cos, sin = self.rotary_emb.get(max_pos, x.device)
         ctx = get_context()
         attn = self.attn
-        if self._qkv_w is None or self._qkv_w.data_ptr() != self.q_proj.weight.data_ptr():
+        if (self._qkv_w is None or self._qkv_w.data_ptr() != self.q_proj.weight.data_ptr()
+                or self._fused.stale(self._projection_params())):
             self.fuse_qkv()      # first use, or the parameters were replaced since (load, cast, move)
-        q, k, v = project_qkv(h, self._qkv_w, self._qkv_b, nh, hkv, D, position_ids, cos, sin, attn, ctx)
+        q, k, v = project_qkv(h, self._qkv_w, self._qkv_b, nh, hkv, D, position_ids, cos, sin, attn, ctx, self._fused)
         att = attn(q, k, v).reshape(n, nh * D)
         attn.kv_already_stored = False
-        h = self.ff_norm(x, self.attn_out(att))
-        return x, self.ff_out(ops.act_mul(self.ff_proj(h), self.up_proj(h), cfg.activation_type))
+        h = self.ff_norm(x, dense(att, self.attn_out.weight, self.attn_out.bias))
+        h = gated_mlp_input(h, self._fused, self.ff_proj, self.up_proj, cfg.activation_type)
+        return x, dense(h, self.ff_out.weight, self.ff_out.bias)
 
 
 class LLaDAModel(nn.Module):
@@ -95,7 +107,10 @@ class LLaDAModel(nn.Module):
                                                          bias=config.include_bias, **kw)})
 
     def forward(self, input_ids, position_ids=None, output_hidden_states=None, compute_logits=True,
-                logits_keep_indices=None, max_pos: int | None = None):
+                logits_keep_indices=None, max_pos: int | None = None, greedy_stats: bool = False):
+        """``greedy_stats``: the caller only needs the arg-max token and its confidence of every
+        kept row; when the fused output head can serve that, ``.stats = (x0, confidence)`` (flat,
+        one entry per row) is returned and ``.logits`` is None (the logits are never written)."""
         shape = input_ids.shape
         ids = input_ids.reshape(-1)
         if position_ids is None:
@@ -115,15 +130,16 @@ class LLaDAModel(nn.Module):
                 x = x.index_select(0, logits_keep_indices)
                 delta = delta.index_select(0, logits_keep_indices) if delta is not None else None
             x = self.transformer["ln_f"](x, delta)
-            if self.config.weight_tying:
-                logits = F.linear(x, self.transformer["wte"].weight)
-            else:
-                logits = self.transformer["ff_out"](x)
+            head = self.transformer["wte"] if self.config.weight_tying else self.transformer["ff_out"]
+            if (greedy_stats and mc.OWN_GEMM and getattr(head, "bias", None) is None and not self.config.scale_logits
+                    and ops._gemm_ok(x, head.weight)):
+                return SimpleNamespace(logits=None, stats=ops.linear_argmax(x, head.weight), hidden_states=None)
+            logits = dense(x, head.weight, getattr(head, "bias", None))
             if self.config.scale_logits:
                 logits = logits * (self.config.d_model ** -0.5)
             if logits_keep_indices is None:
                 logits = logits.view(*shape, -1)
-        return SimpleNamespace(logits=logits, hidden_states=None)
+        return SimpleNamespace(logits=logits, stats=None, hidden_states=None)
 
 
 class LLaDAModelLM(nn.Module):
@@ -162,6 +178,6 @@ class LLaDAModelLM(nn.Module):
         return self
 
     def forward(self, input_ids=None, output_hidden_states=None, position_ids=None, logits_keep_indices=None,
-                compute_logits=True, max_pos=None):
+                compute_logits=True, max_pos=None, greedy_stats=False):
         return self.model(input_ids, position_ids=position_ids, compute_logits=compute_logits,
-                          logits_keep_indices=logits_keep_indices, max_pos=max_pos)
+                          logits_keep_indices=logits_keep_indices, max_pos=max_pos, greedy_stats=greedy_stats)

@@ -165,7 +165,8 @@ class _DecodeGraph:
     """One block-decode forward (all layers and the output head) of ``n_rows`` requests captured
     in a CUDA graph.  Inputs live at fixed addresses: the block's tokens, and the step metadata
     in a ``_StaticStaging``; the logits come back in a tensor of the graph's memory pool.  The
-    graph is replayed for every decode step with this many rows, whatever the requests are."""
+    graph is replayed for every decode step with this many rows, whatever the requests are.
+    ``logits`` holds what the forward returns: ``(logits, None)`` or ``(None, (x0, confidence))``."""
 
     def __init__(self, runner, n_rows: int, names_and_dtypes: dict, read_capacity: int, max_pos: int):
         T = runner.config.block_length
@@ -203,8 +204,7 @@ class _DecodeGraph:
                 self.graph, self.eager = None, True
                 runner.config.use_cuda_graphs = False
         if self.eager:
-            out = runner._forward_model(self.tokens, positions, max_pos=self.max_pos).logits
-            return runner._dream_decode_logits(out)
+            return runner._decode_forward(self.tokens, positions, self.max_pos)
         runner.harvest_graph_timers()
         self.graph.replay()
         _lib.LAUNCHES += self.launches
@@ -215,8 +215,7 @@ class _DecodeGraph:
 
     def _capture(self, runner, positions, timers: bool):
         def forward():
-            out = runner._forward_model(self.tokens, positions, max_pos=self.max_pos).logits
-            return runner._dream_decode_logits(out)
+            return runner._decode_forward(self.tokens, positions, self.max_pos)
 
         forward()   # eager once: tables, workspaces and library handles exist before the capture
         torch.cuda.synchronize()
@@ -305,9 +304,27 @@ class ModelRunner(DkvMixin):
         table_dtype = self.kv_cache.dtype if self._is_dream_model() else torch.float32
         return theta, table_dtype
 
-    def _forward_model(self, input_ids, position_ids=None, compute_logits=True, logits_keep_indices=None, max_pos=None):
+    def _forward_model(self, input_ids, position_ids=None, compute_logits=True, logits_keep_indices=None, max_pos=None,
+                       greedy_stats=False):
         return self.base_model(input_ids=input_ids, position_ids=position_ids, compute_logits=compute_logits,
-                               logits_keep_indices=logits_keep_indices, max_pos=max_pos)
+                               logits_keep_indices=logits_keep_indices, max_pos=max_pos, greedy_stats=greedy_stats)
+
+    def _greedy(self):
+        """Unmasking only needs each position's arg-max and confidence (temperature 0, confidence
+        remasking): the output head may then return those instead of the logits."""
+        return self.config.temperature == 0 and self.config.remasking == "low_confidence"
+
+    def _decode_forward(self, block_tokens, positions, max_pos):
+        """Block-decode forward as unmasking sees it: ``(logits [B, T, V], None)`` or
+        ``(None, (x0 [B, T], confidence [B, T]))``, Dream's shift by one position applied."""
+        out = self._forward_model(block_tokens, positions, max_pos=max_pos, greedy_stats=self._greedy())
+        if out.stats is None:
+            return self._dream_decode_logits(out.logits), None
+        x0, conf = (t.view(block_tokens.shape) for t in out.stats)
+        if self._is_dream_model():
+            x0 = torch.cat([x0[:, :1], x0[:, :-1]], dim=1).contiguous()
+            conf = torch.cat([conf[:, :1], conf[:, :-1]], dim=1).contiguous()
+        return None, (x0, conf)
 
     def _dream_decode_logits(self, logits):
         """Dream predicts token j from position j-1: shift right inside the block
@@ -1020,8 +1037,11 @@ class ModelRunner(DkvMixin):
         hf = self.config.hf_config
         vocab = int(getattr(hf, "embedding_size", None) or getattr(hf, "vocab_size", 0) or 0)
         row_bytes = self.config.block_length * vocab * self.kv_cache.element_size()
+        def held(g):   # a graph whose output head returns statistics keeps no logits
+            return 0 if isinstance(g.logits, tuple) and g.logits[0] is None else g.tokens.shape[0] * row_bytes
+
         while len(graphs) > 1:
-            total = sum(g.tokens.shape[0] * row_bytes for g in graphs.values())
+            total = sum(held(g) for g in graphs.values())
             if len(graphs) <= self.MAX_DECODE_GRAPHS and total <= self.MAX_DECODE_GRAPH_LOGITS_BYTES:
                 break
             oldest = next(k for k in graphs if k != keep)
@@ -1086,6 +1106,15 @@ class ModelRunner(DkvMixin):
         x0, ti = self.get_transfer_index(lg, cfg.temperature, cfg.remasking, sub == cfg.mask_id, sub, cfg.threshold)
         working_blocks.index_copy_(0, rows, torch.where(ti, x0, sub))
 
+    def _commit_output(self, logits, stats, working_blocks, rows):
+        """Unmask ``working_blocks[rows]`` from a forward's output, whichever form it has."""
+        if stats is None:
+            return self._commit(logits.reshape(rows.numel() * self.config.block_length, -1), working_blocks, rows)
+        x0, conf = stats
+        sub = working_blocks.index_select(0, rows).contiguous()
+        ops.apply_transfer(x0.reshape(-1), conf.reshape(-1), sub, self.config.mask_id, self.config.threshold)
+        working_blocks.index_copy_(0, rows, sub)
+
     # ------------------------------------------------------------------ generation loops
     @torch.inference_mode()
     def generate_with_dual_cache(self, prompts, arrival_times=None):
@@ -1134,7 +1163,8 @@ class ModelRunner(DkvMixin):
                 keep = self._dream_shift_keep_indices(keep, row_starts)
             keep = keep.flatten()
             t0 = self._start_timing()
-            out = self._forward_model(input_ids, positions, logits_keep_indices=keep, max_pos=max(len(s) for s in seqs))
+            out = self._forward_model(input_ids, positions, logits_keep_indices=keep, max_pos=max(len(s) for s in seqs),
+                                      greedy_stats=self._greedy())
             self._finish_timing(timing, "cache_forward", t0)
             self._add_timing_count(timing, "cache_forward_calls", 1)
             self._add_timing_count(timing, "cache_forward_nfe", len(chunk))
@@ -1143,15 +1173,18 @@ class ModelRunner(DkvMixin):
             if self._is_dream_model():
                 # only the block's first token is seeded from the refresh logits
                 # (reference: model_runner.py:2114-2118)
-                logits = out.logits.view(len(chunk), T, -1)
-                if cfg.temperature > 0:
-                    seed = torch.distributions.Categorical(
-                        probs=torch.softmax(logits[:, 0].float() / cfg.temperature, dim=-1)).sample()
+                if out.stats is not None:
+                    seed = out.stats[0].view(len(chunk), T)[:, 0]
                 else:
-                    seed = logits[:, 0].argmax(dim=-1)
+                    logits = out.logits.view(len(chunk), T, -1)
+                    if cfg.temperature > 0:
+                        seed = torch.distributions.Categorical(
+                            probs=torch.softmax(logits[:, 0].float() / cfg.temperature, dim=-1)).sample()
+                    else:
+                        seed = logits[:, 0].argmax(dim=-1)
                 working_blocks[rows, 0] = seed
             else:
-                self._commit(out.logits, working_blocks, rows)
+                self._commit_output(out.logits, out.stats, working_blocks, rows)
             self._finish_timing(timing, "cache_update", t0)
             reset_context()
 
@@ -1304,15 +1337,14 @@ class ModelRunner(DkvMixin):
                 t0 = self._start_timing()
                 block_tokens = working.index_select(0, decode_rows) if len(active) != len(batched) else working
                 if decode_graph is not None:
-                    logits = decode_graph.run(self, block_tokens, decode_positions)
+                    logits, stats = decode_graph.run(self, block_tokens, decode_positions)
                 else:
-                    logits = self._forward_model(block_tokens, decode_positions, max_pos=decode_max_pos).logits
-                    logits = self._dream_decode_logits(logits)
+                    logits, stats = self._decode_forward(block_tokens, decode_positions, decode_max_pos)
                 self._finish_timing(timing, "decode_forward", t0)
                 self._add_timing_count(timing, "decode_forward_calls", 1)
                 self._add_timing_count(timing, "decode_forward_nfe", len(active))
                 t0 = self._start_timing()
-                self._commit(logits.reshape(len(active) * T, -1), working, decode_rows)
+                self._commit_output(logits, stats, working, decode_rows)
                 self._finish_timing(timing, "decode_update", t0)
                 total_nfe += len(active)
         finally:

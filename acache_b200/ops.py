@@ -136,6 +136,95 @@ def qkv_rope_scatter(x, w_qkv, bias, n_heads, n_kv_heads, head_dim, positions, r
     return q
 
 
+# ---- dense projections on CTA-pair tcgen05 GEMMs ---------------------------------------------
+# tile override for experiments: (row blocks per pair, columns per tile); (0, 0) = chosen per launch
+GEMM_TILE = (0, 0)
+
+
+def interleave_rows(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Rows of ``a`` and ``b`` (same shape) interleaved in groups of 8: the weight layout of
+    ``linear_swiglu`` (``a`` = gate projection, ``b`` = up projection)."""
+    assert a.shape == b.shape and a.shape[0] % 8 == 0
+    n = a.shape[0] // 8
+    return torch.stack((a.reshape(n, 8, *a.shape[1:]), b.reshape(n, 8, *b.shape[1:])), dim=1).reshape(2 * a.shape[0], *a.shape[1:])
+
+
+def interleave_heads(w: torch.Tensor, head_dim: int = 128) -> torch.Tensor:
+    """Rows (or entries) of a fused q/k/v weight (bias) interleaved inside every head in groups of
+    8, low half against high half: the layout of ``linear_qkv_rope_scatter``."""
+    assert head_dim == 128 and w.shape[0] % head_dim == 0
+    h = w.shape[0] // head_dim
+    v = w.reshape(h, 2, 8, 8, *w.shape[1:])            # head, half, group, lane
+    return v.transpose(1, 2).reshape(w.shape).contiguous()
+
+
+def _gemm_ok(x, w):
+    return (x.is_cuda and x.dim() == 2 and x.dtype in (torch.bfloat16, torch.float16) and w.dtype == x.dtype
+            and x.stride(1) == 1 and w.is_contiguous() and x.shape[1] == w.shape[1] and x.shape[1] % 8 == 0
+            and x.stride(0) % 8 == 0 and w.shape[0] % 16 == 0)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """``x [n, in] @ weight[out, in]^T (+ bias)`` (an ``nn.Linear`` of the reference model blocks)."""
+    assert _gemm_ok(x, weight), "shape or dtype the projection kernel does not take"
+    n, N = x.shape[0], weight.shape[0]
+    out = torch.empty(n, N, dtype=x.dtype, device=x.device)
+    if n:
+        check(_lib.load().acache_linear(ptr(x), x.stride(0), n, x.shape[1], ptr(weight), N, ptr(bias), dtype_code(x.dtype),
+                                        ptr(out), out.stride(0), GEMM_TILE[0], GEMM_TILE[1], ptr(_lib.err_flag(x.device)),
+                                        stream_ptr()), "linear")
+    return out
+
+
+def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """``act(x @ Wg^T) * (x @ Wu^T)`` with the two weights interleaved by ``interleave_rows``."""
+    assert _gemm_ok(x, weight_gate_up)
+    n, F = x.shape[0], weight_gate_up.shape[0] // 2
+    out = torch.empty(n, F, dtype=x.dtype, device=x.device)
+    if n:
+        check(_lib.load().acache_linear_swiglu(ptr(x), x.stride(0), n, x.shape[1], ptr(weight_gate_up), F, _ACT[act],
+                                               dtype_code(x.dtype), ptr(out), out.stride(0), GEMM_TILE[0], GEMM_TILE[1],
+                                               ptr(_lib.err_flag(x.device)), stream_ptr()), "linear_swiglu")
+    return out
+
+
+def linear_qkv_rope_scatter(x, w_qkv_interleaved, bias_interleaved, n_heads, n_kv_heads, head_dim, positions, rope_cos,
+                            rope_sin, k_cache, v_cache, slot_mapping):
+    """``qkv_rope_scatter`` on CTA pairs; the weight (and bias) rows are in the ``interleave_heads``
+    layout.  Returns the rotated queries ``[n, n_heads, head_dim]``."""
+    assert _gemm_ok(x, w_qkv_interleaved) and w_qkv_interleaved.shape[0] == (n_heads + 2 * n_kv_heads) * head_dim
+    n = x.shape[0]
+    assert positions.dtype == torch.int64 and positions.numel() == n
+    assert slot_mapping.dtype == torch.int32 and slot_mapping.numel() == n
+    q = torch.empty(n, n_heads, head_dim, dtype=x.dtype, device=x.device)
+    num_slots = k_cache.numel() // (n_kv_heads * head_dim)
+    if n:
+        check(_lib.load().acache_linear_qkv_rope_scatter(
+            ptr(x), x.stride(0), n, x.shape[1], ptr(w_qkv_interleaved), ptr(bias_interleaved), n_heads, n_kv_heads,
+            head_dim, dtype_code(x.dtype), ptr(positions), ptr(rope_cos), ptr(rope_sin), rope_cos.stride(0),
+            rope_cos.shape[0], dtype_code(rope_cos.dtype), ptr(q), q.stride(0), ptr(k_cache), ptr(v_cache),
+            ptr(slot_mapping), num_slots, GEMM_TILE[0], GEMM_TILE[1], ptr(_lib.err_flag(x.device)), stream_ptr()),
+            "linear_qkv_rope_scatter")
+    return q
+
+
+def linear_argmax(x: torch.Tensor, weight: torch.Tensor):
+    """Output head + greedy statistics: ``(argmax over the vocabulary int64 [n], confidence fp32
+    [n])`` of ``x @ weight^T`` without materialising the logits."""
+    assert _gemm_ok(x, weight)
+    n, N = x.shape[0], weight.shape[0]
+    x0 = torch.empty(n, dtype=torch.int64, device=x.device)
+    conf = torch.empty(n, dtype=torch.float32, device=x.device)
+    if n:
+        lib = _lib.load()
+        nbytes = lib.acache_linear_argmax_scratch_bytes(n, N)
+        scratch = _scratch_for(x.device, nbytes)
+        check(lib.acache_linear_argmax(ptr(x), x.stride(0), n, x.shape[1], ptr(weight), N, dtype_code(x.dtype), ptr(x0),
+                                       ptr(conf), ptr(scratch), scratch.numel(), GEMM_TILE[0], GEMM_TILE[1],
+                                       ptr(_lib.err_flag(x.device)), stream_ptr()), "linear_argmax", 2)
+    return x0, conf
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     """``weight * cast(x * rsqrt(mean(x^2) + eps))`` with the mean in fp32
     (reference: nano-vdllm/model/modeling_llada.py:308-323)."""
@@ -183,3 +272,14 @@ def transfer_tokens(logits: torch.Tensor, blocks: torch.Tensor, mask_id: int, th
                                              ptr(blocks), R, T, int(mask_id), float(threshold), ptr(x0), ptr(conf),
                                              stream_ptr()), "transfer_tokens", 2)
     return x0, conf
+
+
+def apply_transfer(x0: torch.Tensor, conf: torch.Tensor, blocks: torch.Tensor, mask_id: int, threshold: float):
+    """The commit rule of ``transfer_tokens`` from statistics that already exist (``linear_argmax``):
+    edits ``blocks`` int64 ``[R, T]`` in place from ``x0`` int64 / ``conf`` fp32 of ``R * T`` entries."""
+    R, T = blocks.shape
+    assert blocks.is_contiguous() and blocks.dtype == torch.int64
+    assert x0.is_contiguous() and x0.dtype == torch.int64 and x0.numel() == R * T
+    assert conf.is_contiguous() and conf.dtype == torch.float32 and conf.numel() == R * T
+    check(_lib.load().acache_apply_transfer(ptr(blocks), ptr(x0), ptr(conf), R, T, int(mask_id), float(threshold),
+                                            stream_ptr()), "apply_transfer")

@@ -110,6 +110,56 @@ ACACHE_API int acache_qkv_rope_scatter(const void* x, int64_t x_stride, int n_ro
                                        int64_t q_stride, void* k_cache, void* v_cache, const int32_t* slot_mapping,
                                        int64_t num_slots, int32_t* err_flag, void* stream);
 
+/* ------------------------------------------------------------------ dense projections (CTA-pair tcgen05 GEMMs)
+ * Replace the nn.Linear calls of the served model blocks (LLaDA: attn_out, ff_proj / up_proj, ff_out
+ * and the output head, nano-vdllm/model/modeling_llada.py:687-704,738,757-763,978; Dream: o_proj,
+ * gate_proj / up_proj, down_proj and lm_head, modeling_dream.py:297-303,351-354,880) together with
+ * the elementwise work that follows each of them.  All compute
+ *   acc[n_rows, N] = x[n_rows, in_features] . weight[N, in_features]^T   (fp32 accumulation)
+ * on pairs of CTAs with tcgen05.mma.cta_group::2; x rows are x_stride elements apart, weight is
+ * row-major and dense.  16-bit dtypes only, N a multiple of 16, in_features a multiple of 8,
+ * 16-byte aligned pointers and row strides; anything else returns ACACHE_EUNSUPPORTED.
+ * tile_mb (0, 1 or 2) and tile_bn (0 or a multiple of 16 in 64..256) override the tile shape
+ * the launch would choose (256 * tile_mb rows by tile_bn columns per CTA pair); 0 = choose.
+ *
+ * acache_linear: out[n_rows, out_features] = acc (+ bias), rounded once to dtype.  */
+ACACHE_API int acache_linear(const void* x, int64_t x_stride, int n_rows, int in_features, const void* weight,
+                             int out_features, const void* bias, int dtype, void* out, int64_t out_stride,
+                             int tile_mb, int tile_bn, int32_t* err_flag, void* stream);
+
+/* acache_linear_swiglu: the gate and up projections and act(gate) * up (modeling_llada.py:757-763,
+ * modeling_dream.py:297-303) in one GEMM.  weight_gate_up is [2 * ffn_features, in_features] with the
+ * two projections interleaved in groups of 8 rows: rows 16g..16g+7 are gate rows 8g..8g+7, rows
+ * 16g+8..16g+15 are up rows 8g..8g+7.  out[n_rows, ffn_features]; act: 0 silu, 1 relu, 2 gelu.
+ * Both projections are rounded to dtype, then the activation, then the product, as the separate
+ * operators do. */
+ACACHE_API int acache_linear_swiglu(const void* x, int64_t x_stride, int n_rows, int in_features,
+                                    const void* weight_gate_up, int ffn_features, int act, int dtype, void* out,
+                                    int64_t out_stride, int tile_mb, int tile_bn, int32_t* err_flag, void* stream);
+
+/* acache_linear_qkv_rope_scatter: acache_qkv_rope_scatter on CTA pairs.  The rows of w_qkv (and the
+ * entries of bias) are interleaved inside every 128-row head in groups of 8: rows 16g..16g+7 of a head
+ * are its features 8g..8g+7, rows 16g+8..16g+15 its features 64+8g..64+8g+7, so that both halves of
+ * a rotation pair reach the same thread.  Outputs are in the natural feature order. */
+ACACHE_API int acache_linear_qkv_rope_scatter(const void* x, int64_t x_stride, int n_rows, int hidden,
+                                              const void* w_qkv_interleaved, const void* bias_interleaved, int n_heads,
+                                              int n_kv_heads, int head_dim, int dtype, const int64_t* positions,
+                                              const void* rope_cos, const void* rope_sin, int64_t rope_row_stride,
+                                              int rope_rows, int rope_dtype, void* out_q, int64_t q_stride,
+                                              void* k_cache, void* v_cache, const int32_t* slot_mapping,
+                                              int64_t num_slots, int tile_mb, int tile_bn, int32_t* err_flag,
+                                              void* stream);
+
+/* acache_linear_argmax: the output head followed by the statistics greedy unmasking needs
+ * (modeling_llada.py:978 + model_runner.py:2279-2296): per row the arg-max of the logits (rounded
+ * to dtype as the projection leaves them; the lowest index among equal maxima) as int64 x0[n_rows]
+ * and confidence[n_rows] = exp(max - logsumexp) in fp32.  The logits are never written to global
+ * memory.  scratch must hold acache_linear_argmax_scratch_bytes() bytes. */
+ACACHE_API int64_t acache_linear_argmax_scratch_bytes(int n_rows, int out_features);
+ACACHE_API int acache_linear_argmax(const void* x, int64_t x_stride, int n_rows, int in_features, const void* weight,
+                                    int out_features, int dtype, int64_t* x0, float* confidence, void* scratch,
+                                    int64_t scratch_bytes, int tile_mb, int tile_bn, int32_t* err_flag, void* stream);
+
 /* ------------------------------------------------------------------ anchor top-k
  * Replaces torch.topk + sort + add in anchor selection (nano-vdllm/model_runner.py:833-843;
  * llada/generate_ACache.py:225-262).  scores: fp32 [n_rows, row_stride] (first n_cols of
@@ -263,6 +313,12 @@ ACACHE_API int acache_act_mul(const void* gate, const void* up, void* y, int64_t
 ACACHE_API int acache_transfer_tokens(const void* logits, int64_t logits_stride, int vocab, int dtype, int64_t* blocks,
                            int n_rows, int block_len, int64_t mask_id, float threshold, int64_t* x0_out,
                            float* conf_out, void* stream);
+
+/* The commit rule of acache_transfer_tokens alone (model_runner.py:2297-2312), for callers that
+ * already hold the per-position statistics (acache_linear_argmax): blocks[n_rows, block_len] is
+ * edited in place from x0 / confidence of the same shape. */
+ACACHE_API int acache_apply_transfer(int64_t* blocks, const int64_t* x0, const float* confidence, int n_rows,
+                                     int block_len, int64_t mask_id, float threshold, void* stream);
 
 #ifdef __cplusplus
 }

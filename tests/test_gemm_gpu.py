@@ -1,0 +1,162 @@
+"""The CTA-pair tcgen05 projections against plain fp32 references of the same operators (a
+floating-point kernel: the reference is the fp32 product rounded the way the unfused operator
+chain rounds it; tolerance = one bf16 step of accumulation-order noise, stated per test)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+# (rows, in, out): ragged row counts, row blocks that are partly or wholly outside the matrix,
+# column counts that are not a multiple of the tile, one real projection shape
+SHAPES = [(300, 512, 384), (77, 448, 272), (1, 64, 64), (700, 256, 1040), (512, 4096, 4096), (513, 128, 2048)]
+TILES = [(0, 0), (1, 64), (1, 256), (2, 128), (2, 176), (1, 112)]
+
+
+def _ops():
+    from acache_b200 import _lib, ops
+
+    _lib.load()
+    return _lib, ops
+
+
+def _close(got, ref, what):
+    """bf16 operands, fp32 accumulation on both sides: results may differ by one rounding step of
+    the output (2^-8 relative) where the two summation orders straddle a rounding boundary."""
+    got, ref = got.float().cpu(), ref.float().cpu()
+    scale = ref.abs().max().item()
+    torch.testing.assert_close(got, ref, rtol=2 ** -7, atol=2 ** -8 * scale, msg=lambda m: f"{what}: {m}")
+
+
+@pytest.mark.parametrize("tile", TILES)
+@pytest.mark.parametrize("n,k,m_out", SHAPES)
+def test_linear_matches_fp32_reference(n, k, m_out, tile):
+    _lib, ops = _ops()
+    g = torch.Generator().manual_seed(n + k)
+    x = torch.randn(n, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(m_out, k, generator=g) * k ** -0.5).to(torch.bfloat16)
+    b = torch.randn(m_out, generator=g).to(torch.bfloat16) if n % 2 else None
+    ref = x.float() @ w.float().T
+    if b is not None:
+        ref = ref + b.float()
+    ops.GEMM_TILE = tile
+    try:
+        got = ops.linear(x.to(DEV), w.to(DEV), None if b is None else b.to(DEV))
+    finally:
+        ops.GEMM_TILE = (0, 0)
+    _close(got, ref.to(torch.bfloat16), f"linear {n}x{k}x{m_out} tile {tile}")
+    _lib.check_device_errors()
+
+
+def test_linear_takes_strided_rows_and_fp16():
+    _lib, ops = _ops()
+    g = torch.Generator().manual_seed(3)
+    big = torch.randn(200, 640, generator=g).to(torch.float16).to(DEV)
+    x = big[:, 128:384]                      # rows 640 elements apart, 256 used
+    w = (torch.randn(96, 256, generator=g) / 16).to(torch.float16).to(DEV)
+    got = ops.linear(x, w)
+    ref = (x.float() @ w.float().T).to(torch.float16)
+    _close(got, ref, "strided fp16")
+    _lib.check_device_errors()
+
+
+@pytest.mark.parametrize("tile", [(0, 0), (2, 112), (1, 256)])
+@pytest.mark.parametrize("n,k,f,act", [(300, 512, 768, "silu"), (64, 256, 136, "gelu"), (512, 4096, 12288, "silu")])
+def test_linear_swiglu_matches_the_separate_operators(n, k, f, act, tile):
+    _lib, ops = _ops()
+    g = torch.Generator().manual_seed(f)
+    x = torch.randn(n, k, generator=g).to(torch.bfloat16).to(DEV)
+    wg = (torch.randn(f, k, generator=g) * k ** -0.5).to(torch.bfloat16).to(DEV)
+    wu = (torch.randn(f, k, generator=g) * k ** -0.5).to(torch.bfloat16).to(DEV)
+    gate = (x.float() @ wg.float().T).to(torch.bfloat16)
+    up = (x.float() @ wu.float().T).to(torch.bfloat16)
+    fn = {"silu": torch.nn.functional.silu, "gelu": torch.nn.functional.gelu}[act]
+    ref = (fn(gate.float()).to(torch.bfloat16).float() * up.float()).to(torch.bfloat16)
+    ops.GEMM_TILE = tile
+    try:
+        got = ops.linear_swiglu(x, ops.interleave_rows(wg, wu), act)
+    finally:
+        ops.GEMM_TILE = (0, 0)
+    # a one-step difference in gate or up moves the product by up to two steps
+    got, ref = got.float().cpu(), ref.float().cpu()
+    torch.testing.assert_close(got, ref, rtol=2 ** -6, atol=2 ** -7 * ref.abs().max().item())
+    _lib.check_device_errors()
+
+
+@pytest.mark.parametrize("tile", [(0, 0), (2, 176), (1, 64)])
+@pytest.mark.parametrize("kind,n,hidden,nh,hkv", [("llada", 300, 512, 4, 4), ("dream", 77, 448, 7, 1),
+                                                   ("llada", 512, 4096, 32, 32)])
+def test_linear_qkv_rope_scatter_matches_unfused_path(kind, n, hidden, nh, hkv, tile):
+    """Interleaved-weight QKV projection with bias + RoPE + cache scatter in the epilogue against
+    the unfused sequence (fp32 product rounded to bf16, CPU restatement of RoPE and of the
+    scatter)."""
+    from oracle import kv_ops
+    from oracle.rope import dream_rope_qk, llada_rope_qk, rope_table
+
+    _lib, ops = _ops()
+    g = torch.Generator().manual_seed(20)
+    D, dt = 128, torch.bfloat16
+    N = (nh + 2 * hkv) * D
+    x = torch.randn(n, hidden, generator=g).to(dt)
+    w = (torch.randn(N, hidden, generator=g) * hidden ** -0.5).to(dt)
+    bias = (torch.randn(N, generator=g) * 0.1).to(dt) if kind == "dream" else None
+    pos = torch.randint(0, 900, (n,), generator=g)
+    nb, Bk = n // 64 + 2, 64
+    slots = torch.randperm(nb * Bk, generator=g)[:n].to(torch.int32)
+    slots[3] = -1
+    theta = 500000.0
+    ref = x.float() @ w.float().T
+    if bias is not None:
+        ref = ref + bias.float()
+    ref = ref.to(dt)
+    q_ref, k_ref, v_ref = ref[:, : nh * D].view(n, nh, D), ref[:, nh * D: (nh + hkv) * D].view(n, hkv, D), \
+        ref[:, (nh + hkv) * D:].view(n, hkv, D)
+    if kind == "llada":
+        q_ref, k_ref = llada_rope_qk(q_ref, k_ref, pos, theta)
+        cos, sin = rope_table(1024, D, theta, torch.float32)
+    else:
+        q_ref, k_ref = dream_rope_qk(q_ref, k_ref, pos, theta)
+        cos, sin = rope_table(1024, D, theta, dt)
+    kc, vc = torch.zeros(nb, Bk, hkv, D, dtype=dt), torch.zeros(nb, Bk, hkv, D, dtype=dt)
+    kv_ops.store_kvcache(k_ref, v_ref, kc, vc, slots)
+    kcd, vcd = torch.zeros_like(kc, device=DEV), torch.zeros_like(vc, device=DEV)
+    ops.GEMM_TILE = tile
+    try:
+        q = ops.linear_qkv_rope_scatter(x.to(DEV), ops.interleave_heads(w).to(DEV),
+                                        None if bias is None else ops.interleave_heads(bias).to(DEV), nh, hkv, D,
+                                        pos.to(DEV), cos.to(DEV), sin.to(DEV), kcd, vcd, slots.to(DEV))
+    finally:
+        ops.GEMM_TILE = (0, 0)
+    tol = 3e-2      # one bf16 step of the projection, carried through the rotation
+    assert (q.cpu().float() - q_ref.float()).abs().max() < tol
+    assert (kcd.cpu().float() - kc.float()).abs().max() < tol
+    assert (vcd.cpu().float() - vc.float()).abs().max() < tol
+    unused = ~torch.isin(torch.arange(nb * Bk), slots.long())
+    assert float(kcd.cpu().float().abs().sum(dim=(-1, -2)).view(-1)[unused].sum()) == 0
+    _lib.check_device_errors()
+
+
+@pytest.mark.parametrize("n,k,vocab", [(96, 256, 5008), (512, 4096, 126464)])
+def test_linear_argmax_matches_logits_then_argmax(n, k, vocab):
+    """Output head fused with the greedy statistics against logits -> arg-max / logsumexp:
+    identical choices wherever the top two logits are not within a rounding step, confidence
+    within 1 % (the fused path sums exponentials of the same rounded logits in another order)."""
+    _lib, ops = _ops()
+    g = torch.Generator().manual_seed(vocab)
+    x = torch.randn(n, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(vocab, k, generator=g) * k ** -0.5).to(torch.bfloat16).to(DEV)
+    w[7] = w[3]                                   # equal logits: the lower index must win
+    logits = (x.float() @ w.float().T).to(torch.bfloat16)
+    want = logits.argmax(-1)
+    lf = logits.float()
+    want_conf = torch.exp(lf.max(-1).values - torch.logsumexp(lf, -1))
+    x0, conf = ops.linear_argmax(x, w)
+    top2 = lf.topk(2, -1).values
+    clear = (top2[:, 0] - top2[:, 1]) > 2 ** -6 * top2[:, 0].abs()
+    assert clear.float().mean() > 0.5
+    assert torch.equal(x0[clear], want[clear])
+    picked = lf.gather(1, x0[:, None])[:, 0]
+    assert ((top2[:, 0] - picked) <= 2 ** -6 * top2[:, 0].abs() + 1e-6).all()
+    assert not (x0 == 7).any()
+    torch.testing.assert_close(conf[clear], want_conf[clear], rtol=2e-2, atol=1e-6)
+    _lib.check_device_errors()
