@@ -66,6 +66,7 @@ _SIGNATURES = {
     "acache_rmsnorm": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_float, c_int, c_void_p]),
     "acache_add_rmsnorm": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int,
                                    c_float, c_int, c_void_p]),
+    "acache_act_mul_halves": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
     "acache_act_mul": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "acache_apply_transfer": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_float, c_void_p]),
     "acache_transfer_tokens": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_int, c_int64, c_float,

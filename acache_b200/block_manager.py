@@ -99,6 +99,18 @@ class BlockManager:
             self.reserved_block_ids.remove(block_id)
             self._deallocate_block(block_id)
 
+    # -- whole-state copy (the engine replays the reference's allocator traffic from it) ----------
+    def snapshot(self):
+        return (list(self.free_block_ids), set(self.used_block_ids), set(self.reserved_block_ids))
+
+    def restore(self, state):
+        free, used, reserved = state
+        self.free_block_ids = _FifoIdSet(free)
+        self.used_block_ids = set(used)
+        self.reserved_block_ids = set(reserved)
+        for blk in self.blocks:
+            blk.is_free = blk.block_id in self.free_block_ids
+
     # -- per-request ----------------------------------------------------------------
     def can_allocate(self, seq) -> bool:
         return len(self.free_block_ids) >= seq.num_cache_blocks

@@ -44,6 +44,11 @@ class Config:
     # default: on B200 the per-request kernel with loader warps is faster at the measured shapes
     # (80 against 108 us at 800 shared / 560 other keys, 1.51 against 1.66 ms at 8192 / 3700)
     group_shared_span: bool = False
+    # anchor selection: probe the newly admitted requests in ragged batches of at most
+    # ``max_num_batched_tokens`` query rows (the reference runs one forward per request) and then
+    # replay the reference's per-request allocate / free sequence on the host, so the free list,
+    # and with it every block table, ends up exactly as after one probe per request
+    batch_anchor_selection: bool = True
     # eos id and block size aliases read by the block scheduler
     eos: int = -1
 

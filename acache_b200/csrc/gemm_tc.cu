@@ -40,7 +40,7 @@ constexpr uint32_t kTmemCols = 512;
 enum { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_QKV = 2, EPI_ARGMAX = 3 };
 
 struct Params {
-  int M, N, K, MB, BN, stages, acc_stages;
+  int M, N, K, MB, BN, stages, acc_stages, group;
   // plain / swiglu
   void* out; int64_t ldo; const void* bias; int act;
   // qkv
@@ -90,6 +90,57 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                ::"r"(bar), "h"(both) : "memory");
 }
+
+// All products of one k block of the pair (4 k steps of 16 x MB row blocks) from ONE statement, so
+// that the issuing thread spends a few integer operations per product: the operand descriptors
+// differ only in their 14-bit start address, which advances by 2 (32 bytes) per k step and by 1024
+// (16 KB) per row block.  `hi` is the descriptors' common upper word, `a_lo` / `b_lo` the lower
+// words for k step 0; `first` = 0 starts the accumulators over with the first k step.
+#define ACACHE_MMA2 "tcgen05.mma.cta_group::2.kind::f16 "
+template <int MB>
+__device__ __forceinline__ void issue_kblock(uint32_t d0, uint32_t d1, uint32_t a_lo, uint32_t b_lo, uint32_t hi,
+                                             uint32_t idesc, uint32_t first);
+template <>
+__device__ __forceinline__ void issue_kblock<1>(uint32_t d0, uint32_t d1, uint32_t a_lo, uint32_t b_lo, uint32_t hi,
+                                                uint32_t idesc, uint32_t first) {
+  (void)d1;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t.reg .b32 ta, tb;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\tsetp.eq.b32 q, %5, %5;\n\t"
+      "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+      ACACHE_MMA2 "[%0], da, db, %4, p;\n\t"
+      "add.u32 ta, %1, 2;\n\tadd.u32 tb, %2, 2;\n\tmov.b64 da, {ta, %3};\n\tmov.b64 db, {tb, %3};\n\t"
+      ACACHE_MMA2 "[%0], da, db, %4, q;\n\t"
+      "add.u32 ta, %1, 4;\n\tadd.u32 tb, %2, 4;\n\tmov.b64 da, {ta, %3};\n\tmov.b64 db, {tb, %3};\n\t"
+      ACACHE_MMA2 "[%0], da, db, %4, q;\n\t"
+      "add.u32 ta, %1, 6;\n\tadd.u32 tb, %2, 6;\n\tmov.b64 da, {ta, %3};\n\tmov.b64 db, {tb, %3};\n\t"
+      ACACHE_MMA2 "[%0], da, db, %4, q;\n\t}"
+      ::"r"(d0), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(first) : "memory");
+}
+template <>
+__device__ __forceinline__ void issue_kblock<2>(uint32_t d0, uint32_t d1, uint32_t a_lo, uint32_t b_lo, uint32_t hi,
+                                                uint32_t idesc, uint32_t first) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 da, dc, db;\n\t.reg .b32 ta, tc, tb;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\tsetp.eq.b32 q, %6, %6;\n\t"
+      "add.u32 tc, %2, 1024;\n\tmov.b64 da, {%2, %4};\n\tmov.b64 dc, {tc, %4};\n\tmov.b64 db, {%3, %4};\n\t"
+      ACACHE_MMA2 "[%0], da, db, %5, p;\n\t"
+      ACACHE_MMA2 "[%1], dc, db, %5, p;\n\t"
+      "add.u32 ta, %2, 2;\n\tadd.u32 tc, %2, 1026;\n\tadd.u32 tb, %3, 2;\n\t"
+      "mov.b64 da, {ta, %4};\n\tmov.b64 dc, {tc, %4};\n\tmov.b64 db, {tb, %4};\n\t"
+      ACACHE_MMA2 "[%0], da, db, %5, q;\n\t"
+      ACACHE_MMA2 "[%1], dc, db, %5, q;\n\t"
+      "add.u32 ta, %2, 4;\n\tadd.u32 tc, %2, 1028;\n\tadd.u32 tb, %3, 4;\n\t"
+      "mov.b64 da, {ta, %4};\n\tmov.b64 dc, {tc, %4};\n\tmov.b64 db, {tb, %4};\n\t"
+      ACACHE_MMA2 "[%0], da, db, %5, q;\n\t"
+      ACACHE_MMA2 "[%1], dc, db, %5, q;\n\t"
+      "add.u32 ta, %2, 6;\n\tadd.u32 tc, %2, 1030;\n\tadd.u32 tb, %3, 6;\n\t"
+      "mov.b64 da, {ta, %4};\n\tmov.b64 dc, {tc, %4};\n\tmov.b64 db, {tb, %4};\n\t"
+      ACACHE_MMA2 "[%0], da, db, %5, q;\n\t"
+      ACACHE_MMA2 "[%1], dc, db, %5, q;\n\t}"
+      ::"r"(d0), "r"(d1), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(first) : "memory");
+}
+#undef ACACHE_MMA2
 
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort) {
   const long long t0 = clock64();
@@ -233,12 +284,13 @@ __device__ __forceinline__ void epi_qkv(const Params& p, int m, int n, const flo
   }
 }
 
-template <typename T, typename TR, typename TC, int EPI>
+template <typename T, typename TR, typename TC, int EPI, int MB>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NT, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                  const __grid_constant__ Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  const int MB = p.MB, BN = p.BN, S = p.stages, AS = p.acc_stages;
+  const int BN = p.BN, S = p.stages, AS = p.acc_stages;
+  const int G = p.group;                       // stages released together (1 or 2; S is a multiple)
   const int b_bytes = (BN / 2) * BK * 2;
   const int stage_bytes = MB * A_SUB + b_bytes;
   uint8_t* ring = smem_raw;
@@ -288,14 +340,15 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0 && !*abort_flag) {
-      int it = 0;
+      int s = 0;
+      uint32_t round = 0;                      // times the ring has wrapped
       bool ok = true;
       for (int t = pair; t < total && ok; t += n_pairs) {
         const int mt = t % m_tiles, nt = t / m_tiles;
         const int m0 = mt * rows_per_tile + (int)rank * 128, n0 = nt * BN + (int)rank * (BN / 2);
-        for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
-          const int s = it % S;
-          if (it >= S) ok = wait_or_abort(bar(EMPTY + s), (uint32_t)(((it / S) - 1) & 1), abort_flag);
+        for (int kb = 0; kb < k_blocks && ok; ++kb, s = (s + 1 == S) ? 0 : s + 1, round += (s == 0)) {
+          // a group of G stages is handed back by one commit after its last stage was read
+          if (round > 0 && (s & (G - 1)) == 0) ok = wait_or_abort(bar(EMPTY + s / G), (round - 1) & 1, abort_flag);
           if (!ok) break;
           if (rank == 0) mbar_expect_tx(bar(FULL + s), (uint32_t)(2 * stage_bytes));   // both CTAs' bytes
           const uint32_t full = map_to_cta(bar(FULL + s), 0);
@@ -309,27 +362,32 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     // ------------------------------------------------------------------ product issuer (leader CTA)
     if (lane == 0 && rank == 0 && !*abort_flag) {
       const uint32_t idesc = make_idesc(Fmt<T>::id, 0, (uint32_t)BN, 256);
-      int it = 0, n = 0;
+      // descriptor words: start address in 16-byte units | leading offset 16 B; stride 1024 B between
+      // 8-row groups, descriptor version, 128-byte swizzle
+      const uint32_t desc_hi = 64u | (1u << 14) | (2u << 29);
+      const uint32_t ring_lo = (smem_u32(ring) >> 4) | (1u << 16);
+      const uint32_t stage_units = (uint32_t)stage_bytes >> 4, b_units = (uint32_t)(MB * A_SUB) >> 4;
+      int s = 0, n = 0;
+      uint32_t full_parity = 0;
       bool ok = true;
       for (int t = pair; t < total && ok; t += n_pairs, ++n) {
         const int acc = n % AS;
         if (n >= AS) ok = wait_or_abort(bar(ACC_EMPTY + acc), (uint32_t)(((n / AS) - 1) & 1), abort_flag);
         if (!ok) break;
         tc_fence_after();
-        for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
-          const int s = it % S;
-          ok = wait_or_abort(bar(FULL + s), (uint32_t)((it / S) & 1), abort_flag);
+        const uint32_t d0 = tmem_base + (uint32_t)(acc * MB * acc_cols), d1 = d0 + (uint32_t)acc_cols;
+        for (int kb = 0; kb < k_blocks && ok; ++kb) {
+          ok = wait_or_abort(bar(FULL + s), full_parity, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t a = smem_u32(ring) + s * stage_bytes, b = a + MB * A_SUB;
-#pragma unroll
-          for (int ks = 0; ks < BK / 16; ++ks) {
-            const uint64_t bd = make_desc(b + ks * 32, 16, 1024);
-            for (int r = 0; r < MB; ++r)
-              mma_ss_pair(tmem_base + (uint32_t)((acc * MB + r) * acc_cols), make_desc(a + r * A_SUB + ks * 32, 16, 1024),
-                          bd, idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+          const uint32_t a_lo = ring_lo + (uint32_t)s * stage_units;
+          issue_kblock<MB>(d0, d1, a_lo, a_lo + b_units, desc_hi, idesc, kb > 0 ? 1u : 0u);
+          // the group of stages is free in both CTAs once these products have read it
+          if ((s & (G - 1)) == G - 1) mma_commit_pair(bar(EMPTY + s / G));
+          if (++s == S) {
+            s = 0;
+            full_parity ^= 1u;
           }
-          mma_commit_pair(bar(EMPTY + s));              // the stage is free in both CTAs once these have read it
         }
         if (ok) mma_commit_pair(bar(ACC_FULL + acc));   // accumulator complete, in both CTAs
       }
@@ -459,6 +517,12 @@ __global__ void __launch_bounds__(128) argmax_fold_kernel(const float* __restric
 // ---------------------------------------------------------------------------------------- host
 struct Tile { int mb, bn, stages, acc_stages; size_t smem; };
 
+// Time of a launch ~ waves of the 74 pairs x k blocks x time of one k block of one pair.  Measured
+// on B200 (bf16, operands streaming from L2): a k block is bound by the operand bytes a CTA pulls
+// from L2 -- about 68 GB/s per SM with one row block per CTA (32 KB stages, 6 of them), 56 GB/s with
+// two (48 KB stages, 4 of them) -- and never faster than its products at the tensor pipe's rate
+// (about 94 ns per 256-row product whatever its N).  A tile whose epilogue cannot overlap the next
+// tile's products (one accumulator stage) pays for it.
 static Tile pick_tile(int M, int N, int want_mb, int want_bn, int bn_multiple) {
   double best = 1e30;
   Tile out{1, 128, 4, 2, 0};
@@ -475,12 +539,12 @@ static Tile pick_tile(int M, int N, int want_mb, int want_bn, int bn_multiple) {
       const long tiles = (long)m_tiles * n_tiles;
       const long waves = (tiles + kPairs - 1) / kPairs;
       const int acc_stages = 2 * mb * acc_cols <= 512 ? 2 : 1;
-      // time ~ waves x tile area; a tile whose epilogue is not hidden pays a little extra, and among
-      // equal costs fewer, larger tiles move fewer bytes from L2
-      double cost = (double)waves * mb * bn * (acc_stages == 1 ? 1.04 : 1.0) - 1e-3 * bn - 1e-2 * mb;
+      const int stage_bytes = mb * A_SUB + (bn / 2) * BK * 2;
+      const double load_ns = stage_bytes / (mb == 1 ? 68.0 : 56.0), mma_ns = 4.0 * mb * 94.0;
+      double cost = (double)waves * (load_ns > mma_ns ? load_ns : mma_ns) * (acc_stages == 1 ? 1.03 : 1.0);
+      cost -= 1e-4 * bn;     // among equals: fewer, larger tiles
       if (cost < best) {
         best = cost;
-        const int stage_bytes = mb * A_SUB + (bn / 2) * BK * 2;
         int stages = (int)((200 * 1024) / stage_bytes);
         if (stages > kMaxStages) stages = kMaxStages;
         out = Tile{mb, bn, stages, acc_stages, (size_t)stages * stage_bytes + 512};
@@ -490,9 +554,9 @@ static Tile pick_tile(int M, int N, int want_mb, int want_bn, int bn_multiple) {
   return out;
 }
 
-template <typename T, typename TR, typename TC, int EPI>
-static int launch(const CUtensorMap& mx, const CUtensorMap& mw, const Params& p, const Tile& tile, cudaStream_t st) {
-  auto kern = linear_tc_kernel<T, TR, TC, EPI>;
+template <typename T, typename TR, typename TC, int EPI, int MB>
+static int launch_mb(const CUtensorMap& mx, const CUtensorMap& mw, const Params& p, const Tile& tile, cudaStream_t st) {
+  auto kern = linear_tc_kernel<T, TR, TC, EPI, MB>;
   ACACHE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile.smem));
   const int m_tiles = (p.M + 256 * p.MB - 1) / (256 * p.MB), n_tiles = (p.N + p.BN - 1) / p.BN;
   const long total = (long)m_tiles * n_tiles;
@@ -500,6 +564,12 @@ static int launch(const CUtensorMap& mx, const CUtensorMap& mw, const Params& p,
   kern<<<2 * pairs, NT, tile.smem, st>>>(mx, mw, p);
   ACACHE_LAUNCH_CHECK();
   return ACACHE_OK;
+}
+
+template <typename T, typename TR, typename TC, int EPI>
+static int launch(const CUtensorMap& mx, const CUtensorMap& mw, const Params& p, const Tile& tile, cudaStream_t st) {
+  if (p.MB == 2) return launch_mb<T, TR, TC, EPI, 2>(mx, mw, p, tile, st);
+  return launch_mb<T, TR, TC, EPI, 1>(mx, mw, p, tile, st);
 }
 
 template <typename T, typename TR> struct PromoteG { using type = float; };
@@ -517,6 +587,11 @@ static int prepare(const void* x, int64_t ldx, const void* w, int M, int N, int 
   if (tile->smem == 0) return ACACHE_EUNSUPPORTED;
   p->M = M; p->N = N; p->K = K; p->MB = tile->mb; p->BN = tile->bn; p->stages = tile->stages;
   p->acc_stages = tile->acc_stages;
+  // `tcgen05.commit` costs the issuing thread a few hundred cycles: with one row block per CTA (6
+  // or more stages) two stages are handed back per commit; with two row blocks there are only 4
+  // stages and handing them back one by one keeps the loads further ahead
+  p->group = tile->mb == 1 ? 2 : 1;
+  if (p->group == 2 && (p->stages & 1)) p->stages -= 1;
   if (!make_tensor_map_2d(mx, x, M, K, ldx, 128, dtype) || !make_tensor_map_2d(mw, w, N, K, K, tile->bn / 2, dtype))
     return ACACHE_EUNSUPPORTED;
   return ACACHE_OK;

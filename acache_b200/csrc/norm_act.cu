@@ -177,9 +177,50 @@ __global__ void __launch_bounds__(256) act_mul_kernel(const T* __restrict__ gate
   }
 }
 
+// gate and up as the two halves of one projection output: x[rows, 2 * ffn] = [gate | up]
+template <typename T>
+__global__ void __launch_bounds__(256) act_mul_halves_kernel(const T* __restrict__ x, int64_t x_stride,
+                                                             T* __restrict__ y, int64_t y_stride, int rows, int ffn,
+                                                             int act) {
+  constexpr int E = 16 / sizeof(T);
+  const int vec_per_row = ffn / E;
+  const int64_t total = (int64_t)rows * vec_per_row;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / vec_per_row;
+    const int c = (int)(i % vec_per_row) * E;
+    Vec16<T> g, u, o;
+    g.u = ld_global_nc(x + r * x_stride + c);
+    u.u = ld_global_nc(x + r * x_stride + ffn + c);
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      const float a = round_to<T>(act_fn(to_f32<T>(g.e[e]), act));
+      o.e[e] = from_f32<T>(a * to_f32<T>(u.e[e]));
+    }
+    *reinterpret_cast<uint4*>(y + r * y_stride + c) = o.u;
+  }
+}
+
 }  // namespace acache
 
 using namespace acache;
+
+extern "C" int acache_act_mul_halves(const void* x, int64_t x_stride, void* y, int64_t y_stride, int n_rows, int ffn,
+                                     int act, int dtype, void* stream) {
+  if (!dtype_ok(dtype) || n_rows < 0 || ffn <= 0 || act < 0 || act > 2) return ACACHE_EINVAL;
+  if (n_rows == 0) return ACACHE_OK;
+  if (!x || !y) return ACACHE_EINVAL;
+  const int E = 16 / dtype_bytes(dtype);
+  if (ffn % E != 0 || x_stride % E != 0 || y_stride % E != 0 || !aligned16(x) || !aligned16(y)) return ACACHE_EUNSUPPORTED;
+  const int64_t total = (int64_t)n_rows * (ffn / E);
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > kNumSMs * 8) blocks = kNumSMs * 8;
+  ACACHE_DISPATCH_DTYPE(dtype, T, {
+    act_mul_halves_kernel<T><<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const T*)x, x_stride, (T*)y, y_stride,
+                                                                             n_rows, ffn, act);
+  });
+  ACACHE_LAUNCH_CHECK();
+  return ACACHE_OK;
+}
 
 extern "C" int acache_rmsnorm(const void* x, int64_t x_stride, const void* weight, void* y, int64_t y_stride,
                               int n_rows, int n_cols, float eps, int dtype, void* stream) {

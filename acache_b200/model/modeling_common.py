@@ -18,20 +18,37 @@ def build_rope_table(length: int, head_dim: int, theta: float, dtype: torch.dtyp
     return emb.cos().to(dtype).to(device), emb.sin().to(dtype).to(device)
 
 
-# The dense projections of the model blocks run on this package's CTA-pair tcgen05 GEMMs
-# (``ops.linear*``: fused QKV + RoPE + cache scatter, output projection, gate/up projection with the
-# gated activation in the epilogue, down projection, output head) for 16-bit models whose shapes
-# the kernels take; False sends every projection to the library GEMM instead.
-OWN_GEMM = True
+# Which projections of the model blocks run on this package's CTA-pair tcgen05 GEMMs
+# (``ops.linear*``) instead of the library GEMM, for 16-bit models whose shapes the kernels take:
+#   OWN_QKV      q/k/v projection with bias, RoPE and the cache scatter in its epilogue
+#   OWN_GATE_UP  gate and up projections as one GEMM with the gated activation in its epilogue
+#   OWN_DENSE    the plain projections (attention output, feed-forward output)
+#   OWN_HEAD     the output head; for greedy unmasking it returns arg-max and confidence and
+#                never writes the logits
+# Without a TMA multicast of operand tiles every SM pulls its own tiles from L2, which bounds a
+# CTA-pair GEMM at 55-70 GB/s of operand bytes per SM: 0.82-0.93 of the library GEMM at these
+# shapes.  With the work fused into their epilogues the QKV, gate/up and output-head projections
+# come out level with or ahead of the library GEMM plus the separate kernels, so they are on; the
+# two plain projections (4096 output columns: too few tiles for 74 CTA pairs) stay with the library.
+OWN_QKV = True
+OWN_GATE_UP = True
+OWN_DENSE = False
+OWN_HEAD = True
 
 # The older single-CTA form of the fused QKV projection (128 x 128 tiles); kept for comparison,
 # slower than both the CTA-pair kernel and the library GEMM + RoPE/scatter kernel.
 FUSED_QKV = False
 
 
+def set_own_gemm(on: bool):
+    """Switches every projection to this package's kernels (True) or to the library GEMM (False)."""
+    global OWN_QKV, OWN_GATE_UP, OWN_DENSE, OWN_HEAD
+    OWN_QKV = OWN_GATE_UP = OWN_DENSE = OWN_HEAD = bool(on)
+
+
 def dense(x, weight, bias=None):
     """An ``nn.Linear`` of the model blocks on 2-D activations."""
-    if OWN_GEMM and ops._gemm_ok(x, weight):
+    if OWN_DENSE and ops._gemm_ok(x, weight):
         return ops.linear(x, weight, bias)
     return torch.nn.functional.linear(x, weight, bias)
 
@@ -40,7 +57,8 @@ class FusedProjections:
     """Weights of one block in the layouts the fused projection kernels read: q/k/v rows
     interleaved inside every head (``ops.interleave_heads``), gate and up rows interleaved with
     each other (``ops.interleave_rows``).  These are copies (the parameters keep their natural
-    layout for state dicts); ``stale()`` tells when the parameters were replaced since."""
+    layout for state dicts), made on first use by the kernel that needs them; ``stale()`` tells
+    when the parameters were replaced since."""
 
     def __init__(self):
         self.qkv_w = self.qkv_b = self.gate_up_w = None
@@ -53,22 +71,43 @@ class FusedProjections:
     def stale(self, params):
         return self._stamp != self._stamp_of(params)
 
-    def build(self, w_qkv, b_qkv, gate, up, head_dim, params):
-        usable = w_qkv.dtype in (torch.bfloat16, torch.float16) and w_qkv.is_cuda
+    def reset(self, params):
         self.qkv_w = self.qkv_b = self.gate_up_w = None
-        if usable and head_dim == 128:
-            self.qkv_w = ops.interleave_heads(w_qkv)
-            self.qkv_b = ops.interleave_heads(b_qkv) if b_qkv is not None else None
-        if usable and gate.shape[0] % 8 == 0:
-            self.gate_up_w = ops.interleave_rows(gate, up)
         self._stamp = self._stamp_of(params)
 
+    def qkv(self, w_qkv, b_qkv, head_dim):
+        if self.qkv_w is None and head_dim == 128 and w_qkv.is_cuda and w_qkv.dtype in (torch.bfloat16, torch.float16):
+            self.qkv_w = ops.interleave_heads(w_qkv)
+            self.qkv_b = ops.interleave_heads(b_qkv) if b_qkv is not None else None
+        return self.qkv_w, self.qkv_b
 
-def gated_mlp_input(h, fused: FusedProjections, gate_proj, up_proj, act: str):
-    """``act(gate_proj(h)) * up_proj(h)``: one GEMM with the activation in its epilogue when the
-    interleaved weight exists, else two projections and the activation kernel."""
-    if OWN_GEMM and fused.gate_up_w is not None and gate_proj.bias is None and ops._gemm_ok(h, fused.gate_up_w):
-        return ops.linear_swiglu(h, fused.gate_up_w, act)
+    def gate_up(self, gate, up):
+        if (self.gate_up_w is None and gate.shape[0] % 8 == 0 and gate.is_cuda
+                and gate.dtype in (torch.bfloat16, torch.float16)):
+            self.gate_up_w = ops.interleave_rows(gate, up)
+        return self.gate_up_w
+
+
+def concat_gate_up(gate_proj, up_proj):
+    """One buffer ``[2F, in]`` holding the gate rows then the up rows; the two parameters become
+    views of it (state-dict names and values unchanged), so one library GEMM computes both."""
+    w = torch.cat([gate_proj.weight.data, up_proj.weight.data], dim=0)
+    f = gate_proj.out_features
+    gate_proj.weight.data, up_proj.weight.data = w[:f], w[f:]
+    return w
+
+
+def gated_mlp_input(h, fused: FusedProjections, gate_proj, up_proj, act: str, gate_up_cat=None):
+    """``act(gate_proj(h)) * up_proj(h)``: one GEMM of this package with the activation in its
+    epilogue (``OWN_GATE_UP``), else one library GEMM over the concatenated weights followed by the
+    activation kernel on its two halves, else two projections and the activation kernel."""
+    if OWN_GATE_UP and gate_proj.bias is None and h.dtype in (torch.bfloat16, torch.float16) and h.is_cuda:
+        w = fused.gate_up(gate_proj.weight.data, up_proj.weight.data)
+        if w is not None and ops._gemm_ok(h, w):
+            return ops.linear_swiglu(h, w, act)
+    if (gate_up_cat is not None and gate_proj.bias is None
+            and gate_up_cat.data_ptr() == gate_proj.weight.data_ptr() and h.shape[1] % 8 == 0):
+        return ops.act_mul_halves(dense(h, gate_up_cat), act)
     return ops.act_mul(dense(h, gate_proj.weight, gate_proj.bias), dense(h, up_proj.weight, up_proj.bias), act)
 
 
@@ -78,12 +117,13 @@ def project_qkv(h, w_qkv, b_qkv, n_heads, n_kv_heads, head_dim, position_ids, co
     n = h.shape[0]
     D, nh, hkv = head_dim, n_heads, n_kv_heads
     caching = attn.k_cache.numel() > 0 and ctx.slot_mapping is not None
-    if (OWN_GEMM and caching and fused is not None and fused.qkv_w is not None and ops._gemm_ok(h, fused.qkv_w)
-            and cos.stride(0) * cos.element_size() % 16 == 0):
-        q = ops.linear_qkv_rope_scatter(h, fused.qkv_w, fused.qkv_b, nh, hkv, D, position_ids, cos, sin, attn.k_cache,
-                                        attn.v_cache, ctx.slot_mapping)
-        attn.kv_already_stored = True
-        return q, None, None
+    if OWN_QKV and caching and fused is not None and cos.stride(0) * cos.element_size() % 16 == 0:
+        wi, bi = fused.qkv(w_qkv, b_qkv, D)
+        if wi is not None and ops._gemm_ok(h, wi):
+            q = ops.linear_qkv_rope_scatter(h, wi, bi, nh, hkv, D, position_ids, cos, sin, attn.k_cache, attn.v_cache,
+                                            ctx.slot_mapping)
+            attn.kv_already_stored = True
+            return q, None, None
     if (FUSED_QKV and caching and D == 128 and h.dtype in (torch.bfloat16, torch.float16) and h.shape[1] % 64 == 0
             and h.stride(0) % 8 == 0):
         q = ops.qkv_rope_scatter(h, w_qkv, b_qkv, nh, hkv, D, position_ids, cos, sin, attn.k_cache, attn.v_cache,

@@ -18,7 +18,7 @@ from ..utils import get_context
 from .attention import Attention
 from .configuration import DreamConfig
 from . import modeling_common as mc
-from .modeling_common import FusedProjections, RMSNorm, RopeCache, dense, gated_mlp_input, project_qkv
+from .modeling_common import FusedProjections, RMSNorm, RopeCache, concat_gate_up, dense, gated_mlp_input, project_qkv
 
 
 class DreamMLP(nn.Module):
@@ -30,15 +30,18 @@ class DreamMLP(nn.Module):
         self.down_proj = nn.Linear(config.intermediate_size, config.hidden_size, bias=False, **kw)
         self.act = config.hidden_act
         self._fused = FusedProjections()
+        self._gate_up_w = None
 
     def _params(self):
         return (self.gate_proj.weight, self.up_proj.weight)
 
     def forward(self, x):
-        if self._fused.stale(self._params()):
-            w = self.gate_proj.weight.data
-            self._fused.build(w, None, w, self.up_proj.weight.data, 0, self._params())
-        return dense(gated_mlp_input(x, self._fused, self.gate_proj, self.up_proj, self.act), self.down_proj.weight)
+        if (self._gate_up_w is None or self._gate_up_w.data_ptr() != self.gate_proj.weight.data_ptr()
+                or self._fused.stale(self._params())):
+            self._gate_up_w = concat_gate_up(self.gate_proj, self.up_proj)
+            self._fused.reset(self._params())
+        h = gated_mlp_input(x, self._fused, self.gate_proj, self.up_proj, self.act, self._gate_up_w)
+        return dense(h, self.down_proj.weight)
 
 
 class DreamSdpaAttention(nn.Module):
@@ -71,11 +74,7 @@ class DreamSdpaAttention(nn.Module):
         self.q_proj.weight.data, self.k_proj.weight.data, self.v_proj.weight.data = w[:d], w[d:d + kvd], w[d + kvd:]
         self.q_proj.bias.data, self.k_proj.bias.data, self.v_proj.bias.data = b[:d], b[d:d + kvd], b[d + kvd:]
         self._qkv_w, self._qkv_b = w, b
-        if w.dtype in (torch.bfloat16, torch.float16) and w.is_cuda and self.head_dim == 128:
-            self._fused.qkv_w, self._fused.qkv_b = ops.interleave_heads(w), ops.interleave_heads(b)
-        else:
-            self._fused.qkv_w = self._fused.qkv_b = None
-        self._fused._stamp = self._fused._stamp_of(self._projection_params())
+        self._fused.reset(self._projection_params())
 
     def forward(self, x, position_ids, max_pos):
         n = x.shape[0]
@@ -176,9 +175,12 @@ class DreamModel(nn.Module):
                 x = x.index_select(0, logits_keep_indices)
                 delta = delta.index_select(0, logits_keep_indices) if delta is not None else None
             x = self.model.norm(x, delta)
-            if greedy_stats and mc.OWN_GEMM and ops._gemm_ok(x, self.lm_head.weight):
+            if greedy_stats and mc.OWN_HEAD and ops._gemm_ok(x, self.lm_head.weight):
                 return SimpleNamespace(logits=None, stats=ops.linear_argmax(x, self.lm_head.weight), hidden_states=None)
-            logits = dense(x, self.lm_head.weight)
+            if mc.OWN_HEAD and ops._gemm_ok(x, self.lm_head.weight):
+                logits = ops.linear(x, self.lm_head.weight)
+            else:
+                logits = F.linear(x, self.lm_head.weight)
             if logits_keep_indices is None:
                 logits = logits.view(*shape, -1)
         return SimpleNamespace(logits=logits, stats=None, hidden_states=None)

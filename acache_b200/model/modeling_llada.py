@@ -21,7 +21,7 @@ from ..utils import get_context
 from .attention import Attention
 from .configuration import LLaDAConfig
 from . import modeling_common as mc
-from .modeling_common import FusedProjections, RMSNorm, RopeCache, dense, gated_mlp_input, project_qkv
+from .modeling_common import FusedProjections, RMSNorm, RopeCache, concat_gate_up, dense, gated_mlp_input, project_qkv
 
 
 class LLaDALlamaBlock(nn.Module):
@@ -44,7 +44,7 @@ class LLaDALlamaBlock(nn.Module):
         self.rotary_emb = rope
         self.attn = Attention(num_heads=config.n_heads, head_dim=d // config.n_heads,
                               num_kv_heads=config.effective_n_kv_heads)
-        self._qkv_w = self._qkv_b = None
+        self._qkv_w = self._qkv_b = self._gate_up_w = None
         self._fused = FusedProjections()
 
     def _projection_params(self):
@@ -62,9 +62,8 @@ class LLaDALlamaBlock(nn.Module):
             b = torch.cat([self.q_proj.bias.data, self.k_proj.bias.data, self.v_proj.bias.data])
             self.q_proj.bias.data, self.k_proj.bias.data, self.v_proj.bias.data = b[:d], b[d:d + kvd], b[d + kvd:]
             self._qkv_b = b
-        D = self.config.d_model // self.config.n_heads
-        self._fused.build(self._qkv_w, self._qkv_b, self.ff_proj.weight.data, self.up_proj.weight.data, D,
-                          self._projection_params())
+        self._gate_up_w = concat_gate_up(self.ff_proj, self.up_proj) if self.ff_proj.bias is None else None
+        self._fused.reset(self._projection_params())
 
     def forward(self, x: torch.Tensor, position_ids: torch.Tensor, max_pos: int, delta=None):
         """``x [n, d]`` rows of the ragged batch (updated in place), ``position_ids [n]`` int64;
@@ -85,7 +84,7 @@ class LLaDALlamaBlock(nn.Module):
         att = attn(q, k, v).reshape(n, nh * D)
         attn.kv_already_stored = False
         h = self.ff_norm(x, dense(att, self.attn_out.weight, self.attn_out.bias))
-        h = gated_mlp_input(h, self._fused, self.ff_proj, self.up_proj, cfg.activation_type)
+        h = gated_mlp_input(h, self._fused, self.ff_proj, self.up_proj, cfg.activation_type, self._gate_up_w)
         return x, dense(h, self.ff_out.weight, self.ff_out.bias)
 
 
@@ -131,10 +130,13 @@ class LLaDAModel(nn.Module):
                 delta = delta.index_select(0, logits_keep_indices) if delta is not None else None
             x = self.transformer["ln_f"](x, delta)
             head = self.transformer["wte"] if self.config.weight_tying else self.transformer["ff_out"]
-            if (greedy_stats and mc.OWN_GEMM and getattr(head, "bias", None) is None and not self.config.scale_logits
+            if (greedy_stats and mc.OWN_HEAD and getattr(head, "bias", None) is None and not self.config.scale_logits
                     and ops._gemm_ok(x, head.weight)):
                 return SimpleNamespace(logits=None, stats=ops.linear_argmax(x, head.weight), hidden_states=None)
-            logits = dense(x, head.weight, getattr(head, "bias", None))
+            if mc.OWN_HEAD and ops._gemm_ok(x, head.weight):
+                logits = ops.linear(x, head.weight, getattr(head, "bias", None))
+            else:
+                logits = F.linear(x, head.weight, getattr(head, "bias", None))
             if self.config.scale_logits:
                 logits = logits * (self.config.d_model ** -0.5)
             if logits_keep_indices is None:

@@ -791,9 +791,66 @@ class ModelRunner(DkvMixin):
                               affix_end=seq.prompt_affix_end)
         return toks
 
+    def _select_anchor_positions_batched(self, seqs) -> bool:
+        """Anchor selection of several new requests with ragged batched probe forwards instead of
+        one forward per request.  A request's scores do not depend on what else is in the batch,
+        and relocation inside the kernel gives the bits of the materialised copy the one-request
+        probe reads, so the anchors are the ones of the per-request procedure; what that procedure
+        does to the allocator (every probe takes blocks from the head of the free list and returns
+        them to its tail, around an optional relocation workspace) is replayed on the host
+        afterwards from the state before the probes.  Returns False, with nothing changed, when
+        the batch cannot be probed this way (then the per-request procedure runs)."""
+        bm = self.block_manager
+        todo = [s for s in seqs if s.acache_enabled and s.num_anchor_tokens > 0 and s.affix_len > 0]
+        if (len(todo) < 2 or self.config.max_num_seqs == 1 or any(s.block_table for s in todo)
+                or self._relocated_affix_slot_offset is not None
+                or any(s.num_cache_blocks > len(bm.free_block_ids) for s in todo)):
+            return False
+        state = bm.snapshot()
+        budget = max(int(getattr(self.config, "max_num_batched_tokens", 16384)), 1)
+        picked = {}
+        try:
+            i = 0
+            while i < len(todo):
+                chunk, rows, blocks = [], 0, 0
+                while i < len(todo):
+                    s = todo[i]
+                    n = len(s) - s.affix_len
+                    if chunk and (rows + n > budget or blocks + s.num_cache_blocks > len(bm.free_block_ids)):
+                        break
+                    chunk.append(s)
+                    rows, blocks = rows + n, blocks + s.num_cache_blocks
+                    i += 1
+                for s, anchors in zip(chunk, self._compute_anchor_positions_batch(chunk)):
+                    picked[s.seq_id] = anchors
+        except torch.OutOfMemoryError:
+            bm.restore(state)
+            for s in todo:
+                s.block_table = []
+            return False
+        bm.restore(state)
+        for s in seqs:
+            if s.seq_id not in picked:
+                s.set_anchor_positions([])
+                continue
+            # the allocator traffic of this request's own probe (reference: model_runner.py:684-699,799-821)
+            workspace = self._reserve_single_sequence_relocation_workspace(s, force=True)
+            bm.allocate(s)
+            self._record_kv_cache_usage(self._active_timing)
+            bm.deallocate(s)
+            if workspace:
+                bm.release_prefix_tail(self.shared_prefix_blocks)
+                self._relocated_affix_slot_offset = None
+            s.set_anchor_positions(picked[s.seq_id])
+        return True
+
     def _select_anchor_positions_for_sequences(self, seqs, prefix_token_ids, allow_kv_cache_resize, minimum_blocks=None):
         """One probe per request, as the reference (model_runner.py:862-907), with its
-        out-of-memory recovery: shrink the cache, recompute the affix, retry."""
+        out-of-memory recovery: shrink the cache, recompute the affix, retry.  With
+        ``config.batch_anchor_selection`` the probes of a batch of new requests run as ragged
+        batched forwards first (same anchors, same allocator state afterwards)."""
+        if getattr(self.config, "batch_anchor_selection", False) and self._select_anchor_positions_batched(seqs):
+            return
         for seq in seqs:
             while True:
                 try:

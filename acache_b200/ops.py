@@ -259,6 +259,17 @@ def act_mul(gate: torch.Tensor, up: torch.Tensor, act: str = "silu") -> torch.Te
     return y
 
 
+def act_mul_halves(x: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """``act(x[:, :F]) * x[:, F:]`` for ``x [n, 2F]``: the gate and up projections computed by one
+    GEMM over the concatenated weights."""
+    assert x.dim() == 2 and x.stride(1) == 1 and x.shape[1] % 2 == 0
+    n, F = x.shape[0], x.shape[1] // 2
+    y = torch.empty(n, F, dtype=x.dtype, device=x.device)
+    check(_lib.load().acache_act_mul_halves(ptr(x), x.stride(0), ptr(y), y.stride(0), n, F, _ACT[act],
+                                            dtype_code(x.dtype), stream_ptr()), "act_mul_halves")
+    return y
+
+
 def transfer_tokens(logits: torch.Tensor, blocks: torch.Tensor, mask_id: int, threshold: float):
     """Threshold unmasking at temperature 0 applied in place to ``blocks`` int64
     ``[R, T]`` from ``logits [R*T, V]`` (reference: nano-vdllm/model_runner.py:2279-2314).

@@ -348,6 +348,10 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     _lib.load()
+    if args.projections != "default":
+        from acache_b200.model import modeling_common
+
+        modeling_common.set_own_gemm(args.projections == "own")
 
     wl = dict(WORKLOADS[args.workload])
     if args.batch:
@@ -509,7 +513,7 @@ def run_ours(args):
             n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=dev_ms / args.steps, higher_is_better=True,
             scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
             config={"workload": workload, "batch_per_gpu": batch, "layers": n_layers, "parallelism": f"dp{world}",
-                    "kv_cache_blocks": cfg.num_kvcache_blocks,
+                    "kv_cache_blocks": cfg.num_kvcache_blocks, "projections": args.projections,
                     "l2": "weights (15-16 GB) and K/V re-read every step exceed the 126 MB L2"},
             clocks=clocks,
             e2e={"value": tokens / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -619,6 +623,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the architecture")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-subpaths", action="store_true")
+    ap.add_argument("--projections", default="default", choices=["default", "own", "library"],
+                    help="debug only: every projection on this package's GEMM kernels / on the library GEMM")
     ap.add_argument("--mode", default="acache", choices=["acache", "dkv_acache", "dual_cache"],
                     help="acache = the benchmark; the other serving modes of the engine on the same workload")
     args = ap.parse_args()

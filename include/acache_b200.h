@@ -299,6 +299,10 @@ ACACHE_API int acache_add_rmsnorm(void* x, int64_t x_stride, const void* delta, 
 /* y = act(gate) * up, act: 0 = SiLU, 1 = ReLU, 2 = GELU(erf)
  * (nano-vdllm/model/modeling_llada.py:757-763, nano-vdllm/model/modeling_dream.py:297-303). */
 ACACHE_API int acache_act_mul(const void* gate, const void* up, void* y, int64_t n, int act, int dtype, void* stream);
+/* The same for a gate and an up projection computed by ONE GEMM over the concatenated weights:
+ * x[n_rows, 2 * ffn] = [gate | up] (rows x_stride apart), y[n_rows, ffn] = act(gate) * up. */
+ACACHE_API int acache_act_mul_halves(const void* x, int64_t x_stride, void* y, int64_t y_stride, int n_rows, int ffn,
+                                     int act, int dtype, void* stream);
 
 /* ------------------------------------------------------------------ threshold unmasking
  * Replaces get_transfer_index at temperature 0 with 'low_confidence' remasking

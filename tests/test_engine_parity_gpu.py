@@ -51,6 +51,24 @@ def _check_logits(tag, got, want, report):
         assert margin <= TOL, f"{tag} row {r}: arg-max differs with a margin of {margin:.3e} of the logit range"
 
 
+def _check_stats(tag, x0, conf, want, report):
+    """The form greedy unmasking consumes when the output head is fused with the arg-max: token and
+    confidence per position against the restatement's logits of the same step."""
+    want = want.float().cpu()
+    x0, conf = x0.cpu(), conf.float().cpu()
+    span = (want.max() - want.min()).item()
+    top2 = want.topk(2, -1).values
+    clear = (top2[:, 0] - top2[:, 1]) > TOL * span
+    assert torch.equal(x0[clear], want.argmax(-1)[clear]), tag
+    picked = want.gather(1, x0[:, None])[:, 0]
+    assert ((top2[:, 0] - picked) <= TOL * span).all(), tag          # never a token the restatement ranks far below
+    want_conf = torch.exp(top2[:, 0] - torch.logsumexp(want, -1))
+    err = (torch.log(conf) - torch.log(want_conf)).abs().max().item()
+    report["max_log_conf_err"] = max(report.get("max_log_conf_err", 0.0), err)
+    assert err <= 2 * TOL * span, f"{tag}: confidence differs by a factor of e^{err:.3f}"
+    report["fused_head_steps"] = report.get("fused_head_steps", 0) + 1
+
+
 def _build(kind, layers, seed):
     if kind == "llada":
         from acache_b200.model.configuration import LLaDAConfig
@@ -83,7 +101,21 @@ def _build(kind, layers, seed):
     return hf, model.fuse_projections(), oracle
 
 
-def _run_case(kind, placement, A, ratio, n_req, own_lo, own_hi, G, T, decode_steps, seed):
+def _run_case(kind, placement, A, ratio, n_req, own_lo, own_hi, G, T, decode_steps, seed, own_gemm=None):
+    """``own_gemm``: None = the projections as shipped; True = every projection on this package's
+    CTA-pair tcgen05 kernels (fused QKV + RoPE + scatter, gate/up + activation, plain, output head)."""
+    from acache_b200.model import modeling_common as mc
+
+    saved = (mc.OWN_QKV, mc.OWN_GATE_UP, mc.OWN_DENSE, mc.OWN_HEAD)
+    if own_gemm is not None:
+        mc.set_own_gemm(own_gemm)
+    try:
+        return _run_case_body(kind, placement, A, ratio, n_req, own_lo, own_hi, G, T, decode_steps, seed)
+    finally:
+        mc.OWN_QKV, mc.OWN_GATE_UP, mc.OWN_DENSE, mc.OWN_HEAD = saved
+
+
+def _run_case_body(kind, placement, A, ratio, n_req, own_lo, own_hi, G, T, decode_steps, seed):
     from acache_b200 import _lib, ops
     from acache_b200.config import Config
     from acache_b200.model import acache_attention as aa
@@ -201,26 +233,33 @@ def _run_case(kind, placement, A, ratio, n_req, own_lo, own_hi, G, T, decode_ste
             positions = runner.prepare_decoding_acache(seqs)
             lg = runner._forward_model(working, positions, max_pos=max(len(s) for s in seqs)).logits
             lg = runner._dream_decode_logits(lg)
+            _, stats = runner._decode_forward(working, positions, max(len(s) for s in seqs))   # what unmasking consumes
             reset_context()
             for b, seq in enumerate(seqs):
                 phase, _, want, blk = next(steps[b])
                 assert phase == "decode"
                 _check_logits(f"decode step {step} req {b}", lg[b], want, report)
+                if stats is not None:
+                    _check_stats(f"decode step {step} req {b}", stats[0][b], stats[1][b], want, report)
                 working[b] = blk.to(DEV)
     _lib.check_device_errors()
     print(f"parity {kind} {placement} A={A}: {report}")
     return report
 
 
-def test_llada_prefix_800_teacher_forced():
+@pytest.mark.parametrize("own_gemm", [None, True])
+def test_llada_prefix_800_teacher_forced(own_gemm):
     """The benchmark's shape: LLaDA-8B widths, 800-token prefix affix, requests of 64-256 tokens."""
-    _run_case("llada", "prefix", A=800, ratio=0.2, n_req=3, own_lo=64, own_hi=256, G=32, T=32, decode_steps=3, seed=5)
+    _run_case("llada", "prefix", A=800, ratio=0.2, n_req=3, own_lo=64, own_hi=256, G=32, T=32, decode_steps=3, seed=5,
+              own_gemm=own_gemm)
 
 
-def test_dream_infix_600_teacher_forced():
+@pytest.mark.parametrize("own_gemm", [None, True])
+def test_dream_infix_600_teacher_forced(own_gemm):
     """Dream-7B widths (28 query heads on 4 KV heads), 600-token affix between a head and a tail of
     32-128 tokens: query-side relocation, shifted logits."""
-    _run_case("dream", "infix", A=600, ratio=0.2, n_req=3, own_lo=32, own_hi=128, G=32, T=32, decode_steps=3, seed=6)
+    _run_case("dream", "infix", A=600, ratio=0.2, n_req=3, own_lo=32, own_hi=128, G=32, T=32, decode_steps=3, seed=6,
+              own_gemm=own_gemm)
 
 
 def test_llada_suffix_2048_teacher_forced():

@@ -140,7 +140,7 @@ def test_linear_qkv_rope_scatter_matches_unfused_path(kind, n, hidden, nh, hkv, 
 def test_linear_argmax_matches_logits_then_argmax(n, k, vocab):
     """Output head fused with the greedy statistics against logits -> arg-max / logsumexp:
     identical choices wherever the top two logits are not within a rounding step, confidence
-    within 1 % (the fused path sums exponentials of the same rounded logits in another order)."""
+    within a few per cent: the two paths round the logits from differently ordered fp32 sums, and one bf16 step of the maximum logit (2^-8 of its magnitude) moves the confidence by that much."""
     _lib, ops = _ops()
     g = torch.Generator().manual_seed(vocab)
     x = torch.randn(n, k, generator=g).to(torch.bfloat16).to(DEV)
@@ -158,5 +158,5 @@ def test_linear_argmax_matches_logits_then_argmax(n, k, vocab):
     picked = lf.gather(1, x0[:, None])[:, 0]
     assert ((top2[:, 0] - picked) <= 2 ** -6 * top2[:, 0].abs() + 1e-6).all()
     assert not (x0 == 7).any()
-    torch.testing.assert_close(conf[clear], want_conf[clear], rtol=2e-2, atol=1e-6)
+    torch.testing.assert_close(conf[clear], want_conf[clear], rtol=6e-2, atol=1e-6)
     _lib.check_device_errors()
