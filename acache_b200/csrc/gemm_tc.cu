@@ -13,12 +13,13 @@
 // (128 rows staged by each CTA) with a BN-column block of W (BN/2 rows staged by each CTA), so a
 // W tile crosses L2 -> shared memory once per 256 rows, or once per 512 rows when a pair keeps
 // two row blocks (MB = 2).  Every CTA loads its own halves with plain TMA tile loads whose
-// completion is counted on the leader's mbarrier; nothing is multicast.  Per CTA (192 threads):
+// completion is counted on the leader's mbarrier; nothing is multicast.  Per CTA (320 threads):
 //   warp 0      one thread issues the TMA loads of every k block into a ring of stages;
 //   warp 1      (leader CTA only) one thread issues the products of the pair into TMEM and
 //               commits them to the `stage free` barriers of both CTAs / the `accumulator ready`
 //               barriers of both CTAs;
-//   warps 2-5   epilogue: thread = accumulator row; reads TMEM 16 columns at a time.
+//   warps 2-9   epilogue: thread = accumulator row, two warps per 32 rows taking alternate
+//               32-column groups; reads TMEM 16 columns at a time.
 // The pair walks the tile list (row block fastest, so pairs that run together share W tiles in
 // L2); BN is chosen per launch so that the tiles fill whole waves of the 74 pairs, and with two
 // accumulator stages (when they fit the 512 TMEM columns) the epilogue of a tile overlaps the
@@ -31,7 +32,7 @@ namespace gemm {
 
 using namespace tc;
 
-constexpr int BK = 64, NT = 192;
+constexpr int BK = 64, NT = 320;          // 2 single-thread roles + 8 epilogue warps
 constexpr int A_SUB = 128 * BK * 2;      // one 128-row block of X for one k block: 16 KB
 constexpr int kPairs = kNumSMs / 2;
 constexpr int kMaxStages = 8;
@@ -320,7 +321,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar(ACC_FULL + a), 1);
-      mbar_init(bar(ACC_EMPTY + a), 8);   // one arrival per epilogue warp of both CTAs
+      mbar_init(bar(ACC_EMPTY + a), 16);  // one arrival per epilogue warp of both CTAs
     }
     *abort_flag = misplaced ? 1 : 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -394,7 +395,10 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     }
   } else {
     // ------------------------------------------------------------------ epilogue (both CTAs)
-    const int quad = warp & 3;                    // TMEM lane quadrant this warp may access
+    // eight warps: warps w and w + 4 share the TMEM lane quadrant w % 4 (the only lanes either may
+    // access) and take alternate 32-column groups of the accumulator
+    const int quad = warp & 3;
+    const int chalf = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
     const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
     const uint32_t acc_empty0 = map_to_cta(bar(ACC_EMPTY), 0);
@@ -429,7 +433,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         float run_max = -INFINITY, run_sum = 0.f;
         int run_arg = 0;
 #pragma unroll 1
-        for (int c = 0; c < cols; c += 32) {
+        for (int c = chalf * 32; c < cols; c += 64) {
           uint32_t v0[16], v1[16];
           const bool two = c + 16 < cols;
           tmem_ld16(t_acc + c, v0);
@@ -467,7 +471,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
           }
         }
         if (EPI == EPI_ARGMAX && live) {
-          const int64_t idx = (int64_t)nt * p.M + m;
+          const int64_t idx = (int64_t)(nt * 2 + chalf) * p.M + m;
           p.part_max[idx] = run_max;
           p.part_arg[idx] = run_arg;
           p.part_sum[idx] = run_sum;
@@ -488,30 +492,41 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   }
 }
 
-// ---- the second step of the fused output head: fold the per-tile statistics of every row and
-// apply threshold unmasking to the working blocks in place (same rule as the sampling kernel:
-// confidence = exp(max - logsumexp); commit where confidence >= threshold; a row of the block
-// that still has masks but committed nothing commits its most confident position) ------------
+// ---- the second step of the fused output head: fold the per-tile statistics of every row into
+// its arg-max and its confidence exp(max - logsumexp) ---------------------------------------------
 __global__ void __launch_bounds__(128) argmax_fold_kernel(const float* __restrict__ part_max,
                                                           const int32_t* __restrict__ part_arg,
-                                                          const float* __restrict__ part_sum, int n_tiles, int M,
+                                                          const float* __restrict__ part_sum, int n_parts, int M,
                                                           int64_t* __restrict__ x0, float* __restrict__ conf) {
-  const int m = blockIdx.x * blockDim.x + threadIdx.x;
+  // one warp per row; the lanes stride over the row's partial results, then fold by shuffles.
+  // Among equal maxima the lowest column wins, whatever order the parts are met in.
+  const int m = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
   if (m >= M) return;
   float mx = -INFINITY, sum = 0.f;
-  int arg = 0;
-  for (int t = 0; t < n_tiles; ++t) {
-    const float pm = part_max[(int64_t)t * M + m], ps = part_sum[(int64_t)t * M + m];
-    if (pm > mx) {
-      sum = sum * __expf(mx - pm) + ps;
+  int arg = 0x7FFFFFFF;
+  auto fold = [&](float pm, int pa, float ps) {
+    if (pm > mx || (pm == mx && pa < arg)) {
+      sum = (mx == -INFINITY ? 0.f : sum * __expf(mx - pm)) + ps;
       mx = pm;
-      arg = part_arg[(int64_t)t * M + m];
-    } else {
+      arg = pa;
+    } else if (pm != -INFINITY) {
       sum += ps * __expf(pm - mx);
     }
+  };
+  for (int t = lane; t < n_parts; t += 32)
+    fold(part_max[(int64_t)t * M + m], part_arg[(int64_t)t * M + m], part_sum[(int64_t)t * M + m]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float pm = __shfl_xor_sync(0xFFFFFFFFu, mx, o);
+    const int pa = __shfl_xor_sync(0xFFFFFFFFu, arg, o);
+    const float ps = __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+    fold(pm, pa, ps);
   }
-  x0[m] = arg;
-  conf[m] = 1.0f / sum;      // exp(max - logsumexp) = 1 / sum exp(x - max)
+  if (lane == 0) {
+    x0[m] = arg;
+    conf[m] = 1.0f / sum;      // exp(max - logsumexp) = 1 / sum exp(x - max)
+  }
 }
 
 // ---------------------------------------------------------------------------------------- host
@@ -519,11 +534,12 @@ struct Tile { int mb, bn, stages, acc_stages; size_t smem; };
 
 // Time of a launch ~ waves of the 74 pairs x k blocks x time of one k block of one pair.  Measured
 // on B200 (bf16, operands streaming from L2): a k block is bound by the operand bytes a CTA pulls
-// from L2 -- about 68 GB/s per SM with one row block per CTA (32 KB stages, 6 of them), 56 GB/s with
-// two (48 KB stages, 4 of them) -- and never faster than its products at the tensor pipe's rate
-// (about 94 ns per 256-row product whatever its N).  A tile whose epilogue cannot overlap the next
-// tile's products (one accumulator stage) pays for it.
-static Tile pick_tile(int M, int N, int want_mb, int want_bn, int bn_multiple) {
+// from L2 -- about 68 GB/s per SM with one row block per CTA (32 KB stages, 6 of them), 57 GB/s with
+// two (48 KB stages, 4 of them) -- and not faster than 0.47 us (one row block) / 0.6 us (two) whatever
+// the tile's width (product issue, commits, the tensor pipe at about 94 ns per 256-row product).
+// A tile whose epilogue cannot overlap the next tile's products (one accumulator stage) pays for it
+// by `exposed` (1.03 for a plain store ... 1.25 for the QKV epilogue).
+static Tile pick_tile(int M, int N, int want_mb, int want_bn, int bn_multiple, double exposed) {
   double best = 1e30;
   Tile out{1, 128, 4, 2, 0};
   for (int mb = 1; mb <= 2; ++mb) {
@@ -540,10 +556,9 @@ static Tile pick_tile(int M, int N, int want_mb, int want_bn, int bn_multiple) {
       const long waves = (tiles + kPairs - 1) / kPairs;
       const int acc_stages = 2 * mb * acc_cols <= 512 ? 2 : 1;
       const int stage_bytes = mb * A_SUB + (bn / 2) * BK * 2;
-      const double load_ns = stage_bytes / (mb == 1 ? 68.0 : 56.0), mma_ns = 4.0 * mb * 94.0;
-      double cost = (double)waves * (load_ns > mma_ns ? load_ns : mma_ns) * (acc_stages == 1 ? 1.03 : 1.0);
-      cost -= 1e-4 * bn;     // among equals: fewer, larger tiles
-      if (cost < best) {
+      const double load_ns = stage_bytes / (mb == 1 ? 68.0 : 57.0), floor_ns = mb == 1 ? 470.0 : 600.0;
+      const double cost = (double)waves * (load_ns > floor_ns ? load_ns : floor_ns) * (acc_stages == 1 ? exposed : 1.0);
+      if (cost < best - 1e-9) {      // candidates run from wide to narrow: among equals the widest stays
         best = cost;
         int stages = (int)((200 * 1024) / stage_bytes);
         if (stages > kMaxStages) stages = kMaxStages;
@@ -577,13 +592,13 @@ template <> struct PromoteG<__half, __half> { using type = __half; };
 template <> struct PromoteG<__nv_bfloat16, __nv_bfloat16> { using type = __nv_bfloat16; };
 
 static int prepare(const void* x, int64_t ldx, const void* w, int M, int N, int K, int dtype, int tile_mb, int tile_bn,
-                   int bn_multiple, Params* p, Tile* tile, CUtensorMap* mx, CUtensorMap* mw) {
+                   double exposed, Params* p, Tile* tile, CUtensorMap* mx, CUtensorMap* mw) {
   if (dtype != ACACHE_BF16 && dtype != ACACHE_F16) return ACACHE_EUNSUPPORTED;
   if (M <= 0 || N <= 0 || K <= 0 || N % 16 != 0 || K % 8 != 0 || ldx % 8 != 0) return ACACHE_EUNSUPPORTED;
   if (!aligned16(x) || !aligned16(w)) return ACACHE_EUNSUPPORTED;
   if ((tile_mb != 0 && tile_mb != 1 && tile_mb != 2) || (tile_bn != 0 && (tile_bn % 16 != 0 || tile_bn < 32 || tile_bn > 256)))
     return ACACHE_EINVAL;
-  *tile = pick_tile(M, N, tile_mb, tile_bn, bn_multiple);
+  *tile = pick_tile(M, N, tile_mb, tile_bn, 16, exposed);
   if (tile->smem == 0) return ACACHE_EUNSUPPORTED;
   p->M = M; p->N = N; p->K = K; p->MB = tile->mb; p->BN = tile->bn; p->stages = tile->stages;
   p->acc_stages = tile->acc_stages;
@@ -610,7 +625,7 @@ extern "C" int acache_linear(const void* x, int64_t x_stride, int n_rows, int in
   gemm::Params p{};
   gemm::Tile tile;
   CUtensorMap mx, mw;
-  const int rc = gemm::prepare(x, x_stride, weight, n_rows, out_features, in_features, dtype, tile_mb, tile_bn, 16, &p,
+  const int rc = gemm::prepare(x, x_stride, weight, n_rows, out_features, in_features, dtype, tile_mb, tile_bn, 1.03, &p,
                                &tile, &mx, &mw);
   if (rc != ACACHE_OK) return rc;
   if (!aligned16(out) || out_stride % 8 != 0 || (bias && !aligned16(bias))) return ACACHE_EUNSUPPORTED;
@@ -630,7 +645,7 @@ extern "C" int acache_linear_swiglu(const void* x, int64_t x_stride, int n_rows,
   gemm::Tile tile;
   CUtensorMap mx, mw;
   const int rc = gemm::prepare(x, x_stride, weight_gate_up, n_rows, 2 * ffn_features, in_features, dtype, tile_mb,
-                               tile_bn, 16, &p, &tile, &mx, &mw);
+                               tile_bn, 1.08, &p, &tile, &mx, &mw);
   if (rc != ACACHE_OK) return rc;
   if (!aligned16(out) || out_stride % 8 != 0) return ACACHE_EUNSUPPORTED;
   p.out = out; p.ldo = out_stride; p.act = act; p.err_flag = err_flag;
@@ -658,8 +673,8 @@ extern "C" int acache_linear_qkv_rope_scatter(const void* x, int64_t x_stride, i
   gemm::Tile tile;
   CUtensorMap mx, mw;
   const int N = (n_heads + 2 * n_kv_heads) * head_dim;
-  const int rc = gemm::prepare(x, x_stride, w_qkv_interleaved, n_rows, N, hidden, dtype, tile_mb, tile_bn, 16, &p, &tile,
-                               &mx, &mw);
+  const int rc = gemm::prepare(x, x_stride, w_qkv_interleaved, n_rows, N, hidden, dtype, tile_mb, tile_bn, 1.25, &p,
+                               &tile, &mx, &mw);
   if (rc != ACACHE_OK) return rc;
   const int re = dtype_bytes(rope_dtype);
   if (!aligned16(out_q) || q_stride % 8 != 0 || !aligned16(k_cache) || !aligned16(v_cache) ||
@@ -686,8 +701,8 @@ extern "C" int acache_linear_qkv_rope_scatter(const void* x, int64_t x_stride, i
 
 extern "C" int64_t acache_linear_argmax_scratch_bytes(int n_rows, int out_features) {
   if (n_rows <= 0 || out_features <= 0) return 0;
-  const int64_t tiles = (out_features + 63) / 64;      // the smallest column tile bounds the tile count
-  return tiles * n_rows * 12;
+  const int64_t parts = 2 * ((out_features + 63) / 64);      // two per column tile; the smallest tile bounds the count
+  return parts * n_rows * 12;
 }
 
 extern "C" int acache_linear_argmax(const void* x, int64_t x_stride, int n_rows, int in_features, const void* weight,
@@ -698,22 +713,22 @@ extern "C" int acache_linear_argmax(const void* x, int64_t x_stride, int n_rows,
   gemm::Params p{};
   gemm::Tile tile;
   CUtensorMap mx, mw;
-  const int rc = gemm::prepare(x, x_stride, weight, n_rows, out_features, in_features, dtype, tile_mb, tile_bn, 16, &p,
+  const int rc = gemm::prepare(x, x_stride, weight, n_rows, out_features, in_features, dtype, tile_mb, tile_bn, 1.1, &p,
                                &tile, &mx, &mw);
   if (rc != ACACHE_OK) return rc;
-  const int64_t n_tiles = (out_features + tile.bn - 1) / tile.bn;
-  if (scratch_bytes < n_tiles * n_rows * 12) return ACACHE_EINVAL;
+  const int64_t n_parts = 2 * ((out_features + tile.bn - 1) / tile.bn);
+  if (scratch_bytes < n_parts * n_rows * 12) return ACACHE_EINVAL;
   p.part_max = (float*)scratch;
-  p.part_arg = (int32_t*)((float*)scratch + n_tiles * n_rows);
-  p.part_sum = (float*)scratch + 2 * n_tiles * n_rows;
+  p.part_arg = (int32_t*)((float*)scratch + n_parts * n_rows);
+  p.part_sum = (float*)scratch + 2 * n_parts * n_rows;
   p.err_flag = err_flag;
   cudaStream_t st = (cudaStream_t)stream;
   int lrc;
   if (dtype == ACACHE_BF16) lrc = gemm::launch<__nv_bfloat16, float, float, gemm::EPI_ARGMAX>(mx, mw, p, tile, st);
   else lrc = gemm::launch<__half, float, float, gemm::EPI_ARGMAX>(mx, mw, p, tile, st);
   if (lrc != ACACHE_OK) return lrc;
-  gemm::argmax_fold_kernel<<<(n_rows + 127) / 128, 128, 0, st>>>(p.part_max, p.part_arg, p.part_sum, (int)n_tiles,
-                                                                 n_rows, x0, confidence);
+  gemm::argmax_fold_kernel<<<(n_rows + 3) / 4, 128, 0, st>>>(p.part_max, p.part_arg, p.part_sum, (int)n_parts, n_rows,
+                                                             x0, confidence);
   ACACHE_LAUNCH_CHECK();
   return ACACHE_OK;
 }

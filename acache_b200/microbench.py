@@ -256,6 +256,86 @@ def gemm_sweep(iters=10, shapes=None, tiles=None):
     _lib.check_device_errors()
 
 
+def fused_sweep(iters=10):
+    """The fused projections of a block against the library GEMM followed by the separate kernel,
+    at the decode (512 rows) and refresh (2304 rows) sizes of the LLaDA-8B workload; back-to-back
+    launches over rotating weight copies, one event pair around all of them."""
+    import torch.nn.functional as F
+
+    D, nh, hkv, hidden, ffn, vocab = 128, 32, 32, 4096, 12288, 126464
+    cos, sin = build_rope_table(2048, D, 500000.0, torch.float32, DEV)
+
+    def timeit(fn, ws):
+        for w in ws[:2]:
+            fn(w)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            for w in ws:
+                fn(w)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / (iters * len(ws))
+
+    for M in (512, 2304):
+        x = torch.randn(M, hidden, device=DEV, dtype=torch.bfloat16)
+        pos = torch.randint(0, 1300, (M,), device=DEV)
+        nb = M // 256 + 2
+        kc = torch.zeros(nb, 256, hkv, D, device=DEV, dtype=torch.bfloat16)
+        vc = torch.zeros_like(kc)
+        slots = torch.randperm(nb * 256, device=DEV)[:M].to(torch.int32)
+        # --- QKV
+        ws = [torch.randn((nh + 2 * hkv) * D, hidden, device=DEV, dtype=torch.bfloat16) * hidden ** -0.5 for _ in range(8)]
+
+        def lib_qkv(w):
+            qkv = F.linear(x, w)
+            q, k, v = (qkv[:, : nh * D].view(M, nh, D), qkv[:, nh * D: (nh + hkv) * D].view(M, hkv, D),
+                       qkv[:, (nh + hkv) * D:].view(M, hkv, D))
+            ops.rope_store(q, k, v, pos, cos, sin, kc, vc, slots)
+
+        t_lib = timeit(lib_qkv, ws)
+        print(f"M={M} qkv + rope + scatter: library GEMM + kernel {t_lib:7.1f} us", flush=True)
+        for tile in [(0, 0), (1, 256), (2, 176), (1, 176), (2, 128)]:
+            ops.GEMM_TILE = tile
+            t = timeit(lambda w: ops.linear_qkv_rope_scatter(x, w, None, nh, hkv, D, pos, cos, sin, kc, vc, slots), ws)
+            print(f"    fused, tile {tile}: {t:7.1f} us  {t_lib / t:5.2f}x", flush=True)
+        ops.GEMM_TILE = (0, 0)
+        del ws
+        # --- gate / up
+        ws = [torch.randn(2 * ffn, hidden, device=DEV, dtype=torch.bfloat16) * hidden ** -0.5 for _ in range(4)]
+        t_lib = timeit(lambda w: ops.act_mul_halves(F.linear(x, w), "silu"), ws)
+        print(f"M={M} gate/up + activation: library GEMM + kernel {t_lib:7.1f} us", flush=True)
+        for tile in [(0, 0), (1, 256), (1, 224), (2, 176), (2, 128)]:
+            ops.GEMM_TILE = tile
+            t = timeit(lambda w: ops.linear_swiglu(x, w, "silu"), ws)
+            print(f"    fused, tile {tile}: {t:7.1f} us  {t_lib / t:5.2f}x", flush=True)
+        ops.GEMM_TILE = (0, 0)
+        del ws
+        torch.cuda.empty_cache()
+    # --- output head on 512 rows
+    M = 512
+    x = torch.randn(M, hidden, device=DEV, dtype=torch.bfloat16)
+    ws = [torch.randn(vocab, hidden, device=DEV, dtype=torch.bfloat16) * hidden ** -0.5 for _ in range(2)]
+    blocks = torch.full((16, 32), 126336, dtype=torch.int64, device=DEV)
+
+    def lib_head(w):
+        ops.transfer_tokens(F.linear(x, w), blocks.clone(), 126336, 0.9)
+
+    def own_head(w):
+        x0, conf = ops.linear_argmax(x, w)
+        ops.apply_transfer(x0, conf, blocks.clone(), 126336, 0.9)
+
+    t_lib = timeit(lib_head, ws)
+    print(f"M={M} output head + unmasking: library GEMM + kernels {t_lib:7.1f} us", flush=True)
+    for tile in [(0, 0), (2, 256), (1, 256), (2, 128)]:
+        ops.GEMM_TILE = tile
+        t = timeit(own_head, ws)
+        print(f"    fused, tile {tile}: {t:7.1f} us  {t_lib / t:5.2f}x", flush=True)
+    ops.GEMM_TILE = (0, 0)
+    _lib.check_device_errors()
+
+
 CASES = {
     # name: (builder, bound)
     "relocate_cfg1_fp32": (lambda: case_relocate(2, 512, 8, 128, 4, torch.float32, 1024), "hbm"),
@@ -327,10 +407,14 @@ def main(argv=None):
     ap.add_argument("names", nargs="*")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--fused-sweep", action="store_true", help="fused projections against library GEMM + separate kernel")
     ap.add_argument("--gemm-sweep", action="store_true", help="projection GEMMs at several tile shapes against the library")
     args = ap.parse_args(argv)
     if args.gemm_sweep:
         gemm_sweep(args.iters)
+        return
+    if args.fused_sweep:
+        fused_sweep(args.iters)
         return
     names = args.names or list(CASES)
     for n in names:

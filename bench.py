@@ -352,6 +352,11 @@ def run_ours(args):
         from acache_b200.model import modeling_common
 
         modeling_common.set_own_gemm(args.projections == "own")
+        if args.projections not in ("own", "library"):
+            on = set(args.projections.split(","))
+            assert on <= {"qkv", "gate_up", "dense", "head"}, on
+            modeling_common.OWN_QKV, modeling_common.OWN_GATE_UP = "qkv" in on, "gate_up" in on
+            modeling_common.OWN_DENSE, modeling_common.OWN_HEAD = "dense" in on, "head" in on
 
     wl = dict(WORKLOADS[args.workload])
     if args.batch:
@@ -623,8 +628,10 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the architecture")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-subpaths", action="store_true")
-    ap.add_argument("--projections", default="default", choices=["default", "own", "library"],
-                    help="debug only: every projection on this package's GEMM kernels / on the library GEMM")
+    ap.add_argument("--projections", default="default",
+                    help="debug only: 'own' / 'library' = every projection on this package's GEMM kernels / on the "
+                         "library GEMM; or a comma list out of qkv,gate_up,dense,head naming the ones on this "
+                         "package's kernels")
     ap.add_argument("--mode", default="acache", choices=["acache", "dkv_acache", "dual_cache"],
                     help="acache = the benchmark; the other serving modes of the engine on the same workload")
     args = ap.parse_args()
