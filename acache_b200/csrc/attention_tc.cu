@@ -31,14 +31,14 @@
 //
 // Shared-span grouping (SPLIT = true, block decode): when every request has at most 32
 // virtual rows and the first shared_kv_lens[b] entries of all requests name the same slots
-// (up to holes), the keys are split in two kinds of work items:
-//   A  (4 consecutive requests, KV head): warp w holds the rows of request 4a+w; the shared
-//      span is staged ONCE for the four requests (slot = the union of their entries), each
-//      warp masks its own request's holes;
-//   B  (request, KV head): the request's remaining keys.
-// Each item leaves its unnormalised O, reference maximum and row sum in scratch, then takes a
-// ticket per (request, KV head); the second arrival folds the other part into its own and
-// writes the output, so there is no wait between CTAs and no second kernel.
+// (up to holes), one CTA = (4 consecutive requests, KV head): warp w owns the 32 rows of request
+// 4a+w, so the 128 rows of every product are real.  The CTA first walks the shared span, staged
+// ONCE for the four requests (slot = the union of their entries, each warp masks its own
+// request's holes), then the remaining keys of request 0, of request 1, ...: a tile of request r
+// is dead for the other three warps (their P rows are zero).  The products of a 64-key tile
+// cost the same whether 32 or 128 of their rows are real, so the span costs a quarter of the
+// tensor-core instructions and of the L2 -> shared-memory traffic, and a launch has a quarter
+// of the CTAs, each paying its set-up once.
 // Every mbarrier wait is bounded; on expiry the kernel raises the error flag, frees its
 // TMEM and returns.
 #include <type_traits>
@@ -60,12 +60,8 @@ constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kColS = 0, kColO = 128;
 
 struct SplitArgs {
-  int n_items_a;        // work items of kind A = ceil(batch / GROUP) * n_kv_heads
+  int n_items_a;        // work items = ceil(batch / GROUP) * n_kv_heads
   int batch;
-  int64_t total_rows;   // total_q * n_heads
-  int32_t* tickets;     // [batch * n_kv_heads], even between launches
-  float* part_ml;       // [2][total_rows][2]  reference maximum (log2 domain) and row sum
-  float* part_o;        // [2][total_rows][D]  unnormalised accumulator
 };
 
 template <typename T, typename TR, typename TC, int D, bool KEYSIDE, bool SPLIT, int COPIES, bool LOADERS>
@@ -105,7 +101,7 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
   int* rq_shift = rq_kv0 + GROUP;
   volatile int* give_up = rq_shift + GROUP;   // set by the first role whose bounded wait runs out
   // rows of a tile that take no part, published by the loader warps for the row-owning warps
-  volatile uint32_t* dead_ring = reinterpret_cast<volatile uint32_t*>(give_up + 1);   // [4 tiles][2]
+  volatile uint32_t* dead_ring = reinterpret_cast<volatile uint32_t*>(give_up + 1);   // [4 tiles][4 warps][2]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool is_loader = LOADERS && warp >= 5;
@@ -116,18 +112,11 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
 
   // ---- which work item ----------------------------------------------------------------------
   int b, kvh, m0;
-  bool kind_a = false;
+  const bool kind_a = SPLIT;       // an item of four requests
   if (SPLIT) {
     m0 = 0;
-    if ((int)blockIdx.x < sp.n_items_a) {
-      kind_a = true;
-      b = ((int)blockIdx.x / n_kv_heads) * GROUP;
-      kvh = (int)blockIdx.x % n_kv_heads;
-    } else {
-      const int x = (int)blockIdx.x - sp.n_items_a;
-      b = x / n_kv_heads;
-      kvh = x % n_kv_heads;
-    }
+    b = ((int)blockIdx.x / n_kv_heads) * GROUP;
+    kvh = (int)blockIdx.x % n_kv_heads;
   } else {
     b = blockIdx.y;
     kvh = blockIdx.z;
@@ -164,10 +153,20 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
         if (tid == 0 && err_flag) atomicExch(err_flag, 7);
       }
   }
-  // tiles of the first run, tiles of the second run (an item of kind A has only the first,
-  // an item of kind B only the second)
-  const int nt0 = (SPLIT && !kind_a) ? 0 : (n_shared + BN - 1) / BN;
-  const int nt1 = (SPLIT && kind_a) ? 0 : (kv_len - n_shared + BN - 1) / BN;
+  // tiles of the first run, then tiles of the second run (of a group: of its first request's
+  // second run, then its second request's, ...; t0r[r] = first tile of request r's second run)
+  const int nt0 = (n_shared + BN - 1) / BN;
+  int t0r[GROUP + 1], klen[GROUP];
+  t0r[0] = nt0;
+#pragma unroll
+  for (int r = 0; r < GROUP; ++r) {
+    int kl = 0;
+    if (r == 0) kl = kv_len;
+    else if (SPLIT && r < n_req) kl = max(cu_k[b + r + 1] - cu_k[b + r], 0);
+    klen[r] = kl;
+    t0r[r + 1] = t0r[r] + ((r == 0 || SPLIT) ? (max(kl - n_shared, 0) + BN - 1) / BN : 0);
+  }
+  const int nt1 = t0r[GROUP] - nt0;
   const int n_tiles = nt0 + nt1;
 
   // COPIES = 4 (requests of at most 32 virtual rows, block decode): the 32 rows are staged four
@@ -209,7 +208,7 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
   const int64_t q_row = (int64_t)rq_q0[ri] + qi;
   T* out_row = out + q_row * o_stride + (int64_t)head * D;
 
-  if (!SPLIT && n_tiles == 0) {  // no keys: zeros
+  if (n_tiles == 0) {  // no keys: zeros
     if (row_ok && tid < NT) {
       for (int c = 0; c < CH; ++c) *reinterpret_cast<uint4*>(out_row + c * (16 / sizeof(T))) = make_uint4(0, 0, 0, 0);
     }
@@ -264,9 +263,29 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
       }
     }
   };
-  auto tile_span = [&](int i, int& j0, int& j_end) {
-    if (i < nt0) { j0 = i * BN; j_end = n_shared; }
-    else { j0 = n_shared + (i - nt0) * BN; j_end = kv_len; }
+  // keys [j0, j_end) of the tile's run; rr = the one request of the item the tile belongs to, -1 = all
+  auto tile_span = [&](int i, int& j0, int& j_end, int& rr) {
+    if (i < nt0) {
+      j0 = i * BN;
+      j_end = n_shared;
+      rr = -1;
+      return;
+    }
+    rr = 0;
+    if (SPLIT) {
+#pragma unroll
+      for (int r = 1; r < GROUP; ++r)
+        if (i >= t0r[r]) rr = r;
+    }
+    int first = nt0, len = kv_len;
+#pragma unroll
+    for (int r = 0; r < GROUP; ++r)
+      if (r == rr) {
+        first = t0r[r];
+        len = klen[r];
+      }
+    j0 = n_shared + (i - first) * BN;
+    j_end = len;
   };
   // ---- slot lookup -----------------------------------------------------------------------
   // Entry codes: >= 0 a slot, -1 a key that takes no part, -2 an entry outside the cache
@@ -278,8 +297,8 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
   // looked at before the end of the iteration, so no warp waits for them.
   constexpr int NR = SPLIT ? GROUP : 1;   // requests whose entries a warp reads
   auto fetch_raw = [&](int i, int32_t (&raw)[NR][2]) {
-    int j0, j_end;
-    tile_span(i, j0, j_end);
+    int j0, j_end, rr;
+    tile_span(i, j0, j_end, rr);
 #pragma unroll
     for (int r = 0; r < NR; ++r) {
       const int first = (SPLIT && kind_a) ? rq_kv0[r] : kv0;
@@ -287,7 +306,8 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
       for (int h = 0; h < 2; ++h) {
         const int j = j0 + h * 32 + lane;
         int32_t v = 0;
-        if (j < j_end && r < n_req) v = slot_map ? slot_map[first + j] : block_tables[(int64_t)b * table_stride + j / block_size];
+        if (j < j_end && r < n_req && (rr < 0 || rr == r))
+          v = slot_map ? slot_map[first + j] : block_tables[(int64_t)b * table_stride + j / block_size];
         raw[r][h] = v;
       }
     }
@@ -296,17 +316,19 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
   // dead: the rows this warp's own request may not see
   auto interpret = [&](int i, const int32_t (&raw)[NR][2], int32_t& e0, int32_t& e1, uint32_t& dead_lo,
                        uint32_t& dead_hi) {
-    int j0, j_end;
-    tile_span(i, j0, j_end);
+    int j0, j_end, rr;
+    tile_span(i, j0, j_end, rr);
     int32_t uni[2] = {-3, -3}, own[2] = {-3, -3};
     bool clash = false;
+    // the request whose view of the tile this warp works out (a group: one request per warp)
+    const int own_r = (SPLIT && kind_a) ? ((LOADERS ? warp - 5 : warp) & 3) : 0;
 #pragma unroll
     for (int r = 0; r < NR; ++r) {
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int j = j0 + h * 32 + lane;
         int32_t code = -3;
-        if (j < j_end && r < n_req) {
+        if (j < j_end && r < n_req && (rr < 0 || rr == r)) {
           int64_t slot = raw[r][h];
           if (slot_map) {
             code = slot == -1 ? -1 : ((slot < 0 || slot >= num_slots) ? -2 : (int32_t)slot);
@@ -317,7 +339,7 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
         }
         clash |= code >= 0 && uni[h] >= 0 && code != uni[h];
         uni[h] = max(uni[h], code);
-        if (r == ((SPLIT && kind_a) ? warp : 0)) own[h] = code;
+        if (r == own_r) own[h] = code;
       }
     }
     e0 = uni[0];
@@ -331,8 +353,8 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
   };
   auto load_rows = [&](int i, int32_t e0, int32_t e1, const bool want_k, const bool want_v) {
     const uint32_t kb = smem_u32(sK) + (i & 1) * KV_BYTES, vb = smem_u32(sV) + (i & 1) * KV_BYTES;
-    int j0, j_end;
-    tile_span(i, j0, j_end);
+    int j0, j_end, rr_unused;
+    tile_span(i, j0, j_end, rr_unused);
     const int c = my_c;
 #pragma unroll
     for (int it = 0; it < ITER; ++it) {
@@ -480,6 +502,14 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
   };
   auto softmax_half = [&](const bool second, const int i) {
     if (!warp_live) return;  // warps whose 32 rows are all padding skip the softmax (their P rows stay zero)
+    if (SPLIT && dead_lo == 0xFFFFFFFFu && dead_hi == 0xFFFFFFFFu) {
+      // a tile of another request of the group: no key of it counts for these rows
+      if (second) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(sP + tid * 128 + (c << 4)) = make_uint4(0, 0, 0, 0);
+      }
+      return;
+    }
     if constexpr (COPIES > 1) {
       if (spread) {
         if (!second) softmax_scores(std::integral_constant<int, BN / COPIES>{}, warp * (BN / COPIES), i);
@@ -543,10 +573,11 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
     }
   } else if (n_tiles > 0 && (!LOADERS || is_loader)) {
     // ---- the threads that stage K/V (and, without loader warps, also own the rows) ---------
+    // every loader warp publishes the mask of the request it looks at (all the same unless a group)
     auto publish_dead = [&](int tile, uint32_t lo, uint32_t hi) {
-      if (LOADERS && ltid == 0) {
-        dead_ring[(tile & 3) * 2] = lo;
-        dead_ring[(tile & 3) * 2 + 1] = hi;
+      if (LOADERS && lane == 0) {
+        dead_ring[((tile & 3) * 4 + ((warp - 5) & 3)) * 2] = lo;
+        dead_ring[((tile & 3) * 4 + ((warp - 5) & 3)) * 2 + 1] = hi;
       }
     };
     const bool start_rotated = query_side && nt0 > 0;
@@ -649,8 +680,8 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
     for (int i = 0; i < n_tiles; ++i) {
       ok = wait_bar(bar_s + (i & 1) * 8, (uint32_t)((i >> 1) & 1)) && ok;   // also: the tile's dead rows are published
       tc_fence_after();
-      dead_lo = dead_ring[(i & 3) * 2];
-      dead_hi = dead_ring[(i & 3) * 2 + 1];
+      dead_lo = dead_ring[((i & 3) * 4 + warp) * 2];
+      dead_hi = dead_ring[((i & 3) * 4 + warp) * 2 + 1];
       softmax_half(false, i);
       // the previous P V product must be done before O is rescaled or P overwritten
       if (i > 0) ok = wait_bar(bar_o, (uint32_t)((i - 1) & 1)) && ok;
@@ -735,59 +766,21 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
     const int r_qi = r_ok ? r / g : 0, r_head = kvh * g + (r_ok ? r % g : 0);
     const int64_t r_qrow = (int64_t)rq_q0[0] + r_qi;
     T* r_out = out + r_qrow * o_stride + (int64_t)r_head * D + qd * (D / 4);
-    float a_own = l_all > 0.f ? 1.0f / l_all : 0.f;
-    float a_oth = 0.f;
-    const float* ot_o = nullptr;
-    bool write_out = true;
-    if (SPLIT) {
-      // publish this part, take the ticket of (request, KV head); the second arrival folds both
-      const int64_t grow = r_qrow * n_heads + r_head;
-      float4* my_o = reinterpret_cast<float4*>(sp.part_o + ((int64_t)1 * sp.total_rows + grow) * D + qd * (D / 4));
-      if (r_ok) {
-#pragma unroll
-        for (int k = 0; k < QF4; ++k) __stcg(my_o + k, acc[k]);
-        if (qd == 0) __stcg(reinterpret_cast<float2*>(sp.part_ml + ((int64_t)1 * sp.total_rows + grow) * 2), make_float2(m_all, l_all));
-      }
-      __threadfence();
-      rows_sync();
-      int* ticket_box = reinterpret_cast<int*>(xm);   // xm is no longer read
-      if (tid == 0) *ticket_box = atomicAdd(sp.tickets + (int64_t)b * n_kv_heads + kvh, 1);
-      rows_sync();
-      write_out = (*ticket_box & 1) != 0;             // the other part is already in scratch
-      if (write_out) {
-        __threadfence();
-        ot_o = sp.part_o + ((int64_t)0 * sp.total_rows + grow) * D + qd * (D / 4);
-        float2 ml = make_float2(-INFINITY, 0.f);
-        if (r_ok) ml = __ldcg(reinterpret_cast<const float2*>(sp.part_ml + ((int64_t)0 * sp.total_rows + grow) * 2));
-        const float m_both = fmaxf(m_all, ml.x);
-        const float w1 = m_all == -INFINITY ? 0.f : ex2(m_all - m_both);
-        const float w0 = ml.x == -INFINITY ? 0.f : ex2(ml.x - m_both);
-        // rounded one by one, no fused multiply-add: the same whichever part arrives second
-        const float l_both = __fadd_rn(__fmul_rn(l_all, w1), __fmul_rn(ml.y, w0));
-        const float inv = l_both > 0.f ? 1.0f / l_both : 0.f;
-        a_own = w1 * inv;
-        a_oth = w0 * inv;
-      }
-    }
-    if (write_out && r_ok) {
+    const float a_own = l_all > 0.f ? 1.0f / l_all : 0.f;
+    if (r_ok) {
 #pragma unroll
       for (int k = 0; k < QF4; k += 2) {
-        float4 x0 = acc[k], x1 = acc[k + 1];
-        float4 y0 = make_float4(0.f, 0.f, 0.f, 0.f), y1 = y0;
-        if (SPLIT) {
-          y0 = __ldcg(reinterpret_cast<const float4*>(ot_o) + k);
-          y1 = __ldcg(reinterpret_cast<const float4*>(ot_o) + k + 1);
-        }
-        auto fold = [&](float own, float oth) { return __fadd_rn(__fmul_rn(own, a_own), __fmul_rn(oth, a_oth)); };
+        const float4 x0 = acc[k], x1 = acc[k + 1];
         uint4 w;
-        w.x = pack2<T>(fold(x0.x, y0.x), fold(x0.y, y0.y));
-        w.y = pack2<T>(fold(x0.z, y0.z), fold(x0.w, y0.w));
-        w.z = pack2<T>(fold(x1.x, y1.x), fold(x1.y, y1.y));
-        w.w = pack2<T>(fold(x1.z, y1.z), fold(x1.w, y1.w));
+        w.x = pack2<T>(x0.x * a_own, x0.y * a_own);
+        w.y = pack2<T>(x0.z * a_own, x0.w * a_own);
+        w.z = pack2<T>(x1.x * a_own, x1.y * a_own);
+        w.w = pack2<T>(x1.z * a_own, x1.w * a_own);
         *reinterpret_cast<uint4*>(r_out + k * 4) = w;
       }
     }
-  } else if (!SPLIT) {
+  } else {
+    // thread = row: divide by the row sum and write (a group: warp w writes request w's rows)
     const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
     uint32_t o[32];
 #pragma unroll 1
@@ -806,85 +799,6 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
         }
       }
     }
-  } else if (warp_live) {
-    // ---- publish this part, take a ticket, the second arrival folds both parts ------------------
-    // (one party = one warp = the rows of one request and KV head)
-    const int side = kind_a ? 0 : 1;
-    const int64_t grow = q_row * n_heads + head;           // row of the [total_q, n_heads] grid
-    float* my_o = sp.part_o + ((int64_t)side * sp.total_rows + grow) * D;
-    float* my_ml = sp.part_ml + ((int64_t)side * sp.total_rows + grow) * 2;
-    const bool have = n_tiles > 0;                          // otherwise O was never written: it counts as 0
-    uint32_t o[32];
-#pragma unroll 1
-    for (int c0 = 0; c0 < D; c0 += 32) {
-      if (have) {
-        tmem_ld32(t_lane + kColO + c0, o);
-        tmem_wait_ld();
-      } else {
-#pragma unroll
-        for (int c = 0; c < 32; ++c) o[c] = 0u;
-      }
-      if (row_ok) {
-#pragma unroll
-        for (int c = 0; c < 32; c += 4)
-          __stcg(reinterpret_cast<uint4*>(my_o + c0 + c), make_uint4(o[c], o[c + 1], o[c + 2], o[c + 3]));
-      }
-    }
-    if (row_ok) __stcg(reinterpret_cast<float2*>(my_ml), make_float2(m_ref, l_sum));
-    __threadfence();
-    __syncwarp();
-    int ticket = 0;
-    if (lane == 0) ticket = atomicAdd(sp.tickets + (int64_t)(b + ri) * n_kv_heads + kvh, 1);
-    ticket = __shfl_sync(0xFFFFFFFFu, ticket, 0);
-    if (ticket & 1) {  // the other part is already in scratch
-      __threadfence();
-      const float* ot_o = sp.part_o + ((int64_t)(1 - side) * sp.total_rows + grow) * D;
-      const float* ot_ml = sp.part_ml + ((int64_t)(1 - side) * sp.total_rows + grow) * 2;
-      float2 ml = make_float2(-INFINITY, 0.f);
-      if (row_ok) ml = __ldcg(reinterpret_cast<const float2*>(ot_ml));
-      const float m_all = fmaxf(m_ref, ml.x);
-      const float w_own = m_ref == -INFINITY ? 0.f : ex2(m_ref - m_all);
-      const float w_oth = ml.x == -INFINITY ? 0.f : ex2(ml.x - m_all);
-      // products and sums are rounded one by one (no fused multiply-add): the result is the same
-      // whichever part arrives second
-      const float l_all = __fadd_rn(__fmul_rn(l_sum, w_own), __fmul_rn(ml.y, w_oth));
-      const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
-      const float a_own = w_own * inv, a_oth = w_oth * inv;
-      auto fold = [&](uint32_t own, float oth) { return __fadd_rn(__fmul_rn(__uint_as_float(own), a_own), __fmul_rn(oth, a_oth)); };
-      // the other part's row is fetched one 32-column chunk ahead of its use
-      float4 x[8], xn[8];
-      auto fetch_other = [&](int c0, float4 (&dst)[8]) {
-#pragma unroll
-        for (int c = 0; c < 8; ++c)
-          dst[c] = row_ok ? __ldcg(reinterpret_cast<const float4*>(ot_o + c0 + 4 * c)) : make_float4(0.f, 0.f, 0.f, 0.f);
-      };
-      fetch_other(0, x);
-#pragma unroll 1
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        if (c0 + 32 < D) fetch_other(c0 + 32, xn);
-        if (have) {
-          tmem_ld32(t_lane + kColO + c0, o);
-          tmem_wait_ld();
-        } else {
-#pragma unroll
-          for (int c = 0; c < 32; ++c) o[c] = 0u;
-        }
-        if (row_ok) {
-#pragma unroll
-          for (int c = 0; c < 32; c += 8) {
-            const float4 xa = x[c / 4], xb = x[c / 4 + 1];
-            uint4 w;
-            w.x = pack2<T>(fold(o[c], xa.x), fold(o[c + 1], xa.y));
-            w.y = pack2<T>(fold(o[c + 2], xa.z), fold(o[c + 3], xa.w));
-            w.z = pack2<T>(fold(o[c + 4], xb.x), fold(o[c + 5], xb.y));
-            w.w = pack2<T>(fold(o[c + 6], xb.z), fold(o[c + 7], xb.w));
-            *reinterpret_cast<uint4*>(out_row + c0 + c) = w;
-          }
-        }
-#pragma unroll
-        for (int c = 0; c < 8; ++c) x[c] = xn[c];
-      }
-    }
   }
   cp_async_wait<0>();
   tc_fence_before();
@@ -901,7 +815,7 @@ template <> struct PromoteT<__nv_bfloat16, __nv_bfloat16> { using type = __nv_bf
 template <typename T, typename TR, int D>
 static int launch(const AttnArgs& a, const SplitArgs* split) {
   using TC = typename PromoteT<T, TR>::type;
-  constexpr size_t smem = BM * D * sizeof(T) + 4 * BN * D * sizeof(T) + BM * BN * sizeof(T) + 256;
+  constexpr size_t smem = BM * D * sizeof(T) + 4 * BN * D * sizeof(T) + BM * BN * sizeof(T) + 512;
   const int g = a.n_heads / a.n_kv_heads;
   const bool relocate = a.shared_prefix_len > 0 && a.affix_shifts != nullptr;
   const bool query_side = relocate && a.shared_kv_lens != nullptr;
@@ -910,7 +824,7 @@ static int launch(const AttnArgs& a, const SplitArgs* split) {
   dim3 grid((a.max_q * g + BM - 1) / BM, a.batch, a.n_kv_heads);
   if (split) {
     sp = *split;
-    grid = dim3(sp.n_items_a + a.batch * a.n_kv_heads, 1, 1);
+    grid = dim3(sp.n_items_a, 1, 1);
   }
 #define ACACHE_TC_LAUNCH(KS, SPL, CP, LD)                                                                             \
   do {                                                                                                                \
@@ -925,7 +839,7 @@ static int launch(const AttnArgs& a, const SplitArgs* split) {
   // requests of at most 32 virtual rows (block decode): spread the softmax over the four warps
   // and give the K/V staging to four more warps
   const bool small_rows = a.max_q * g <= 32;
-  if (split) ACACHE_TC_LAUNCH(false, true, 4, false);
+  if (split) ACACHE_TC_LAUNCH(false, true, 1, true);
   else if (key_side) ACACHE_TC_LAUNCH(true, false, 1, false);
   else if (small_rows) ACACHE_TC_LAUNCH(false, false, 4, true);
   else ACACHE_TC_LAUNCH(false, false, 1, false);
@@ -964,33 +878,23 @@ int attention_tc_dispatch(const AttnArgs& a, int dtype, int rope_dtype) {
   return tc::by_dtype(a, dtype, rope_dtype, nullptr);
 }
 
-// Scratch of the shared-span grouping: tickets (kept even between launches, so the buffer is
-// zeroed once and then reused), then per part and output row the reference maximum, the row
-// sum and the unnormalised accumulator in fp32.
-static int64_t split_ticket_bytes(int batch, int n_kv_heads) {
-  return (((int64_t)batch * n_kv_heads * 4 + 255) / 256) * 256;
-}
+// The grouped form keeps nothing between its CTAs and needs no scratch.
 int64_t attention_split_scratch_bytes(int total_q, int n_heads, int head_dim, int batch, int n_kv_heads) {
-  if (total_q <= 0 || n_heads <= 0 || head_dim <= 0 || batch <= 0 || n_kv_heads <= 0) return 0;
-  return split_ticket_bytes(batch, n_kv_heads) + (int64_t)2 * total_q * n_heads * (head_dim + 2) * 4;
+  (void)total_q; (void)n_heads; (void)head_dim; (void)batch; (void)n_kv_heads;
+  return 0;
 }
 
 // Shared-span grouping; declines what it does not cover (also: relocation on the key side,
 // block tables, more than 32 virtual rows per request, no shared_kv_lens).
 int attention_split_dispatch(const AttnArgs& a, int dtype, int rope_dtype, int total_q, void* scratch,
                              int64_t scratch_bytes) {
+  (void)total_q; (void)scratch; (void)scratch_bytes;
   if (!a.slot_map || !a.shared_kv_lens) return ACACHE_EUNSUPPORTED;
   if (a.n_kv_heads <= 0 || a.n_heads % a.n_kv_heads != 0) return ACACHE_EINVAL;
   if (a.max_q * (a.n_heads / a.n_kv_heads) > 32) return ACACHE_EUNSUPPORTED;
-  const int64_t need = attention_split_scratch_bytes(total_q, a.n_heads, a.head_dim, a.batch, a.n_kv_heads);
-  if (!scratch || scratch_bytes < need || !aligned16(scratch)) return ACACHE_EINVAL;
   tc::SplitArgs sp;
   sp.n_items_a = ((a.batch + tc::GROUP - 1) / tc::GROUP) * a.n_kv_heads;
   sp.batch = a.batch;
-  sp.total_rows = (int64_t)total_q * a.n_heads;
-  sp.tickets = reinterpret_cast<int32_t*>(scratch);
-  sp.part_ml = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + split_ticket_bytes(a.batch, a.n_kv_heads));
-  sp.part_o = sp.part_ml + (int64_t)2 * sp.total_rows * 2;
   return tc::by_dtype(a, dtype, rope_dtype, &sp);
 }
 

@@ -207,6 +207,35 @@ def case_qkv(n, hidden, nh, hkv, D, fused):
     return fn, dict(flops=2.0 * n * hidden * (nh + 2 * hkv) * D, bytes=2.0 * (nh + 2 * hkv) * D * hidden)
 
 
+def case_linear(kind, M, K=4096, nh=32, hkv=32, D=128, ffn=12288, vocab=126464):
+    """One fused projection of this package at the LLaDA-8B sizes: "qkv" (+ RoPE + cache scatter),
+    "gate_up" (+ gated activation), "head" (+ arg-max statistics), "plain" (K -> 4096)."""
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    if kind == "qkv":
+        N = (nh + 2 * hkv) * D
+        w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * K ** -0.5
+        pos = torch.randint(0, 1300, (M,), device=DEV)
+        cos, sin = build_rope_table(2048, D, 500000.0, torch.float32, DEV)
+        nb = M // 256 + 2
+        kc = torch.zeros(nb, 256, hkv, D, device=DEV, dtype=torch.bfloat16)
+        vc = torch.zeros_like(kc)
+        slots = torch.randperm(nb * 256, device=DEV)[:M].to(torch.int32)
+        fn = lambda: ops.linear_qkv_rope_scatter(x, w, None, nh, hkv, D, pos, cos, sin, kc, vc, slots)
+    elif kind == "gate_up":
+        N = 2 * ffn
+        w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * K ** -0.5
+        fn = lambda: ops.linear_swiglu(x, w, "silu")
+    elif kind == "head":
+        N = vocab
+        w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * K ** -0.5
+        fn = lambda: ops.linear_argmax(x, w)
+    else:
+        N = 4096
+        w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * K ** -0.5
+        fn = lambda: ops.linear(x, w)
+    return fn, dict(flops=2.0 * M * N * K, bytes=2.0 * N * K + 2.0 * M * K)
+
+
 def gemm_sweep(iters=10, shapes=None, tiles=None):
     """Projection shapes of the served models: this package's CTA-pair GEMM at several tile
     shapes against the library GEMM.  Back-to-back launches over 8 rotating weight copies (so the
@@ -363,6 +392,12 @@ CASES = {
     "qkv_cublas_refresh_llada": (lambda: case_qkv(2304, 4096, 32, 32, 128, False), "tensor"),
     "qkv_fused_decode_dream": (lambda: case_qkv(1024, 3584, 28, 4, 128, True), "tensor"),
     "qkv_cublas_decode_dream": (lambda: case_qkv(1024, 3584, 28, 4, 128, False), "tensor"),
+    "linear_qkv_decode_llada": (lambda: case_linear("qkv", 512), "tensor"),
+    "linear_qkv_refresh_llada": (lambda: case_linear("qkv", 2304), "tensor"),
+    "linear_gate_up_decode_llada": (lambda: case_linear("gate_up", 512), "tensor"),
+    "linear_gate_up_refresh_llada": (lambda: case_linear("gate_up", 2304), "tensor"),
+    "linear_head_decode_llada": (lambda: case_linear("head", 512), "tensor"),
+    "linear_plain_decode_llada": (lambda: case_linear("plain", 512), "tensor"),
     "act_mul_decode_llada": (lambda: case_act_mul(512, 12288), "hbm"),
     "add_rmsnorm_decode_llada": (lambda: case_add_rmsnorm(512, 4096), "hbm"),
     "topk_cfg1": (lambda: case_topk(4, 512, 103), "latency"),

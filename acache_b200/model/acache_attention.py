@@ -91,14 +91,11 @@ def _attention_call(q, out, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, max_q,
         rc, rs, rstride, rrows, rdt = _rope_args(rope_cos, rope_sin)
         with _lib.timed("attention_decode" if ATTENTION_PHASE == "decode" else "attention_refresh", ATTENTION_WORK):
             if group_shared_span and shared_kv_lens is not None:
-                need = lib.acache_attention_grouped_scratch_bytes(total_q, nh, D, batch, hkv)
-                scratch = _grouped_scratch(q.device, need)
                 status = lib.acache_attention_grouped(
                     ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_cache), ptr(v_cache), num_slots, nh, hkv, D,
                     dtype_code(q.dtype), ptr(cu_seqlens_q), ptr(cu_seqlens_k), batch, total_q, int(max_q),
                     ptr(read_slot_mapping), float(softmax_scale), int(shared_prefix_len), ptr(shared_kv_lens),
-                    ptr(affix_shifts), rc, rs, rstride, rrows, rdt, ptr(scratch), scratch.numel(), ptr(flag),
-                    stream_ptr())
+                    ptr(affix_shifts), rc, rs, rstride, rrows, rdt, None, 0, ptr(flag), stream_ptr())
                 if status != _lib.ACACHE_EUNSUPPORTED:
                     check(status, "acache_attention_grouped")
                     return
@@ -115,23 +112,9 @@ def _attention_call(q, out, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, max_q,
             stream_ptr()), "paged_attention")
 
 
-_GROUPED_SCRATCH: dict = {}
-
-
-def _grouped_scratch(device, nbytes: int) -> torch.Tensor:
-    """Per-device scratch of ``acache_attention_grouped``: zeroed when it is created or grown and
-    after a reported device error (its tickets must start even), otherwise reused as it is."""
-    key = (device.type, device.index)
-    buf = _GROUPED_SCRATCH.get(key)
-    if buf is None or buf.numel() < nbytes:
-        buf = torch.zeros(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=device)
-        _GROUPED_SCRATCH[key] = buf
-    return buf
-
-
 def reset_grouped_scratch():
-    """Forget the scratch buffers (the next call allocates zeroed ones)."""
-    _GROUPED_SCRATCH.clear()
+    """Kept for callers of the earlier two-part kernel, which held tickets in a scratch buffer;
+    the grouped kernel keeps nothing between calls, so there is nothing to reset."""
 
 
 def _check_qkv(q, k_cache, v_cache):
@@ -154,8 +137,9 @@ def acache_attention(q, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, read_slot_
     acache_attention.py:643-738).  An entry of -1 in ``read_slot_mapping`` is a key that takes
     no part; ``shared_kv_lens`` without relocation only splits the keys into two runs.
     ``group_shared_span``: the caller guarantees that the first ``shared_kv_lens[b]`` entries of
-    all requests name the same slots up to holes; block decode then stages that span once per
-    four requests (falls back to the plain kernel for shapes the grouped one declines)."""
+    all requests name the same slots up to holes; block decode then serves four requests per CTA
+    and stages that span once for the four (falls back to the plain kernel for shapes the grouped
+    one declines)."""
     _check_qkv(q, k_cache, v_cache)
     _require_cuda(cu_seqlens_q, cu_seqlens_k, read_slot_mapping)
     batch = cu_seqlens_q.numel() - 1

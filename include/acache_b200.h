@@ -250,18 +250,18 @@ ACACHE_API int acache_attention(const void* q, int64_t q_stride, void* out, int6
                      const void* rope_cos, const void* rope_sin, int64_t rope_row_stride, int rope_rows,
                      int rope_dtype, int32_t* err_flag, void* stream);
 
-/* Block-decode form of acache_attention that stages the shared span once per group of four
- * consecutive requests instead of once per request (no counterpart in the reference, which
- * reads the span per request; same result up to the order of the floating-point sums).
+/* Block-decode form of acache_attention in which one CTA serves four consecutive requests of a
+ * KV head: the shared span is staged once for the four (no counterpart in the reference, which
+ * reads the span per request; same result up to the order of the floating-point sums), then the
+ * CTA walks each request's remaining keys.
  * Contract on top of acache_attention's: shared_kv_lens != NULL; within each group of four
  * consecutive requests shared_kv_lens[b] is the same and the first shared_kv_lens[b] entries of
  * read_slot_mapping name the same slots, up to holes (-1); every request has at most
  * 32 / (n_heads / n_kv_heads) queries; no key-side relocation.  A violated contract is reported
  * through err_flag (code 7), never by a fault.  ACACHE_EUNSUPPORTED means "use acache_attention".
- * scratch: acache_attention_grouped_scratch_bytes(...) bytes, 16-byte aligned, ZEROED ONCE by the
- * caller and then left alone between calls (it holds tickets that every call returns to an even
- * count); calls that share a scratch buffer must not overlap on the GPU; re-zero it after a call
- * that reported an error.  total_q = number of query rows (cu_seqlens_q[batch]). */
+ * scratch / scratch_bytes are not used (pass NULL / 0; acache_attention_grouped_scratch_bytes
+ * returns 0): nothing is kept between the CTAs of a call or between calls.  total_q = number
+ * of query rows (cu_seqlens_q[batch]). */
 ACACHE_API int64_t acache_attention_grouped_scratch_bytes(int total_q, int n_heads, int head_dim, int batch,
                                                           int n_kv_heads);
 ACACHE_API int acache_attention_grouped(const void* q, int64_t q_stride, void* out, int64_t o_stride,

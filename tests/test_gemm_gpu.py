@@ -160,3 +160,35 @@ def test_linear_argmax_matches_logits_then_argmax(n, k, vocab):
     assert not (x0 == 7).any()
     torch.testing.assert_close(conf[clear], want_conf[clear], rtol=6e-2, atol=1e-6)
     _lib.check_device_errors()
+
+
+def test_act_mul_halves_equals_act_mul_on_the_two_halves():
+    """One projection over the concatenated gate / up weights followed by the activation kernel on
+    its halves gives the bits of the two separate projections followed by ``act_mul``."""
+    _lib, ops = _ops()
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(77, 2 * 136, generator=g).to(torch.bfloat16).to(DEV)
+    want = ops.act_mul(x[:, :136].contiguous(), x[:, 136:].contiguous(), "silu")
+    assert torch.equal(ops.act_mul_halves(x, "silu"), want)
+    wide = torch.randn(50, 400, generator=g).to(torch.float16).to(DEV)[:, :272]     # rows 400 elements apart
+    want = ops.act_mul(wide[:, :136].contiguous(), wide[:, 136:].contiguous(), "gelu")
+    assert torch.equal(ops.act_mul_halves(wide, "gelu"), want)
+
+
+def test_apply_transfer_is_the_commit_rule_of_transfer_tokens():
+    """Statistics in, blocks edited in place: the same result as ``transfer_tokens`` on the logits
+    the statistics came from (threshold commits, forced commit of the most confident position)."""
+    _lib, ops = _ops()
+    g = torch.Generator().manual_seed(10)
+    R, T, V, mask = 6, 8, 96, 95
+    logits = (torch.randn(R * T, V, generator=g) * 4).to(torch.bfloat16).to(DEV)
+    logits[:, mask] = -30.0
+    blocks = torch.full((R, T), mask, dtype=torch.int64)
+    blocks[0, :] = 3                      # nothing left to unmask
+    blocks[1, ::2] = 5                    # partly unmasked
+    for thr in (0.3, 0.999):
+        a, b = blocks.clone().to(DEV), blocks.clone().to(DEV)
+        x0, conf = ops.transfer_tokens(logits, a, mask, thr)
+        ops.apply_transfer(x0.reshape(-1).contiguous(), conf.reshape(-1).contiguous(), b, mask, thr)
+        assert torch.equal(a, b)
+        assert (a[0] == 3).all() and (a[1, ::2] == 5).all()
