@@ -43,6 +43,7 @@ _SIGNATURES = {
     "acache_linear_argmax_scratch_bytes": (c_int64, [c_int, c_int]),
     "acache_linear_argmax": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                      c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
+    "acache_diag_mma_rate": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "acache_anchor_topk": (c_int, [c_void_p, c_int, c_int, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "acache_anchor_importance_scratch_bytes": (c_int64, [c_int, c_int, c_int]),
     "acache_anchor_importance": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,

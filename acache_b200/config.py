@@ -39,11 +39,11 @@ class Config:
     # cost of about 330 launches per step
     use_cuda_graphs: bool = True
     # block decode: hand attention every request's shared span as the same run of slots (with -1
-    # where an anchor's private copy replaces the shared row) and let one CTA serve four requests
-    # of a KV head, staging the span once for the four (same result as the logical order up to the
-    # order of the floating-point sums).  Off by default: on B200 the per-request kernel, two CTAs
-    # per SM hiding each other's waits, is faster at the measured shapes (81 against 117 us at 800
-    # shared / 560 other keys, 1.51 against 2.00 ms at 8192 / 3700)
+    # where an anchor's private copy replaces the shared row) and let one CTA serve two requests
+    # of a KV head, staging the span once for both (same result as the logical order up to the
+    # order of the floating-point sums).  Off by default: on B200 it is level with the per-request
+    # kernel at 800 shared / 560 other keys (78 against 81 us) and slower over a long span (1.77
+    # against 1.53 ms at 8192 / 3700)
     group_shared_span: bool = False
     # anchor selection: probe the newly admitted requests in ragged batches of at most
     # ``max_num_batched_tokens`` query rows (the reference runs one forward per request) and then

@@ -31,14 +31,16 @@
 //
 // Shared-span grouping (SPLIT = true, block decode): when every request has at most 32
 // virtual rows and the first shared_kv_lens[b] entries of all requests name the same slots
-// (up to holes), one CTA = (4 consecutive requests, KV head): warp w owns the 32 rows of request
-// 4a+w, so the 128 rows of every product are real.  The CTA first walks the shared span, staged
-// ONCE for the four requests (slot = the union of their entries, each warp masks its own
-// request's holes), then the remaining keys of request 0, of request 1, ...: a tile of request r
-// is dead for the other three warps (their P rows are zero).  The products of a 64-key tile
-// cost the same whether 32 or 128 of their rows are real, so the span costs a quarter of the
-// tensor-core instructions and of the L2 -> shared-memory traffic, and a launch has a quarter
-// of the CTAs, each paying its set-up once.
+// (up to holes), one CTA = (two consecutive requests, KV head): warps 2r and 2r + 1 hold two
+// copies of the 32 rows of request r and split a tile's key columns between them, as the
+// per-request kernel does with four copies.  The CTA first walks the shared span, staged ONCE
+// for both requests (slot = the union of their entries, each warp masks its own request's
+// holes), then the remaining keys of request 0, then of request 1: a tile of one request is
+// dead for the other's warps (their P rows are zero).  The products of a 64-key tile cost the
+// same however many of their 128 rows are distinct, so the span costs half the tensor-core
+// instructions and half the L2 -> shared-memory traffic, and a launch has half the CTAs, each
+// paying its set-up once; two CTAs still share an SM and hide each other's waits.  (The code
+// also instantiates as four requests with one copy each, COPIES = 1; one CTA per SM was slower.)
 // Every mbarrier wait is bounded; on expiry the kernel raises the error flag, frees its
 // TMEM and returns.
 #include <type_traits>
@@ -55,12 +57,13 @@ constexpr int BN = 64;       // keys per tile
 constexpr int NT = 128;      // threads that stage K/V and own the rows (warps 0-3)
 constexpr int NT_ALL = 160;  // + warp 4, whose first lane issues every tensor-core product
 constexpr int NT_LOAD = 288; // + warps 5-8 that take the K/V staging over from the row-owning warps (LOADERS)
-constexpr int GROUP = 4;     // requests per shared-span work item (one per warp)
+constexpr int GROUP = 4;     // row-owning warps = most requests a work item can hold
+constexpr int kGroupedRequests = 2;   // requests per work item of the grouped kernel as launched (two warps each)
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kColS = 0, kColO = 128;
 
 struct SplitArgs {
-  int n_items_a;        // work items = ceil(batch / GROUP) * n_kv_heads
+  int n_items_a;        // work items = ceil(batch / requests per item) * n_kv_heads
   int batch;
 };
 
@@ -74,6 +77,12 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
     const int32_t* __restrict__ affix_shifts, const TR* __restrict__ rope_cos, const TR* __restrict__ rope_sin,
     int64_t rope_stride, int rope_rows, int32_t* err_flag, SplitArgs sp) {
   constexpr int CH = D * (int)sizeof(T) / 16;     // 16-byte chunks per row
+  // requests per work item, and copies of a request's (at most 32) rows among the 128 rows of the
+  // products: every copy runs the softmax of 1 / CP of a tile's key columns.  Plain kernel: one
+  // request, COPIES copies; grouped kernel: COPIES = 1 -> four requests, one copy each,
+  // COPIES = 2 -> two requests, two copies each
+  constexpr int GR = SPLIT ? (COPIES == 2 ? 2 : GROUP) : 1;
+  constexpr int CP = SPLIT ? GROUP / GR : COPIES;
   constexpr int Q_BYTES = BM * D * (int)sizeof(T);
   constexpr int KV_BYTES = BN * D * (int)sizeof(T);
   constexpr int P_BYTES = BM * BN * (int)sizeof(T);
@@ -112,17 +121,17 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
 
   // ---- which work item ----------------------------------------------------------------------
   int b, kvh, m0;
-  const bool kind_a = SPLIT;       // an item of four requests
+  const bool kind_a = SPLIT;       // an item of several requests
   if (SPLIT) {
     m0 = 0;
-    b = ((int)blockIdx.x / n_kv_heads) * GROUP;
+    b = ((int)blockIdx.x / n_kv_heads) * GR;
     kvh = (int)blockIdx.x % n_kv_heads;
   } else {
     b = blockIdx.y;
     kvh = blockIdx.z;
     m0 = blockIdx.x * BM;
   }
-  const int n_req = kind_a ? min(GROUP, sp.batch - b) : 1;
+  const int n_req = kind_a ? min(GR, sp.batch - b) : 1;
   if (tid < GROUP) {
     int q0r = 0, vr = 0, kv0r = 0, sh = 0;
     if (tid < n_req) {
@@ -174,11 +183,12 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
   // every tile only (its P row is zero elsewhere), so each copy accumulates the attention over a
   // quarter of the keys with its own reference maximum; the four slices are folded at the end.
   // The tensor cores compute 128 rows either way; this spreads the softmax, the part that
-  // bounds block decode, over all four warps.  Items of kind A fill the rows with four requests
-  // instead and do not spread.
-  const bool spread = COPIES > 1 && !kind_a;
-  // this thread's row: request slot ri of the item, virtual row vr
-  const int ri = kind_a ? (warp & 3) : 0;
+  // bounds block decode, over all four warps.  A grouped item holds GR requests with CP = 4 / GR
+  // copies each.
+  const bool spread = CP > 1;
+  // this thread's row: request slot ri of the item (copy ci of its rows), virtual row vr
+  const int ri = kind_a ? (warp & 3) / CP : 0;
+  const int ci = (warp & 3) % CP;
   const int vr = (kind_a || spread) ? lane : m0 + tid;
 
   const uint32_t bar_k = smem_u32(&bars[0]), bar_s = smem_u32(&bars[2]), bar_p = smem_u32(&bars[4]),
@@ -230,7 +240,7 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
     // chunk id = it*NT + tid: 16 consecutive threads cover one row
     for (int id = ltid; id < BM * CH; id += NT) {
       const int r = id / CH, c = id % CH;
-      const int rr = kind_a ? (r >> 5) : 0;             // request slot of the row
+      const int rr = kind_a ? (r >> 5) / CP : 0;        // request slot of the row
       const int v = (kind_a || spread) ? (r & 31) : m0 + r;
       const bool ok = v < rq_vrows[rr];
       const int rq = ok ? v / g : 0, rh = kvh * g + (ok ? v % g : 0);
@@ -295,7 +305,7 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
   const int my_c = ltid % CH, my_r = ltid / CH;
   // The words of the slot map (or block table) are only LOADED here, two tiles ahead, and not
   // looked at before the end of the iteration, so no warp waits for them.
-  constexpr int NR = SPLIT ? GROUP : 1;   // requests whose entries a warp reads
+  constexpr int NR = GR;                  // requests whose entries a warp reads
   auto fetch_raw = [&](int i, int32_t (&raw)[NR][2]) {
     int j0, j_end, rr;
     tile_span(i, j0, j_end, rr);
@@ -312,7 +322,7 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
       }
     }
   };
-  // e0/e1: the entries the rows are fetched from (kind A: the union over the group's requests);
+  // e0/e1: the entries the rows are fetched from (grouped: the union over the item's requests);
   // dead: the rows this warp's own request may not see
   auto interpret = [&](int i, const int32_t (&raw)[NR][2], int32_t& e0, int32_t& e1, uint32_t& dead_lo,
                        uint32_t& dead_hi) {
@@ -321,7 +331,7 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
     int32_t uni[2] = {-3, -3}, own[2] = {-3, -3};
     bool clash = false;
     // the request whose view of the tile this warp works out (a group: one request per warp)
-    const int own_r = (SPLIT && kind_a) ? ((LOADERS ? warp - 5 : warp) & 3) : 0;
+    const int own_r = (SPLIT && kind_a) ? ((LOADERS ? warp - 5 : warp) & 3) / CP : 0;
 #pragma unroll
     for (int r = 0; r < NR; ++r) {
 #pragma unroll
@@ -450,8 +460,10 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
     if constexpr (NC == 64) {
       tmem_ld32(t_lane + kColS + (i & 1) * BN, s);
       tmem_ld32(t_lane + kColS + (i & 1) * BN + 32, s + 32);
+    } else if constexpr (NC == 32) {
+      tmem_ld32(t_lane + kColS + (i & 1) * BN + col0, s);
     } else {
-      static_assert(NC == 16, "column slices are 16 wide");
+      static_assert(NC == 16, "column slices are 16, 32 or 64 wide");
       tmem_ld16(t_lane + kColS + (i & 1) * BN + col0, s);
     }
     tmem_wait_ld();
@@ -510,12 +522,10 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
       }
       return;
     }
-    if constexpr (COPIES > 1) {
-      if (spread) {
-        if (!second) softmax_scores(std::integral_constant<int, BN / COPIES>{}, warp * (BN / COPIES), i);
-        else softmax_weights(std::integral_constant<int, BN / COPIES>{}, warp * (BN / COPIES), i);
-        return;
-      }
+    if constexpr (CP > 1) {
+      if (!second) softmax_scores(std::integral_constant<int, BN / CP>{}, ci * (BN / CP), i);
+      else softmax_weights(std::integral_constant<int, BN / CP>{}, ci * (BN / CP), i);
+      return;
     }
     if (!second) softmax_scores(std::integral_constant<int, BN>{}, 0, i);
     else softmax_weights(std::integral_constant<int, BN>{}, 0, i);
@@ -703,28 +713,29 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
     // nothing to write
   } else if (failed) {
     if (tid == 0 && err_flag) atomicExch(err_flag, 5);
-  } else if (COPIES > 1 && spread) {
-    // ---- fold the four column slices of every row, then write (or publish) the rows ----------
+  } else if (CP > 1) {
+    // ---- fold the column slices (copies) of every row, then write the rows -----------------------
     constexpr int F4 = D / 4;                       // float4 per row
     cp_async_wait<0>();
     float* xm = reinterpret_cast<float*>(sP);       // [128] reference maxima, [128] row sums
-    float4* part = reinterpret_cast<float4*>(sK);   // [4 slices][32 rows][F4], float4 index swizzled by the row
+    float4* part = reinterpret_cast<float4*>(sK);   // [4 warps][32 rows][F4], float4 index swizzled by the row
     xm[tid] = m_ref;
     xm[BM + tid] = l_sum;
     rows_sync();
-    auto fold_ml = [&](int row, float& m_all, float& l_all) {   // same order for every reader
+    // copies of request slot rs sit in warps rs * CP .. rs * CP + CP - 1; same order for every reader
+    auto fold_ml = [&](int rs, int row, float& m_all, float& l_all) {
       m_all = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < COPIES; ++c) m_all = fmaxf(m_all, xm[c * 32 + row]);
+      for (int c = 0; c < CP; ++c) m_all = fmaxf(m_all, xm[(rs * CP + c) * 32 + row]);
       l_all = 0.f;
 #pragma unroll
-      for (int c = 0; c < COPIES; ++c) {
-        const float mc = xm[c * 32 + row];
-        l_all += mc == -INFINITY ? 0.f : xm[BM + c * 32 + row] * ex2(mc - m_all);
+      for (int c = 0; c < CP; ++c) {
+        const float mc = xm[(rs * CP + c) * 32 + row];
+        l_all += mc == -INFINITY ? 0.f : xm[BM + (rs * CP + c) * 32 + row] * ex2(mc - m_all);
       }
     };
     float m_all, l_all;
-    fold_ml(lane, m_all, l_all);
+    fold_ml(ri, lane, m_all, l_all);
     const float w_own = m_ref == -INFINITY ? 0.f : ex2(m_ref - m_all);
     const bool have = n_tiles > 0;                  // otherwise O was never written: it counts as 0
     uint32_t o[32];
@@ -746,26 +757,28 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
       }
     }
     rows_sync();
-    // thread t: row t / 4, quarter t % 4 of its columns
-    const int r = tid >> 2, qd = tid & 3;
-    constexpr int QF4 = F4 / 4;                     // float4 per quarter row
+    // the item has GR x 32 output rows; TPR threads share one, each a 1 / TPR part of its columns
+    constexpr int TPR = NT / (GR * 32);
+    const int orow = tid / TPR, pt = tid % TPR;
+    const int rs = orow >> 5, r = orow & 31;
+    constexpr int QF4 = F4 / TPR;                   // float4 per thread
     float4 acc[QF4];
 #pragma unroll
     for (int k = 0; k < QF4; ++k) {
-      const int idx = qd * QF4 + k;
-      float4 a4 = part[r * F4 + (idx ^ (r & (F4 - 1)))];
+      const int idx = pt * QF4 + k;
+      float4 a4 = part[((rs * CP) * 32 + r) * F4 + (idx ^ (r & (F4 - 1)))];
 #pragma unroll
-      for (int c = 1; c < COPIES; ++c) {
-        const float4 b4 = part[(c * 32 + r) * F4 + (idx ^ (r & (F4 - 1)))];
+      for (int c = 1; c < CP; ++c) {
+        const float4 b4 = part[((rs * CP + c) * 32 + r) * F4 + (idx ^ (r & (F4 - 1)))];
         a4.x += b4.x; a4.y += b4.y; a4.z += b4.z; a4.w += b4.w;
       }
       acc[k] = a4;
     }
-    fold_ml(r, m_all, l_all);
-    const bool r_ok = r < my_vrows;
+    fold_ml(rs, r, m_all, l_all);
+    const bool r_ok = r < rq_vrows[rs];
     const int r_qi = r_ok ? r / g : 0, r_head = kvh * g + (r_ok ? r % g : 0);
-    const int64_t r_qrow = (int64_t)rq_q0[0] + r_qi;
-    T* r_out = out + r_qrow * o_stride + (int64_t)r_head * D + qd * (D / 4);
+    const int64_t r_qrow = (int64_t)rq_q0[rs] + r_qi;
+    T* r_out = out + r_qrow * o_stride + (int64_t)r_head * D + pt * (D / TPR);
     const float a_own = l_all > 0.f ? 1.0f / l_all : 0.f;
     if (r_ok) {
 #pragma unroll
@@ -839,7 +852,7 @@ static int launch(const AttnArgs& a, const SplitArgs* split) {
   // requests of at most 32 virtual rows (block decode): spread the softmax over the four warps
   // and give the K/V staging to four more warps
   const bool small_rows = a.max_q * g <= 32;
-  if (split) ACACHE_TC_LAUNCH(false, true, 1, true);
+  if (split) ACACHE_TC_LAUNCH(false, true, 2, true);
   else if (key_side) ACACHE_TC_LAUNCH(true, false, 1, false);
   else if (small_rows) ACACHE_TC_LAUNCH(false, false, 4, true);
   else ACACHE_TC_LAUNCH(false, false, 1, false);
@@ -893,7 +906,7 @@ int attention_split_dispatch(const AttnArgs& a, int dtype, int rope_dtype, int t
   if (a.n_kv_heads <= 0 || a.n_heads % a.n_kv_heads != 0) return ACACHE_EINVAL;
   if (a.max_q * (a.n_heads / a.n_kv_heads) > 32) return ACACHE_EUNSUPPORTED;
   tc::SplitArgs sp;
-  sp.n_items_a = ((a.batch + tc::GROUP - 1) / tc::GROUP) * a.n_kv_heads;
+  sp.n_items_a = ((a.batch + tc::kGroupedRequests - 1) / tc::kGroupedRequests) * a.n_kv_heads;
   sp.batch = a.batch;
   return tc::by_dtype(a, dtype, rope_dtype, &sp);
 }

@@ -285,6 +285,27 @@ def gemm_sweep(iters=10, shapes=None, tiles=None):
     _lib.check_device_errors()
 
 
+def mma_rate():
+    """Rate at which one issuing thread's tcgen05.mma stream is retired (no memory traffic): per
+    product width N, CTA group, number of alternating accumulators, commits and k steps per loop."""
+    lib = _lib.load()
+    out = torch.zeros(4, dtype=torch.int64, device=DEV)
+    for cg in (1, 2):
+        for n in (64, 128, 256):
+            for nacc in (1, 2):
+                for ce in (0, 1):
+                    for kper in (4, 8):
+                        _lib.check(lib.acache_diag_mma_rate(cg, n, nacc, ce, kper, 2000, _lib.ptr(out), _lib.stream_ptr()),
+                                   "diag_mma_rate")
+                        clk, ns, issued, done = out.tolist()
+                        units = 74 if cg == 2 else 148
+                        flop = issued * 2.0 * (256 if cg == 2 else 128) * n * 16
+                        print(f"cta_group {cg} N={n:3d} accumulators {nacc} commit every {ce} k steps {kper}: "
+                              f"{clk / issued:6.1f} cycles and {ns / issued:6.1f} ns per product at {clk / ns:.2f} GHz"
+                              f" = {flop / (ns * 1e-9) / 1e12 * units:7.1f} TFLOP/s over the GPU"
+                              f"{'' if done else '  (final wait ran out)'}", flush=True)
+
+
 def fused_sweep(iters=10):
     """The fused projections of a block against the library GEMM followed by the separate kernel,
     at the decode (512 rows) and refresh (2304 rows) sizes of the LLaDA-8B workload; back-to-back
@@ -442,6 +463,7 @@ def main(argv=None):
     ap.add_argument("names", nargs="*")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--mma-rate", action="store_true", help="issue rate of a stream of tcgen05.mma without memory traffic")
     ap.add_argument("--fused-sweep", action="store_true", help="fused projections against library GEMM + separate kernel")
     ap.add_argument("--gemm-sweep", action="store_true", help="projection GEMMs at several tile shapes against the library")
     args = ap.parse_args(argv)
@@ -450,6 +472,9 @@ def main(argv=None):
         return
     if args.fused_sweep:
         fused_sweep(args.iters)
+        return
+    if args.mma_rate:
+        mma_rate()
         return
     names = args.names or list(CASES)
     for n in names:

@@ -806,6 +806,10 @@ class ModelRunner(DkvMixin):
                 or self._relocated_affix_slot_offset is not None
                 or any(s.num_cache_blocks > len(bm.free_block_ids) for s in todo)):
             return False
+        # a batch rotates the shared keys inside the attention kernel where the one-request probe
+        # reads a materialised copy; over a long span that costs more than the batching saves
+        if any(s.affix_start != 0 for s in todo) and self.shared_prefix_len > 2048:
+            return False
         state = bm.snapshot()
         budget = max(int(getattr(self.config, "max_num_batched_tokens", 16384)), 1)
         picked = {}

@@ -250,8 +250,8 @@ ACACHE_API int acache_attention(const void* q, int64_t q_stride, void* out, int6
                      const void* rope_cos, const void* rope_sin, int64_t rope_row_stride, int rope_rows,
                      int rope_dtype, int32_t* err_flag, void* stream);
 
-/* Block-decode form of acache_attention in which one CTA serves four consecutive requests of a
- * KV head: the shared span is staged once for the four (no counterpart in the reference, which
+/* Block-decode form of acache_attention in which one CTA serves two consecutive requests of a
+ * KV head: the shared span is staged once for both (no counterpart in the reference, which
  * reads the span per request; same result up to the order of the floating-point sums), then the
  * CTA walks each request's remaining keys.
  * Contract on top of acache_attention's: shared_kv_lens != NULL; within each group of four
@@ -323,6 +323,17 @@ ACACHE_API int acache_transfer_tokens(const void* logits, int64_t logits_stride,
  * edited in place from x0 / confidence of the same shape. */
 ACACHE_API int acache_apply_transfer(int64_t* blocks, const int64_t* x0, const float* confidence, int n_rows,
                                      int block_len, int64_t mask_id, float threshold, void* stream);
+
+/* ------------------------------------------------------------------ diagnostics
+ * No counterpart in the reference.  Runs, on every SM (cta_group 1) or every pair of SMs (2), one
+ * thread that issues `iters` x `k_steps` x `n_accumulators` tcgen05.mma products of 128 (256 for a
+ * pair) rows x n columns x 16 on zeroed shared-memory operands, alternating between
+ * `n_accumulators` TMEM accumulators, with a tcgen05.commit every `commit_every` iterations (0 =
+ * only at the end), and waits for the last one.  result4 (device, 4 x int64): SM cycles, nanoseconds,
+ * products issued, 1 if the final wait completed.  Measures the tensor pipe and its issue path
+ * without any memory traffic. */
+ACACHE_API int acache_diag_mma_rate(int cta_group, int n, int n_accumulators, int commit_every, int k_steps, int iters,
+                                    long long* result4, void* stream);
 
 #ifdef __cplusplus
 }
