@@ -613,10 +613,12 @@ class ModelRunner(DkvMixin):
         self.acache_ready = True
 
     def export_shared_prefix_kv(self) -> torch.Tensor:
-        """Contiguous ``[2, layers, A, kv_heads, head_dim]`` copy of the shared affix K/V."""
+        """Contiguous ``[2, layers, A, kv_heads, head_dim]`` copy of the shared affix K/V (the
+        packing a collective needs: in the cache a layer's affix rows are ``blocks * block_size``
+        slots apart)."""
         k, v = self._flat_kv()
         n = self.shared_prefix_len
-        return torch.stack((k[:, :n], v[:, :n])).contiguous()
+        return torch.stack((k[:, :n], v[:, :n]))
 
     def _minimum_kv_cache_blocks_for_acache(self, seqs, prefix_len):
         shared = -(-prefix_len // self.config.cache_block_size)

@@ -218,7 +218,9 @@ def linear_argmax(x: torch.Tensor, weight: torch.Tensor):
     if n:
         lib = _lib.load()
         nbytes = lib.acache_linear_argmax_scratch_bytes(n, N)
-        scratch = _scratch_for(x.device, nbytes)
+        # a tensor of this call's own (not the shared growing buffer): inside a CUDA-graph capture it
+        # then belongs to the graph's pool and stays valid for every replay
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
         check(lib.acache_linear_argmax(ptr(x), x.stride(0), n, x.shape[1], ptr(weight), N, dtype_code(x.dtype), ptr(x0),
                                        ptr(conf), ptr(scratch), scratch.numel(), GEMM_TILE[0], GEMM_TILE[1],
                                        ptr(_lib.err_flag(x.device)), stream_ptr()), "linear_argmax", 2)

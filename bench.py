@@ -397,6 +397,7 @@ def run_ours(args):
             packed = runner.export_shared_prefix_kv()
         else:
             packed = torch.empty(2, L, len(affix), hkv, D, dtype=torch.bfloat16, device=dev)
+        dist.broadcast(torch.zeros(1, device=dev), src=0)     # sets the communicator up outside the timed copy
         torch.cuda.synchronize()
         dist.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -272,3 +272,38 @@ def test_llada_infix_4096_teacher_forced():
     """A long affix inside the prompt: the influence score walks it in chunks, decode and refresh
     read a 4096-token shared span through query-side relocation."""
     _run_case("llada", "infix", A=4096, ratio=0.1, n_req=2, own_lo=5, own_hi=300, G=32, T=32, decode_steps=2, seed=8)
+
+
+def test_graph_replay_equals_eager_at_real_widths_with_fused_projections():
+    """Two layers at LLaDA-8B widths, bf16, the shipped projection kernels (fused QKV, gate/up and
+    output head with arg-max statistics): the block-decode forward replayed from CUDA graphs gives
+    exactly the tokens of the eager forward while the number of active rows changes (five
+    requests, three slots), i.e. every buffer a captured kernel uses stays valid across replays
+    and across graphs of other row counts."""
+    from acache_b200 import _lib
+    from acache_b200.config import Config
+    from acache_b200.model_runner import ModelRunner
+    from acache_b200.sequence import Sequence
+
+    hf, model, _ = _build("llada", 2, seed=11)
+    rng = random.Random(12)
+    A, G, T = 300, 64, 32
+    affix = [rng.randrange(1, 20000) for _ in range(A)]
+    prompts = [affix + [rng.randrange(1, 20000) for _ in range(rng.randint(20, 200))] for _ in range(5)]
+
+    def run(graphs):
+        cfg = Config(hf_config=hf, mask_id=hf.mask_token_id, recompute_batch_size=2, max_num_seqs=3, gen_length=G,
+                     block_length=T, threshold=0.9, cache_block_size=256, num_kvcache_blocks=2 + 3 * 3 + 2,
+                     enable_acache=True, anchor_ratio=0.2, selection_mode="top", model_type="llada",
+                     use_cuda_graphs=graphs)
+        runner = ModelRunner(model, cfg)
+        seqs = [Sequence(p, block_length=T, gen_length=G, cache_block_size=256, mask_id=hf.mask_token_id,
+                         prompt_affix_len=A) for p in prompts]
+        outs, nfe = runner.generate_with_acache(seqs)
+        return outs, nfe, [s.anchor_positions for s in seqs], runner
+
+    eager = run(False)[:3]
+    replayed = run(True)
+    assert replayed[:3] == eager
+    assert len(replayed[3]._decode_graphs) >= 2          # several row counts were captured
+    _lib.check_device_errors()
