@@ -43,7 +43,6 @@
 // also instantiates as four requests with one copy each, COPIES = 1; one CTA per SM was slower.)
 // Every mbarrier wait is bounded; on expiry the kernel raises the error flag, frees its
 // TMEM and returns.
-#include <cstdlib>
 #include <type_traits>
 
 #include "common.cuh"
@@ -855,7 +854,6 @@ static int launch(const AttnArgs& a, const SplitArgs* split) {
   const bool small_rows = a.max_q * g <= 32;
   if (split) ACACHE_TC_LAUNCH(false, true, 2, true);
   else if (key_side) ACACHE_TC_LAUNCH(true, false, 1, false);
-  else if (small_rows && getenv("ACACHE_ATT_NOSPREAD")) ACACHE_TC_LAUNCH(false, false, 1, true);
   else if (small_rows) ACACHE_TC_LAUNCH(false, false, 4, true);
   else ACACHE_TC_LAUNCH(false, false, 1, false);
 #undef ACACHE_TC_LAUNCH
