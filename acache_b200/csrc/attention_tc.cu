@@ -43,7 +43,6 @@
 // also instantiates as four requests with one copy each, COPIES = 1; one CTA per SM was slower.)
 // Every mbarrier wait is bounded; on expiry the kernel raises the error flag, frees its
 // TMEM and returns.
-#include <cstdlib>
 #include <type_traits>
 
 #include "common.cuh"
@@ -877,7 +876,7 @@ static int by_dtype(const AttnArgs& a, int dtype, int rope_dtype, const SplitArg
   if (a.head_dim != 64 && a.head_dim != 128) return ACACHE_EUNSUPPORTED;
   if (!aligned16(a.q) || !aligned16(a.out) || !aligned16(a.k_cache) || !aligned16(a.v_cache)) return ACACHE_EUNSUPPORTED;
   if (a.q_stride % 8 != 0 || a.o_stride % 8 != 0) return ACACHE_EUNSUPPORTED;
-  if (split == nullptr && getenv("ACACHE_NO_WIDE") == nullptr) {
+  if (split == nullptr) {
     const int rc = attention_tc256_dispatch(a, dtype, rope_dtype);
     if (rc != ACACHE_EUNSUPPORTED) return rc;
   }

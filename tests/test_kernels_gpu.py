@@ -454,6 +454,7 @@ def test_transfer_tokens_golden_and_random():
     (torch.bfloat16, 8, 8, 128, [480, 672, 1], [1120, 1312, 65]),             # refresh
     (torch.float16, 14, 2, 64, [129, 300], [64, 577]),                        # head_dim 64, GQA 7
     (torch.bfloat16, 4, 4, 128, [5, 0, 9], [3, 10, 0]),                       # empty / tiny requests
+    (torch.bfloat16, 4, 2, 128, [600, 130], [700, 1500]),                     # 1200 virtual rows: CTA pairs, a ragged second request
 ])
 def test_attention_tensor_core_shapes(dt, nh, hkv, D, q_lens, kv_lens):
     from oracle import attention as oatt
