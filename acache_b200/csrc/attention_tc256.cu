@@ -7,23 +7,27 @@
 // kernel that gives every 128 rows a CTA of their own (attention_tc.cu).  One CTA per SM, roles
 // that hand over through mbarriers only:
 //   warps 0-7   own the rows: thread t owns virtual row t of the tile (row block t / 128, TMEM
-//               lane t % 128): tcgen05.ld of its scores, online softmax in the exp2 domain, P
-//               written to shared memory as an A operand.  They do nothing else in the loop;
+//               lane t % 128): tcgen05.ld of its scores, online softmax in the exp2 domain, the
+//               weights P written back to TMEM over the scores they came from (two per 32-bit
+//               column), where the P V product reads them as its A operand.  They do nothing
+//               else in the loop;
 //   warps 8,9   one thread each issues the tensor-core products of one row block: S(i+1) = Q K(i+1)^T
 //               one tile ahead of the softmax into one of two S buffers, and O += P(i) V(i);
 //   warps 10,11 gather the K tiles (16-byte cp.async into the 128-byte-swizzled operand layout,
 //               3 stages), look up the slot map and publish which keys of a tile take no part;
 //   warps 12,13 gather the V tiles (2 stages).
-// TMEM: 512 columns; row block r holds S buffers at columns 256 r and 256 r + 64 and O at
-// 256 r + 128.  Shared memory: Q (2 blocks), K (3 stages), V (2 stages), P (2 blocks x 2 buffers).
+// TMEM: 512 columns; row block r holds S buffers at columns 256 r and 256 r + 64 (P(i) takes the
+// first 32 columns of S buffer i & 1) and O at 256 r + 128.  Shared memory: Q (2 blocks), K (3
+// stages), V (2 stages).
 //   bar_k[s]    K stage s has landed           bar_v[s]     V stage s has landed
-//   bar_s[r][b] S buffer b of block r is done  bar_p[r][b]  P buffer b of block r is written
+//   bar_s[r][b] S buffer b of block r is done  bar_p[r][b]  P is written over S buffer b of block r
 //   bar_o[r][i & 1]  P V(i) of block r is done bar_q[r]     the query tile of block r is in place
 // (one arrival per warp: its lanes synchronise, one lane arrives; the product barriers are
 // tcgen05.commit arrivals).
-// The softmax of a row block never waits for its own P V product: P(i) goes to buffer i & 1 (free
-// once P V(i-2) is done), and O, which the products accumulate in place, is only touched by the
-// threads when a row's reference maximum moves, which then (and only then) waits for P V(i-1).
+// The softmax of a row block never waits for its own P V product: P(i) lives in the S buffer it
+// was computed from (S(i+2) is issued after P V(i) by the same thread, and the tensor cores keep
+// that order), and O, which the products accumulate in place, is only touched by the threads when
+// a row's reference maximum moves, which then (and only then) waits for P V(i-1).
 // A K stage is refilled when the S products of BOTH row blocks that read it are done, a V stage
 // when both P V products are; only the loader warps look at both blocks' barriers, so the two
 // blocks need not run in step.  A parity wait is only right while the barrier is at most one
@@ -90,7 +94,6 @@ __global__ void __launch_bounds__(NT_ALL, 1) attention_tc256_kernel(
   constexpr int Q_BYTES = BM * D * (int)sizeof(T);      // one row block
   constexpr int K_BYTES = KROWS * D * (int)sizeof(T);
   constexpr int V_BYTES = BN * VCH * 16;
-  constexpr int P_BYTES = BM * BN * (int)sizeof(T);     // one buffer of one row block
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
@@ -101,8 +104,7 @@ __global__ void __launch_bounds__(NT_ALL, 1) attention_tc256_kernel(
   uint8_t* sQ = smem;                    // RB blocks
   uint8_t* sK = sQ + RB * Q_BYTES;       // NSK stages
   uint8_t* sV = sK + NSK * K_BYTES;      // NSV stages
-  uint8_t* sP = sV + NSV * V_BYTES;      // RB blocks x 2 buffers
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * RB * P_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + NSV * V_BYTES);
   // K landed [NSK], V landed [NSV], then S done [r][b] (4), P written [r][b] (4), P V done [r][tile parity] (4), Q in place [r] (2)
   constexpr int NBAR = NSK + NSV + 14;
   uint32_t* ring_words = reinterpret_cast<uint32_t*>(bars + ((NBAR + 1) & ~1));   // 16-byte aligned
@@ -241,7 +243,7 @@ __global__ void __launch_bounds__(NT_ALL, 1) attention_tc256_kernel(
     if (lane == 0 && rank == 0) {
       const uint32_t idesc_s = make_idesc(Fmt<T>::id, 0, BN, NC * BM);
       const uint32_t idesc_o = make_idesc(Fmt<T>::id, 1, D, NC * BM);
-      const uint32_t qb = smem_u32(sQ) + rb * Q_BYTES, pb = smem_u32(sP) + rb * 2 * P_BYTES;
+      const uint32_t qb = smem_u32(sQ) + rb * Q_BYTES;
       const uint32_t my_s = bar_s + rb * 16, my_p = bar_p + rb * 16, my_o = bar_o + rb * 16, my_q = bar_q + rb * 8;
       auto product = [&](uint32_t d, uint64_t ad, uint64_t bd, uint32_t idesc, uint32_t acc) {
         if (PAIR) mma_ss_pair(d, ad, bd, idesc, acc);
@@ -291,8 +293,10 @@ __global__ void __launch_bounds__(NT_ALL, 1) attention_tc256_kernel(
           const uint32_t vb = smem_u32(sV) + (i % NSV) * V_BYTES;
 #pragma unroll
           for (int ks = 0; ks < BN / 16; ++ks) {
-            product(tmem_base + col_o, make_desc(pb + (i & 1) * P_BYTES + ks * 32, 16, 1024),
-                    make_desc(vb + ks * 2048, BN * 128, 1024), idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
+            // A = P(i): 16 keys = 8 columns of S buffer i & 1, which the softmax overwrote with its weights
+            const uint32_t pa = tmem_base + col_s + (i & 1) * BN + ks * 8;
+            if (PAIR) mma_ts_pair(tmem_base + col_o, pa, make_desc(vb + ks * 2048, BN * 128, 1024), idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
+            else mma_ts(tmem_base + col_o, pa, make_desc(vb + ks * 2048, BN * 128, 1024), idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
           }
         }
         done_on(my_o + (i & 1) * 8);
@@ -424,7 +428,6 @@ __global__ void __launch_bounds__(NT_ALL, 1) attention_tc256_kernel(
   } else {
     // ---- the threads that own the rows ----------------------------------------------------------
     const uint32_t my_s = bar_s + rb * 16, my_p = bar_p + rb * 16, my_o = bar_o + rb * 16, my_q = bar_q + rb * 8;
-    uint8_t* my_P = sP + rb * 2 * P_BYTES + brow * 128;   // this thread's row of P buffer 0
     // the 128 threads of a row block load its query tile
     auto load_q = [&](bool rotated) {
       uint8_t* dstb = sQ + rb * Q_BYTES;
@@ -462,13 +465,6 @@ __global__ void __launch_bounds__(NT_ALL, 1) attention_tc256_kernel(
     };
     load_q(start_rotated);
     cp_async_commit();
-    if (!warp_live) {  // rows of P that are never written stay zero
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        *reinterpret_cast<uint4*>(my_P + (c << 4)) = make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(my_P + P_BYTES + (c << 4)) = make_uint4(0, 0, 0, 0);
-      }
-    }
     cp_async_wait<0>();
     publish_fence();
     warp_arrive_first(my_q);
@@ -508,7 +504,6 @@ __global__ void __launch_bounds__(NT_ALL, 1) attention_tc256_kernel(
           }
           if (tag != (uint32_t)i + 1u) ok = false;
         }
-        if (i > 1) ok = wait_tile(my_o, i - 2) && ok;
         float mx = -INFINITY;
         tmem_wait_ld();
         if ((dl | dh) != 0u) {   // a tile with keys that take no part (holes, the end of a run)
@@ -556,24 +551,21 @@ __global__ void __launch_bounds__(NT_ALL, 1) attention_tc256_kernel(
         // two scores per packed fma, two partial row sums per packed add
         const uint64_t sc2 = pack_f32x2(scale_log2, scale_log2), nm2 = pack_f32x2(-m_use, -m_use);
         uint64_t rs2 = pack_f32x2(0.f, 0.f);
-        uint8_t* prow = my_P + (i & 1) * P_BYTES;
+        uint32_t w[BN / 2];   // the row's weights, two per word
 #pragma unroll
-        for (int c = 0; c < BN; c += 8) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 8; e += 2) {
-            float x0, x1;
-            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[c + e]), __uint_as_float(s[c + e + 1])), sc2, nm2), x0, x1);
-            const float p0 = ex2(x0), p1 = ex2(x1);
-            rs2 = add_f32x2(rs2, pack_f32x2(p0, p1));
-            w[e / 2] = pack2<T>(p0, p1);
-          }
-          *reinterpret_cast<uint4*>(prow + (((c / 8) ^ (brow & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        for (int c = 0; c < BN; c += 2) {
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), sc2, nm2), x0, x1);
+          const float p0 = ex2(x0), p1 = ex2(x1);
+          rs2 = add_f32x2(rs2, pack_f32x2(p0, p1));
+          w[c / 2] = pack2<T>(p0, p1);
         }
+        // P(i) takes the place of the first 32 columns of S(i) in TMEM, where the P V product reads it
+        tmem_st32(t_lane + col_s + (i & 1) * BN, w);
+        tmem_wait_st();
         float r0, r1;
         unpack_f32x2(rs2, r0, r1);
         l_sum += r0 + r1;
-        publish_fence();
       }
       tc_fence_before();
       warp_arrive_first(my_p + (i & 1) * 8);
@@ -626,7 +618,7 @@ template <typename T, typename TR, int D, bool PAIR>
 static int launch(const AttnArgs& a) {
   using TC = typename PromoteT<T, TR>::type;
   constexpr int NC = PAIR ? 2 : 1;
-  constexpr size_t smem = RB * BM * D * sizeof(T) + (NSK + NSV) * (BN / NC) * D * sizeof(T) + 2 * RB * BM * BN * sizeof(T) + 512;
+  constexpr size_t smem = RB * BM * D * sizeof(T) + (NSK + NSV) * (BN / NC) * D * sizeof(T) + 512;
   const int g = a.n_heads / a.n_kv_heads;
   const bool relocate = a.shared_prefix_len > 0 && a.affix_shifts != nullptr;
   const int rows_per_launch_unit = NC * RB * BM;
