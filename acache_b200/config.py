@@ -41,10 +41,10 @@ class Config:
     # block decode: hand attention every request's shared span as the same run of slots (with -1
     # where an anchor's private copy replaces the shared row) and let one CTA serve two requests
     # of a KV head, staging the span once for both (same result as the logical order up to the
-    # order of the floating-point sums).  Off by default: on B200 it is level with the per-request
-    # kernel at 800 shared / 560 other keys (78 against 81 us) and slower over a long span (1.77
-    # against 1.53 ms at 8192 / 3700)
-    group_shared_span: bool = False
+    # order of the floating-point sums).  On B200: 69 against 78 us per launch at 800 shared / 560
+    # other keys (16 requests, 32 heads), level with the per-request kernel over a long span (1.52
+    # ms at 8192 / 3700)
+    group_shared_span: bool = True
     # anchor selection: probe the newly admitted requests in ragged batches of at most
     # ``max_num_batched_tokens`` query rows (the reference runs one forward per request) and then
     # replay the reference's per-request allocate / free sequence on the host, so the free list,

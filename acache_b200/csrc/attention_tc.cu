@@ -5,7 +5,8 @@
 // (query, head-of-the-GQA-group) pair, so all query heads that share a KV head share one
 // pass over its K/V.  Roles inside the CTA, handing over through mbarriers only:
 //   warps 0-3  own the rows: thread t owns row t (TMEM lane t): tcgen05.ld of its scores,
-//              online softmax in the exp2 domain, P written to shared memory as an A operand;
+//              online softmax in the exp2 domain, the weights P written back to TMEM over the
+//              scores (two per 32-bit column), where the P V product reads its A operand;
 //              they also stage K/V, unless (block decode) warps 5-8 do that for them;
 //   warp 4     one thread issues every tcgen05.mma: S(i+1) = Q K(i+1)^T as soon as K(i+1)
 //              has landed, one tile ahead of the softmax, into one of two S buffers in TMEM,
@@ -88,7 +89,6 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
   constexpr int CP = SPLIT ? GROUP / GR : COPIES;
   constexpr int Q_BYTES = BM * D * (int)sizeof(T);
   constexpr int KV_BYTES = BN * D * (int)sizeof(T);
-  constexpr int P_BYTES = BM * BN * (int)sizeof(T);
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
@@ -99,12 +99,13 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + Q_BYTES;            // 2 stages
   uint8_t* sV = sK + 2 * KV_BYTES;       // 2 stages
-  uint8_t* sP = sV + 2 * KV_BYTES;
   // mbarriers: [0],[1] K stage landed (128 arrivals); [2],[3] S buffer computed (tcgen05.commit);
-  // [4] P written (and, without loader warps, V landed) (128 arrivals); [5] P V product done
-  // (tcgen05.commit); [6],[7] V stage landed (128 arrivals, loader warps only)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  // [5] P V product done (tcgen05.commit); [6],[7] V stage landed (128 arrivals, loader warps only);
+  // [8],[9] P(i) written (and, without loader warps, V(i) landed) (128 arrivals), barrier i & 1: a
+  // warp may publish P(i+1) before the others have published P(i), but not P(i+2), whose scores
+  // are only issued once P(i) is complete
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * KV_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   // per request of the item (one unless this is a kind-A item): first query row, virtual
   // rows, first slot-map entry, rotation row
   int* rq_q0 = reinterpret_cast<int*>(tmem_slot + 1);
@@ -194,14 +195,15 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
   const int ci = (warp & 3) % CP;
   const int vr = (kind_a || spread) ? lane : m0 + tid;
 
-  const uint32_t bar_k = smem_u32(&bars[0]), bar_s = smem_u32(&bars[2]), bar_p = smem_u32(&bars[4]),
-                 bar_o = smem_u32(&bars[5]), bar_v = smem_u32(&bars[6]);
+  const uint32_t bar_k = smem_u32(&bars[0]), bar_s = smem_u32(&bars[2]), bar_o = smem_u32(&bars[5]),
+                 bar_v = smem_u32(&bars[6]), bar_p = smem_u32(&bars[8]);
   if (tid == 0) {
     mbar_init(bar_k, NT);
     mbar_init(bar_k + 8, NT);
     mbar_init(bar_s, 1);
     mbar_init(bar_s + 8, 1);
     mbar_init(bar_p, NT);
+    mbar_init(bar_p + 8, NT);
     mbar_init(bar_o, 1);
     mbar_init(bar_v, NT);
     mbar_init(bar_v + 8, NT);
@@ -458,6 +460,7 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
   uint32_t s[BN];
   float mx;
   bool grow;
+  bool pv_ok = true;   // false when the wait for a P V product inside the softmax ran out
   auto softmax_scores = [&](auto nc_tag, const int col0, const int i) {
     constexpr int NC = decltype(nc_tag)::value;
     if constexpr (NC == 64) {
@@ -485,6 +488,11 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
   auto softmax_weights = [&](auto nc_tag, const int col0, const int i) {
     constexpr int NC = decltype(nc_tag)::value;
     if (__any_sync(0xFFFFFFFFu, grow) && i > 0) {
+      // O may only be touched between two products: P V(i-1) done (the scores of tile i have been
+      // seen, so P V(i-2) and everything before it is), and P V(i) is not issued before this thread
+      // publishes P(i)
+      pv_ok = wait_bar(bar_o, (uint32_t)((i - 1) & 1)) && pv_ok;
+      tc_fence_after();
       const float f = grow ? ex2(m_ref - mx) : 1.0f;
       l_sum *= f;
       uint32_t o[32];
@@ -501,18 +509,36 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
     if (grow) m_ref = mx;
     const float m_use = m_ref == -INFINITY ? 0.f : m_ref;   // no live key so far: every p is 0
     float rs = 0.f;
+    uint32_t w[NC / 2];   // this thread's weights, two per word
 #pragma unroll
-    for (int c = 0; c < NC; c += 8) {
-      uint32_t w[4];
-#pragma unroll
-      for (int e = 0; e < 8; e += 2) {
-        const float p0 = ex2(fmaf(__uint_as_float(s[c + e]), scale_log2, -m_use));
-        const float p1 = ex2(fmaf(__uint_as_float(s[c + e + 1]), scale_log2, -m_use));
-        rs += p0 + p1;
-        w[e / 2] = pack2<T>(p0, p1);
-      }
-      *reinterpret_cast<uint4*>(sP + tid * 128 + ((((col0 + c) / 8) ^ (tid & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    for (int c = 0; c < NC; c += 2) {
+      const float p0 = ex2(fmaf(__uint_as_float(s[c]), scale_log2, -m_use));
+      const float p1 = ex2(fmaf(__uint_as_float(s[c + 1]), scale_log2, -m_use));
+      rs += p0 + p1;
+      w[c / 2] = pack2<T>(p0, p1);
     }
+    // P(i) takes the place of the first 32 columns of S buffer i & 1 in TMEM (two weights per
+    // column), where the P V product reads it as its A operand; a thread that runs the softmax of
+    // a slice of the columns only writes zeros over the rest of its row
+    const uint32_t p_at = t_lane + kColS + (i & 1) * BN;
+    if constexpr (NC == 64) {
+      tmem_st32(p_at, w);
+    } else if constexpr (NC == 32) {
+      if (col0 == 0) {
+        tmem_st16(p_at, w);
+        tmem_fill16(p_at + 16, 0u);
+      } else {
+        tmem_fill16(p_at, 0u);
+        tmem_st16(p_at + 16, w);
+      }
+    } else {
+#pragma unroll
+      for (int gq = 0; gq < 4; ++gq) {
+        if (gq * 16 == col0) tmem_st8(p_at + gq * 8, w);
+        else tmem_fill8(p_at + gq * 8, 0u);
+      }
+    }
+    tmem_wait_st();
     l_sum += rs;
   };
   auto softmax_half = [&](const bool second, const int i) {
@@ -520,8 +546,9 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
     if (SPLIT && dead_lo == 0xFFFFFFFFu && dead_hi == 0xFFFFFFFFu) {
       // a tile of another request of the group: no key of it counts for these rows
       if (second) {
-#pragma unroll
-        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(sP + tid * 128 + (c << 4)) = make_uint4(0, 0, 0, 0);
+        tmem_fill16(t_lane + kColS + (i & 1) * BN, 0u);
+        tmem_fill16(t_lane + kColS + (i & 1) * BN + 16, 0u);
+        tmem_wait_st();
       }
       return;
     }
@@ -571,15 +598,15 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
           if (LOADERS) __threadfence_block();   // what the loaders wrote before K(i+1) (the tile's dead rows) is passed on
           issue_s(i + 1);
         }
-        ok = wait_bar(bar_p, (uint32_t)(i & 1));
+        ok = wait_bar(bar_p + (i & 1) * 8, (uint32_t)((i >> 1) & 1));
         if (LOADERS) ok = wait_bar(bar_v + (i & 1) * 8, (uint32_t)((i >> 1) & 1)) && ok;
         tc_fence_after();
         if (!ok) break;
         const uint32_t vb = smem_u32(sV) + (i & 1) * KV_BYTES;
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks) {
-          mma_ss(tmem_base + kColO, make_desc(smem_u32(sP) + ks * 32, 16, 1024),
-                 make_desc(vb + ks * 2048, BN * 128, 1024), idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
+          mma_ts(tmem_base + kColO, tmem_base + kColS + (i & 1) * BN + ks * 8, make_desc(vb + ks * 2048, BN * 128, 1024),
+                 idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
         }
         mma_commit(bar_o);
       }
@@ -620,10 +647,6 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
       publish_dead(1, dead1_lo, dead1_hi);
       publish_dead(2, dead2_lo, dead2_hi);
     }
-    if (!LOADERS && (!warp_live || spread)) {  // rows (or, spread, column slices) of P that are never written stay zero
-#pragma unroll
-      for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(sP + tid * 128 + (c << 4)) = make_uint4(0, 0, 0, 0);
-    }
     cp_async_wait<2>();            // Q + K(0)
     fence_proxy_async();
     arrive(bar_k);
@@ -660,7 +683,7 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
       fence_proxy_async();
       tc_fence_before();
       if (LOADERS) arrive(bar_v + (i & 1) * 8);
-      else arrive(bar_p);
+      else arrive(bar_p + (i & 1) * 8);
       dead_lo = dead1_lo;
       dead_hi = dead1_hi;
       dead1_lo = dead2_lo;
@@ -685,26 +708,25 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
     }
   } else if (n_tiles > 0) {
     // ---- row-owning warps when loader warps do the staging: softmax only ----------------------
-    if (!warp_live || spread) {  // rows (or, spread, column slices) of P that are never written stay zero
-#pragma unroll
-      for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(sP + tid * 128 + (c << 4)) = make_uint4(0, 0, 0, 0);
-    }
+    // (rows of padding need no P: their queries are zero, so are their scores, and a zero score
+    // reads as a zero weight)
     bool ok = true;
     for (int i = 0; i < n_tiles; ++i) {
       ok = wait_bar(bar_s + (i & 1) * 8, (uint32_t)((i >> 1) & 1)) && ok;   // also: the tile's dead rows are published
       tc_fence_after();
       dead_lo = dead_ring[((i & 3) * 4 + warp) * 2];
       dead_hi = dead_ring[((i & 3) * 4 + warp) * 2 + 1];
+      // no wait for the previous P V product: P(i) lives in the S buffer it came from, and the
+      // rescale of O, when a maximum moves, waits for it itself
       softmax_half(false, i);
-      // the previous P V product must be done before O is rescaled or P overwritten
-      if (i > 0) ok = wait_bar(bar_o, (uint32_t)((i - 1) & 1)) && ok;
-      tc_fence_after();
       softmax_half(true, i);
-      fence_proxy_async();
+      ok = ok && pv_ok;
       tc_fence_before();
-      arrive(bar_p);
+      arrive(bar_p + (i & 1) * 8);
       if (!ok) break;
     }
+    // a parity wait needs the phase before the awaited one to be over: P V(n-3) is (S(n-1) was seen)
+    if (ok && n_tiles > 1) ok = wait_bar(bar_o, (uint32_t)((n_tiles - 2) & 1));
     if (ok) ok = wait_bar(bar_o, (uint32_t)((n_tiles - 1) & 1));
     tc_fence_after();
     if (!ok) *give_up = 1;
@@ -720,7 +742,7 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
     // ---- fold the column slices (copies) of every row, then write the rows -----------------------
     constexpr int F4 = D / 4;                       // float4 per row
     cp_async_wait<0>();
-    float* xm = reinterpret_cast<float*>(sP);       // [128] reference maxima, [128] row sums
+    float* xm = reinterpret_cast<float*>(sQ);       // [128] reference maxima, [128] row sums (the queries are no longer read)
     float4* part = reinterpret_cast<float4*>(sK);   // [4 warps][32 rows][F4], float4 index swizzled by the row
     xm[tid] = m_ref;
     xm[BM + tid] = l_sum;
@@ -831,7 +853,7 @@ template <> struct PromoteT<__nv_bfloat16, __nv_bfloat16> { using type = __nv_bf
 template <typename T, typename TR, int D>
 static int launch(const AttnArgs& a, const SplitArgs* split) {
   using TC = typename PromoteT<T, TR>::type;
-  constexpr size_t smem = BM * D * sizeof(T) + 4 * BN * D * sizeof(T) + BM * BN * sizeof(T) + 512;
+  constexpr size_t smem = BM * D * sizeof(T) + 4 * BN * D * sizeof(T) + 512;
   const int g = a.n_heads / a.n_kv_heads;
   const bool relocate = a.shared_prefix_len > 0 && a.affix_shifts != nullptr;
   const bool query_side = relocate && a.shared_kv_lens != nullptr;

@@ -368,6 +368,8 @@ def run_ours(args):
                  gen_length=G, block_length=T, threshold=THRESHOLD, cache_block_size=256,
                  num_kvcache_blocks=cache_blocks(wl, batch, dev), enable_acache=True, anchor_ratio=wl["ratio"],
                  selection_mode="top", model_type=wl["model"], profile_timing=True)
+    if args.group_shared_span >= 0:
+        cfg.group_shared_span = bool(args.group_shared_span)
     if args.mode == "dkv_acache":      # second serving mode of the engine: delayed KV refresh on top of affix reuse
         cfg.enable_dkv_cache, cfg.dkv_steps, cfg.dkv_cache_interval = True, G, 8
     if args.mode == "dual_cache":      # the no-reuse baseline: every request keeps its own copy of the affix
@@ -633,6 +635,8 @@ def main():
                     help="debug only: 'own' / 'library' = every projection on this package's GEMM kernels / on the "
                          "library GEMM; or a comma list out of qkv,gate_up,dense,head naming the ones on this "
                          "package's kernels")
+    ap.add_argument("--group-shared-span", type=int, default=-1, choices=[-1, 0, 1],
+                    help="block-decode attention serves two requests of a KV head per CTA (-1: the engine's default)")
     ap.add_argument("--mode", default="acache", choices=["acache", "dkv_acache", "dual_cache"],
                     help="acache = the benchmark; the other serving modes of the engine on the same workload")
     args = ap.parse_args()
