@@ -41,7 +41,7 @@ AFFIX_LEN, BATCH, GEN, BLOCK, THRESHOLD, RATIO = 800, 16, 256, 32, 0.9, 0.2
 REQ_LO, REQ_HI = 64, 256
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode-attention launch at the default
 # workload's shape, from a profiler capture of that shape (not measured by this program)
-PROFILED_DECODE_ATTENTION_DRAM_BYTES = 171.0e6
+PROFILED_DECODE_ATTENTION_DRAM_BYTES = 170.3e6
 WORKLOAD = ("LLaDA-8B arch random-init bf16, prefix affix 800 tok + 16 ragged requests U[64,256], "
             "gen/steps/block 256/256/32, thr 0.9, anchor_ratio 0.2")
 
