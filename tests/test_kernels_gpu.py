@@ -707,6 +707,51 @@ def test_attention_grouped_declines_and_reports():
     _lib.check_device_errors()
 
 
+def test_attention_many_rows_reports_bad_slots_and_holes():
+    """The 256-row kernel (requests of more than 128 virtual rows; CTA pairs from 1024): read-map
+    entries outside the cache are skipped and reported, the next call works; entries of -1 are
+    keys that take no part; a request whose keys are all holes gets zeros."""
+    from acache_b200._lib import AcacheError
+    from oracle import attention as oatt
+
+    _lib, ops, aa, att = _ops()
+    g = torch.Generator().manual_seed(41)
+    dt, nh, hkv, D, Bk = torch.bfloat16, 4, 2, 128, 64
+    q_lens, kv_lens = [300, 520, 140], [333, 700, 65]           # 600 / 1040 / 280 virtual rows
+    nb = sum(kv_lens) // Bk + 8
+    q, kc, vc, cu_q, cu_k, logical, packed, shl = _random_case(g, dt, nh, hkv, D, Bk, nb, q_lens, kv_lens, 0, None)
+    d = lambda x: x.to(DEV)
+    ref = oatt.acache_attention(q, kc, vc, cu_q, cu_k, logical)
+    got = aa.acache_attention(d(q), d(kc), d(vc), d(cu_q), d(cu_k), d(logical), max_seqlen_q=max(q_lens))
+    _assert_close(got, ref, dt)
+    _lib.check_device_errors()
+
+    bad = logical.clone()
+    bad[int(cu_k[1]) + 77] = nb * Bk + 5                          # one key of request 1 lies outside the cache
+    aa.acache_attention(d(q), d(kc), d(vc), d(cu_q), d(cu_k), d(bad), max_seqlen_q=max(q_lens))
+    with pytest.raises(AcacheError):
+        _lib.check_device_errors()
+    got = aa.acache_attention(d(q), d(kc), d(vc), d(cu_q), d(cu_k), d(logical), max_seqlen_q=max(q_lens))
+    _assert_close(got, ref, dt)
+    _lib.check_device_errors()
+
+    holes = logical.clone()
+    holes[int(cu_k[0]): int(cu_k[1]): 3] = -1                     # every third key of request 0 takes no part
+    holes[int(cu_k[2]): int(cu_k[3])] = -1                        # request 2 sees nothing at all
+    keep = torch.ones(int(cu_k[3]), dtype=torch.bool)
+    keep[int(cu_k[0]): int(cu_k[1]): 3] = False
+    keep[int(cu_k[2]): int(cu_k[3])] = False
+    kept = logical[keep]
+    cu_kept = torch.tensor([0, int(keep[: int(cu_k[1])].sum()), int(keep[: int(cu_k[2])].sum()), int(keep.sum())],
+                           dtype=torch.int32)
+    live_rows = int(cu_q[2])
+    ref = oatt.acache_attention(q[:live_rows], kc, vc, cu_q[:3], cu_kept[:3], kept)
+    got = aa.acache_attention(d(q), d(kc), d(vc), d(cu_q), d(cu_k), d(holes), max_seqlen_q=max(q_lens))
+    _assert_close(got[:live_rows], ref, dt)
+    assert torch.equal(got[live_rows:].cpu().float(), torch.zeros(q_lens[2], nh, D))
+    _lib.check_device_errors()
+
+
 # ----------------------------------------------------------------------------- fused QKV GEMM
 @pytest.mark.parametrize("kind,n,hidden,nh,hkv", [("llada", 300, 512, 4, 4), ("dream", 77, 448, 7, 1),
                                                    ("llada", 512, 4096, 32, 32)])
