@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
   uint8_t* sK = sQ + Q_BYTES;            // 2 stages
   uint8_t* sV = sK + 2 * KV_BYTES;       // 2 stages
   // mbarriers: [0],[1] K stage landed (128 arrivals); [2],[3] S buffer computed (tcgen05.commit);
-  // [5] P V product done (tcgen05.commit); [6],[7] V stage landed (128 arrivals, loader warps only);
+  // [4],[5] P V(i) done (tcgen05.commit), barrier i & 1; [6],[7] V stage landed (128 arrivals, loader warps only);
   // [8],[9] P(i) written (and, without loader warps, V(i) landed) (128 arrivals), barrier i & 1: a
   // warp may publish P(i+1) before the others have published P(i), but not P(i+2), whose scores
   // are only issued once P(i) is complete
@@ -195,7 +195,7 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
   const int ci = (warp & 3) % CP;
   const int vr = (kind_a || spread) ? lane : m0 + tid;
 
-  const uint32_t bar_k = smem_u32(&bars[0]), bar_s = smem_u32(&bars[2]), bar_o = smem_u32(&bars[5]),
+  const uint32_t bar_k = smem_u32(&bars[0]), bar_s = smem_u32(&bars[2]), bar_o = smem_u32(&bars[4]),
                  bar_v = smem_u32(&bars[6]), bar_p = smem_u32(&bars[8]);
   if (tid == 0) {
     mbar_init(bar_k, NT);
@@ -205,6 +205,7 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
     mbar_init(bar_p, NT);
     mbar_init(bar_p + 8, NT);
     mbar_init(bar_o, 1);
+    mbar_init(bar_o + 8, 1);
     mbar_init(bar_v, NT);
     mbar_init(bar_v + 8, NT);
     *give_up = 0;
@@ -451,6 +452,13 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
     }
   };
   auto arrive = [&](uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); };
+  // P V(t) done: barrier t & 1 of the pair, its (t >> 1)-th completion.  Two barriers, because a
+  // row-owning warp no longer waits for every product: a parity wait is only right while the
+  // barrier is at most one phase past the awaited one, and with one barrier for all tiles a warp
+  // that is late for its wait for P V(t) could find P V(t+1) done as well and wait for ever.
+  // With two, the phase before the awaited one (P V(t-2)) is over whenever S(t+1) or P V(t-1) has
+  // been seen, and the phase after it (P V(t+2)) needs this thread's P(t+2)
+  auto wait_pv = [&](int t) { return wait_bar(bar_o + (t & 1) * 8, (uint32_t)((t >> 1) & 1)); };
   // barrier of the 128 row-owning threads only (warp 4 never takes part)
   auto rows_sync = [&]() { asm volatile("bar.sync 1, 128;" ::: "memory"); };
 
@@ -491,7 +499,7 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
       // O may only be touched between two products: P V(i-1) done (the scores of tile i have been
       // seen, so P V(i-2) and everything before it is), and P V(i) is not issued before this thread
       // publishes P(i)
-      pv_ok = wait_bar(bar_o, (uint32_t)((i - 1) & 1)) && pv_ok;
+      pv_ok = wait_pv(i - 1) && pv_ok;
       tc_fence_after();
       const float f = grow ? ex2(m_ref - mx) : 1.0f;
       l_sum *= f;
@@ -608,7 +616,7 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
           mma_ts(tmem_base + kColO, tmem_base + kColS + (i & 1) * BN + ks * 8, make_desc(vb + ks * 2048, BN * 128, 1024),
                  idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
         }
-        mma_commit(bar_o);
+        mma_commit(bar_o + (i & 1) * 8);
       }
     }
   } else if (n_tiles > 0 && (!LOADERS || is_loader)) {
@@ -674,7 +682,7 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
       if (!LOADERS) softmax_half(false, i);
       // the previous P V product must be done before O is rescaled, P overwritten or its V
       // stage refilled
-      if (i > 0) ok = wait_bar(bar_o, (uint32_t)((i - 1) & 1)) && ok;
+      if (i > 0) ok = wait_pv(i - 1) && ok;
       tc_fence_after();
       if (i + 1 < n_tiles) load_rows(i + 1, ev0, ev1, false, true);
       cp_async_commit();                               // V(i+1)
@@ -698,7 +706,7 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
       if (!ok) break;
     }
     if (!LOADERS) {
-      if (ok) ok = wait_bar(bar_o, (uint32_t)((n_tiles - 1) & 1));
+      if (ok) ok = wait_pv(n_tiles - 1);
       tc_fence_after();
       if (!ok) *give_up = 1;
       rows_sync();
@@ -725,9 +733,7 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
       arrive(bar_p + (i & 1) * 8);
       if (!ok) break;
     }
-    // a parity wait needs the phase before the awaited one to be over: P V(n-3) is (S(n-1) was seen)
-    if (ok && n_tiles > 1) ok = wait_bar(bar_o, (uint32_t)((n_tiles - 2) & 1));
-    if (ok) ok = wait_bar(bar_o, (uint32_t)((n_tiles - 1) & 1));
+    if (ok) ok = wait_pv(n_tiles - 1);
     tc_fence_after();
     if (!ok) *give_up = 1;
     rows_sync();
