@@ -120,8 +120,12 @@ __global__ void __launch_bounds__(NT_ALL, 1) attention_tc256_kernel(
   const bool query_side = shared_kv_lens != nullptr && affix_shifts != nullptr;
   const uint32_t rank = PAIR ? cluster_ctarank() : 0u;    // the first CTA of a pair issues its products
 
-  const int b = blockIdx.y, kvh = blockIdx.z, m0 = blockIdx.x * (RB * BM);
-  const int m0_all = PAIR ? (int)(blockIdx.x & ~1u) * (RB * BM) : m0;   // first row of the pair
+  // A pair's two CTAs are neighbours in x.  Without pairs the row tile is the slowest grid index,
+  // so that the CTAs of every request's last, partly filled tile are handed out last and fill the
+  // gaps of the final round instead of each delaying a full one behind it
+  const int b = blockIdx.y, kvh = PAIR ? blockIdx.z : blockIdx.x;
+  const int tile = PAIR ? blockIdx.x : blockIdx.z, m0 = tile * (RB * BM);
+  const int m0_all = PAIR ? (tile & ~1) * (RB * BM) : m0;   // first row of the pair
   const int q0 = cu_q[b];
   const int vrows = (cu_q[b + 1] - q0) * g;
   if (m0_all >= vrows) return;
@@ -622,7 +626,8 @@ static int launch(const AttnArgs& a) {
   const int g = a.n_heads / a.n_kv_heads;
   const bool relocate = a.shared_prefix_len > 0 && a.affix_shifts != nullptr;
   const int rows_per_launch_unit = NC * RB * BM;
-  dim3 grid(NC * ((a.max_q * g + rows_per_launch_unit - 1) / rows_per_launch_unit), a.batch, a.n_kv_heads);
+  const int tiles = NC * ((a.max_q * g + rows_per_launch_unit - 1) / rows_per_launch_unit);
+  const dim3 grid = PAIR ? dim3(tiles, a.batch, a.n_kv_heads) : dim3(a.n_kv_heads, a.batch, tiles);
   auto kern = attention_tc256_kernel<T, TR, TC, D, PAIR>;
   ACACHE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchConfig_t lc = {};
