@@ -34,6 +34,9 @@ _SIGNATURES = {
                                         c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "acache_linear": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int64, c_int,
                               c_int, c_void_p, c_void_p]),
+    "acache_linear_partials_splits": (c_int, [c_int, c_int, c_int]),
+    "acache_linear_partials": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
+                                       c_int, c_void_p, c_void_p]),
     "acache_linear_swiglu": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int64,
                                      c_int, c_int, c_void_p, c_void_p]),
     "acache_linear_qkv_rope_scatter": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -67,6 +70,8 @@ _SIGNATURES = {
     "acache_rmsnorm": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_float, c_int, c_void_p]),
     "acache_add_rmsnorm": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int,
                                    c_float, c_int, c_void_p]),
+    "acache_add_rmsnorm_partials": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p,
+                                            c_int64, c_int, c_int, c_float, c_int, c_void_p]),
     "acache_act_mul_halves": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
     "acache_act_mul": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "acache_apply_transfer": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_float, c_void_p]),

@@ -8,6 +8,10 @@
 //   qkv      bias, RoPE at the row's position, q to its buffer, k / v into the paged cache
 //   argmax   per row: arg-max, maximum and sum of exponentials over the N columns (output
 //            head + greedy unmasking statistics; the logits never reach global memory)
+//   partial  the K range cut into S slices, slice s of every tile is a tile of its own and leaves
+//            its fp32 sums in partial[s]; for projections with so few output tiles that whole
+//            tiles would leave most of the 74 pairs idle.  The normalisation kernel that consumes
+//            the projection adds the slices (`acache_add_rmsnorm_partials`).
 //
 // Two CTAs of a cluster work as one: `tcgen05.mma.cta_group::2` multiplies a 256-row block of X
 // (128 rows staged by each CTA) with a BN-column block of W (BN/2 rows staged by each CTA), so a
@@ -38,10 +42,12 @@ constexpr int kPairs = kNumSMs / 2;
 constexpr int kMaxStages = 8;
 constexpr uint32_t kTmemCols = 512;
 
-enum { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_QKV = 2, EPI_ARGMAX = 3 };
+enum { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_QKV = 2, EPI_ARGMAX = 3, EPI_PARTIAL = 4 };
 
 struct Params {
   int M, N, K, MB, BN, stages, acc_stages, group;
+  int ksplit;           // slices of the K range (1 except for EPI_PARTIAL)
+  float* partial;       // EPI_PARTIAL: [ksplit][M][N] fp32
   // plain / swiglu
   void* out; int64_t ldo; const void* bias; int act;
   // qkv
@@ -179,6 +185,12 @@ __device__ __forceinline__ void epi_plain(const Params& p, int m, int n, const f
   *reinterpret_cast<uint4*>(dst + 8) = pack8<T>(o + 8);
 }
 
+__device__ __forceinline__ void epi_partial(const Params& p, int ks, int m, int n, const float* v) {
+  float4* dst = reinterpret_cast<float4*>(p.partial + ((int64_t)ks * p.M + m) * p.N + n);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+}
+
 // W rows are interleaved in groups of 8: columns n..n+7 are gate features n/2..n/2+7 and columns
 // n+8..n+15 the up features of the same indices; both projections are rounded to T first, the
 // activation is rounded to T, then the product, as the separate kernels do
@@ -277,8 +289,10 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   const int rows_per_tile = 256 * MB;
   const int m_tiles = (p.M + rows_per_tile - 1) / rows_per_tile;
   const int n_tiles = (p.N + BN - 1) / BN;
-  const int total = m_tiles * n_tiles;
+  const int mn_tiles = m_tiles * n_tiles;
+  const int total = mn_tiles * p.ksplit;       // slice-major: the slices of a tile run on different pairs
   const int k_blocks = (p.K + BK - 1) / BK;
+  const int k_per = (k_blocks + p.ksplit - 1) / p.ksplit;   // the host made sure no slice is empty
   const int acc_cols = (BN + 31) & ~31;       // TMEM columns reserved per accumulator
 
   if (tid == 0) {
@@ -312,9 +326,11 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       uint32_t round = 0;                      // times the ring has wrapped
       bool ok = true;
       for (int t = pair; t < total && ok; t += n_pairs) {
-        const int mt = t % m_tiles, nt = t / m_tiles;
+        const int tt = t % mn_tiles, ks = t / mn_tiles;
+        const int mt = tt % m_tiles, nt = tt / m_tiles;
         const int m0 = mt * rows_per_tile + (int)rank * 128, n0 = nt * BN + (int)rank * (BN / 2);
-        for (int kb = 0; kb < k_blocks && ok; ++kb, s = (s + 1 == S) ? 0 : s + 1, round += (s == 0)) {
+        const int kb_end = min(k_blocks, (ks + 1) * k_per);
+        for (int kb = ks * k_per; kb < kb_end && ok; ++kb, s = (s + 1 == S) ? 0 : s + 1, round += (s == 0)) {
           // a group of G stages is handed back by one commit after its last stage was read
           if (round > 0 && (s & (G - 1)) == 0) ok = wait_or_abort(bar(EMPTY + s / G), (round - 1) & 1, abort_flag);
           if (!ok) break;
@@ -344,12 +360,13 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         if (!ok) break;
         tc_fence_after();
         const uint32_t d0 = tmem_base + (uint32_t)(acc * MB * acc_cols), d1 = d0 + (uint32_t)acc_cols;
-        for (int kb = 0; kb < k_blocks && ok; ++kb) {
+        const int ks = t / mn_tiles, kb_begin = ks * k_per, kb_end = min(k_blocks, (ks + 1) * k_per);
+        for (int kb = kb_begin; kb < kb_end && ok; ++kb) {
           ok = wait_or_abort(bar(FULL + s), full_parity, abort_flag);
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_lo = ring_lo + (uint32_t)s * stage_units;
-          issue_kblock<MB>(d0, d1, a_lo, a_lo + b_units, desc_hi, idesc, kb > 0 ? 1u : 0u);
+          issue_kblock<MB>(d0, d1, a_lo, a_lo + b_units, desc_hi, idesc, kb > kb_begin ? 1u : 0u);
           // the group of stages is free in both CTAs once these products have read it
           if ((s & (G - 1)) == G - 1) mma_commit_pair(bar(EMPTY + s / G));
           if (++s == S) {
@@ -372,7 +389,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     int n = 0;
     bool ok = !*abort_flag;
     for (int t = pair; t < total && ok; t += n_pairs, ++n) {
-      const int mt = t % m_tiles, nt = t / m_tiles;
+      const int tt = t % mn_tiles, ks = t / mn_tiles;
+      const int mt = tt % m_tiles, nt = tt / m_tiles;
       const int acc = n % AS;
       ok = wait_or_abort(bar(ACC_FULL + acc), (uint32_t)((n / AS) & 1), abort_flag);
       if (!ok) break;
@@ -413,6 +431,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             const float* v = reinterpret_cast<const float*>(half == 0 ? v0 : v1);
             const int nn = n0 + c + half * 16;
             if (EPI == EPI_PLAIN) epi_plain<T>(p, m, nn, v);
+            if (EPI == EPI_PARTIAL) epi_partial(p, ks, m, nn, v);
             if (EPI == EPI_SWIGLU) epi_swiglu<T>(p, m, nn, v);
             if (EPI == EPI_QKV) epi_qkv<T, TR, TC>(p, m, nn, v, pos, slot);
             if (EPI == EPI_ARGMAX) {
@@ -541,7 +560,7 @@ static int launch_mb(const CUtensorMap& mx, const CUtensorMap& mw, const Params&
   auto kern = linear_tc_kernel<T, TR, TC, EPI, MB>;
   ACACHE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile.smem));
   const int m_tiles = (p.M + 256 * p.MB - 1) / (256 * p.MB), n_tiles = (p.N + p.BN - 1) / p.BN;
-  const long total = (long)m_tiles * n_tiles;
+  const long total = (long)m_tiles * n_tiles * p.ksplit;
   const int pairs = total < kPairs ? (int)total : kPairs;
   kern<<<2 * pairs, NT, tile.smem, st>>>(mx, mw, p);
   ACACHE_LAUNCH_CHECK();
@@ -569,6 +588,7 @@ static int prepare(const void* x, int64_t ldx, const void* w, int M, int N, int 
   if (tile->smem == 0) return ACACHE_EUNSUPPORTED;
   p->M = M; p->N = N; p->K = K; p->MB = tile->mb; p->BN = tile->bn; p->stages = tile->stages;
   p->acc_stages = tile->acc_stages;
+  p->ksplit = 1;
   // `tcgen05.commit` costs the issuing thread a few hundred cycles: with one row block per CTA (6
   // or more stages) two stages are handed back per commit; with two row blocks there are only 4
   // stages and handing them back one by one keeps the loads further ahead
@@ -579,10 +599,50 @@ static int prepare(const void* x, int64_t ldx, const void* w, int M, int N, int 
   return ACACHE_OK;
 }
 
+// Slices of the K range for a projection whose whole tiles (256 rows x 256 columns per pair) would
+// occupy at most half of the 74 pairs: as many as still run in one wave, at most 4 (measured on B200:
+// 512 x 4096 x 4096 in 23 us with 2 slices against 33 us whole; 256 rows: 19 us with 4 against 33 us;
+// more slices only add fp32 traffic), at least 8 k blocks each.
+static int plan_splits(int M, int N, int K) {
+  const long tiles = (long)((M + 255) / 256) * ((N + 255) / 256);
+  const int k_blocks = (K + BK - 1) / BK;
+  long s = kPairs / tiles;
+  if (s > 4) s = 4;
+  while (s > 1 && (k_blocks / s < 8 || (s - 1) * ((k_blocks + s - 1) / s) >= k_blocks)) --s;
+  return s < 2 ? 1 : (int)s;
+}
+
 }  // namespace gemm
 }  // namespace acache
 
 using namespace acache;
+
+extern "C" int acache_linear_partials_splits(int n_rows, int in_features, int out_features) {
+  if (n_rows <= 0 || in_features <= 0 || out_features <= 0) return 1;
+  return gemm::plan_splits(n_rows, out_features, in_features);
+}
+
+extern "C" int acache_linear_partials(const void* x, int64_t x_stride, int n_rows, int in_features, const void* weight,
+                                      int out_features, int dtype, float* partials, int n_splits, int tile_mb,
+                                      int tile_bn, int32_t* err_flag, void* stream) {
+  if (n_splits < 0 || n_splits > 16) return ACACHE_EINVAL;
+  if (n_rows == 0) return ACACHE_OK;
+  if (!x || !weight || !partials) return ACACHE_EINVAL;
+  if (n_splits == 0) n_splits = gemm::plan_splits(n_rows, out_features, in_features);
+  const int k_blocks = (in_features + gemm::BK - 1) / gemm::BK;
+  if ((n_splits - 1) * ((k_blocks + n_splits - 1) / n_splits) >= k_blocks) return ACACHE_EINVAL;   // an empty slice
+  gemm::Params p{};
+  gemm::Tile tile;
+  CUtensorMap mx, mw;
+  const int rc = gemm::prepare(x, x_stride, weight, n_rows, out_features, in_features, dtype, tile_mb ? tile_mb : 1,
+                               tile_bn ? tile_bn : 256, 1.0, &p, &tile, &mx, &mw);
+  if (rc != ACACHE_OK) return rc;
+  if (!aligned16(partials)) return ACACHE_EUNSUPPORTED;
+  p.partial = partials; p.ksplit = n_splits; p.err_flag = err_flag;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == ACACHE_BF16) return gemm::launch<__nv_bfloat16, float, float, gemm::EPI_PARTIAL>(mx, mw, p, tile, st);
+  return gemm::launch<__half, float, float, gemm::EPI_PARTIAL>(mx, mw, p, tile, st);
+}
 
 extern "C" int acache_linear(const void* x, int64_t x_stride, int n_rows, int in_features, const void* weight,
                              int out_features, const void* bias, int dtype, void* out, int64_t out_stride,

@@ -58,14 +58,21 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const T* __restrict__ x, i
 
 // x_new = x + delta (rounded to T, written back in place of x), y = rmsnorm(x_new): the residual
 // add of the previous sub-layer fused into the normalisation that follows it
-template <typename T, int VPT>
+// With PART the update arrives as `n_splits` fp32 slices of a projection's K range
+// (`partials[s][row][col]`, rows `d_stride` floats apart, slices `split_stride` floats apart): they
+// are summed in slice order and rounded to T, which is the projection's output as a GEMM in T
+// leaves it, before the add.
+template <typename T, int VPT, bool PART>
 __global__ void __launch_bounds__(256) add_rmsnorm_kernel(T* __restrict__ x, int64_t x_stride, const T* __restrict__ delta,
                                                           int64_t d_stride, const T* __restrict__ w, T* __restrict__ y,
-                                                          int64_t y_stride, int n_cols, float eps) {
+                                                          int64_t y_stride, int n_cols, float eps,
+                                                          const float* __restrict__ partials, int n_splits,
+                                                          int64_t split_stride) {
   constexpr int E = 16 / sizeof(T);
   const int row = blockIdx.x;
   T* xr = x + (int64_t)row * x_stride;
-  const T* dr = delta + (int64_t)row * d_stride;
+  const T* dr = PART ? nullptr : delta + (int64_t)row * d_stride;
+  const float* pr = PART ? partials + (int64_t)row * d_stride : nullptr;
   T* yr = y + (int64_t)row * y_stride;
   const int nvec = n_cols / E;
   Vec16<T> v[VPT];
@@ -76,7 +83,26 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(T* __restrict__ x, int
     if (c < nvec) {
       Vec16<T> a, b;
       a.u = *reinterpret_cast<const uint4*>(xr + (int64_t)c * E);
-      b.u = ld_global_nc(dr + (int64_t)c * E);
+      if (PART) {
+        float acc[E];
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[e] = 0.f;
+        for (int sp = 0; sp < n_splits; ++sp) {
+          const float* src = pr + sp * split_stride + (int64_t)c * E;
+#pragma unroll
+          for (int q = 0; q < E / 4; ++q) {
+            const uint4 u = ld_global_nc(src + 4 * q);
+            acc[4 * q] += __uint_as_float(u.x);
+            acc[4 * q + 1] += __uint_as_float(u.y);
+            acc[4 * q + 2] += __uint_as_float(u.z);
+            acc[4 * q + 3] += __uint_as_float(u.w);
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < E; ++e) b.e[e] = from_f32<T>(acc[e]);
+      } else {
+        b.u = ld_global_nc(dr + (int64_t)c * E);
+      }
 #pragma unroll
       for (int e = 0; e < E; ++e) {
         v[i].e[e] = from_f32<T>(to_f32<T>(a.e[e]) + to_f32<T>(b.e[e]));
@@ -280,11 +306,37 @@ extern "C" int acache_add_rmsnorm(void* x, int64_t x_stride, const void* delta, 
   if (!vec || nvec > 1024) return ACACHE_EUNSUPPORTED;
   ACACHE_DISPATCH_DTYPE(dtype, T, {
     if (nvec <= 256) {
-      add_rmsnorm_kernel<T, 1><<<n_rows, 256, 0, st>>>((T*)x, x_stride, (const T*)delta, d_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps);
+      add_rmsnorm_kernel<T, 1, false><<<n_rows, 256, 0, st>>>((T*)x, x_stride, (const T*)delta, d_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps, nullptr, 0, 0);
     } else if (nvec <= 512) {
-      add_rmsnorm_kernel<T, 2><<<n_rows, 256, 0, st>>>((T*)x, x_stride, (const T*)delta, d_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps);
+      add_rmsnorm_kernel<T, 2, false><<<n_rows, 256, 0, st>>>((T*)x, x_stride, (const T*)delta, d_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps, nullptr, 0, 0);
     } else {
-      add_rmsnorm_kernel<T, 4><<<n_rows, 256, 0, st>>>((T*)x, x_stride, (const T*)delta, d_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps);
+      add_rmsnorm_kernel<T, 4, false><<<n_rows, 256, 0, st>>>((T*)x, x_stride, (const T*)delta, d_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps, nullptr, 0, 0);
+    }
+  });
+  ACACHE_LAUNCH_CHECK();
+  return ACACHE_OK;
+}
+
+extern "C" int acache_add_rmsnorm_partials(void* x, int64_t x_stride, const float* partials, int n_splits,
+                                           int64_t split_stride, int64_t p_stride, const void* weight, void* y,
+                                           int64_t y_stride, int n_rows, int n_cols, float eps, int dtype,
+                                           void* stream) {
+  if (!dtype_ok(dtype) || n_rows < 0 || n_cols <= 0 || n_splits <= 0) return ACACHE_EINVAL;
+  if (n_rows == 0) return ACACHE_OK;
+  if (!x || !partials || !weight || !y) return ACACHE_EINVAL;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int E = 16 / dtype_bytes(dtype);
+  const bool vec = n_cols % E == 0 && x_stride % E == 0 && y_stride % E == 0 && p_stride % 4 == 0 &&
+                   split_stride % 4 == 0 && aligned16(x) && aligned16(y) && aligned16(weight) && aligned16(partials);
+  const int nvec = n_cols / E;
+  if (!vec || nvec > 1024) return ACACHE_EUNSUPPORTED;
+  ACACHE_DISPATCH_DTYPE(dtype, T, {
+    if (nvec <= 256) {
+      add_rmsnorm_kernel<T, 1, true><<<n_rows, 256, 0, st>>>((T*)x, x_stride, nullptr, p_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps, partials, n_splits, split_stride);
+    } else if (nvec <= 512) {
+      add_rmsnorm_kernel<T, 2, true><<<n_rows, 256, 0, st>>>((T*)x, x_stride, nullptr, p_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps, partials, n_splits, split_stride);
+    } else {
+      add_rmsnorm_kernel<T, 4, true><<<n_rows, 256, 0, st>>>((T*)x, x_stride, nullptr, p_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps, partials, n_splits, split_stride);
     }
   });
   ACACHE_LAUNCH_CHECK();

@@ -285,6 +285,65 @@ def gemm_sweep(iters=10, shapes=None, tiles=None):
     _lib.check_device_errors()
 
 
+def sliced_sweep(iters=10):
+    """The plain projections of a block at block-decode row counts, each followed by the
+    residual-add + RMSNorm kernel that consumes it: library GEMM against this package's GEMM with
+    the K range cut into slices (``ops.linear_partials``) at several slice counts and tiles.
+    Back-to-back launches over rotating weight copies, replayed as a CUDA graph, one event pair
+    around all replays."""
+    import torch.nn.functional as F
+
+    shapes = [("attn_out decode", 512, 4096, 4096), ("ff_out decode", 512, 12288, 4096),
+              ("attn_out decode, 8 requests", 256, 4096, 4096), ("ff_out decode, 8 requests", 256, 12288, 4096),
+              ("o_proj dream decode", 1024, 3584, 3584), ("down_proj dream decode", 1024, 18944, 3584)]
+    for name, M, K, N in shapes:
+        copies = max(2, min(8, int((1 << 30) // (N * K * 2))))
+        x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+        ws = [torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * K ** -0.5 for _ in range(copies)]
+        res = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+        nw = torch.ones(N, device=DEV, dtype=torch.bfloat16)
+
+        def timeit(fn):
+            # the launches of one pass over the weight copies as a CUDA graph: two small kernels per
+            # projection would otherwise be timed at the host's launch rate
+            for w in ws[:2]:
+                fn(w)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for w in ws:
+                    fn(w)
+            graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) * 1e-3 / (iters * copies)
+
+        t_lib = timeit(lambda w: F.linear(x, w))
+        t_lib2 = timeit(lambda w: ops.add_rmsnorm(res, F.linear(x, w), nw, 1e-5))
+        planned = ops.linear_partials_splits(M, K, N)
+        print(f"{name:30s} M={M} K={K} N={N}  library {t_lib * 1e6:7.1f} us, + add_rmsnorm {t_lib2 * 1e6:7.1f} us;"
+              f" planned slices {planned}", flush=True)
+        for tile in ((1, 256), (1, 240), (2, 256)):
+            if tile[0] == 2 and M <= 256:
+                continue
+            for s in (1, 2, 4):
+                try:
+                    t = timeit(lambda w: ops.linear_partials(x, w, s, tile))
+                    t2 = timeit(lambda w: ops.add_rmsnorm(res, ops.linear_partials(x, w, s, tile), nw, 1e-5))
+                    print(f"    tile {tile} slices {s}: {t * 1e6:7.1f} us ({t_lib / t:4.2f}x library), "
+                          f"+ add_rmsnorm {t2 * 1e6:7.1f} us ({t_lib2 / t2:4.2f}x)", flush=True)
+                except (NotImplementedError, _lib.AcacheError) as exc:
+                    print(f"    tile {tile} slices {s}: {exc}", flush=True)
+        del ws, x
+        torch.cuda.empty_cache()
+    _lib.check_device_errors()
+
+
 def mma_rate():
     """Rate at which one issuing thread's tcgen05.mma stream is retired (no memory traffic): per
     product width N, CTA group, number of alternating accumulators, commits and k steps per loop."""
@@ -464,11 +523,16 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--json", action="store_true")
     ap.add_argument("--mma-rate", action="store_true", help="issue rate of a stream of tcgen05.mma without memory traffic")
+    ap.add_argument("--sliced-sweep", action="store_true",
+                    help="plain projections with the K range cut into slices (+ the norm kernel that adds them)")
     ap.add_argument("--fused-sweep", action="store_true", help="fused projections against library GEMM + separate kernel")
     ap.add_argument("--gemm-sweep", action="store_true", help="projection GEMMs at several tile shapes against the library")
     args = ap.parse_args(argv)
     if args.gemm_sweep:
         gemm_sweep(args.iters)
+        return
+    if args.sliced_sweep:
+        sliced_sweep(args.iters)
         return
     if args.fused_sweep:
         fused_sweep(args.iters)

@@ -22,17 +22,20 @@ def build_rope_table(length: int, head_dim: int, theta: float, dtype: torch.dtyp
 # (``ops.linear*``) instead of the library GEMM, for 16-bit models whose shapes the kernels take:
 #   OWN_QKV      q/k/v projection with bias, RoPE and the cache scatter in its epilogue
 #   OWN_GATE_UP  gate and up projections as one GEMM with the gated activation in its epilogue
-#   OWN_DENSE    the plain projections (attention output, feed-forward output)
+#   OWN_DENSE    the plain projections (attention output, feed-forward output): "sliced" = where
+#                the K range is cut into slices (few rows: block decode), True = always
 #   OWN_HEAD     the output head; for greedy unmasking it returns arg-max and confidence and
 #                never writes the logits
 # Without a TMA multicast of operand tiles every SM pulls its own tiles from L2, which bounds a
 # CTA-pair GEMM at 55-70 GB/s of operand bytes per SM: 0.82-0.93 of the library GEMM at these
 # shapes.  With the work fused into their epilogues the QKV, gate/up and output-head projections
-# come out level with or ahead of the library GEMM plus the separate kernels, so they are on; the
-# two plain projections (4096 output columns: too few tiles for 74 CTA pairs) stay with the library.
+# come out level with or ahead of the library GEMM plus the separate kernels, so they are on.  The
+# two plain projections have 4096 output columns: at block-decode row counts that is 16-32 whole
+# tiles for 74 CTA pairs, so there the K range is cut into slices that run as tiles of their own
+# and the normalisation kernel that follows adds the fp32 slices (``dense_pending``).
 OWN_QKV = True
 OWN_GATE_UP = True
-OWN_DENSE = False
+OWN_DENSE = "sliced"
 OWN_HEAD = True
 
 # The older single-CTA form of the fused QKV projection (128 x 128 tiles); kept for comparison,
@@ -48,9 +51,31 @@ def set_own_gemm(on: bool):
 
 def dense(x, weight, bias=None):
     """An ``nn.Linear`` of the model blocks on 2-D activations."""
-    if OWN_DENSE and ops._gemm_ok(x, weight):
+    if OWN_DENSE is True and ops._gemm_ok(x, weight):
         return ops.linear(x, weight, bias)
     return torch.nn.functional.linear(x, weight, bias)
+
+
+def dense_pending(x, weight, bias=None):
+    """A projection whose output is only ever added to the residual stream by the next
+    ``RMSNorm.forward(x, delta)``: returns either the output itself or, where slicing the K range
+    pays (``ops.linear_partials_splits``), its float32 slices ``[n_splits, n, out]``."""
+    if OWN_DENSE and bias is None and ops._gemm_ok(x, weight):
+        if ops.linear_partials_splits(x.shape[0], x.shape[1], weight.shape[0]) > 1:
+            return ops.linear_partials(x, weight)
+        if OWN_DENSE is True:
+            return ops.linear(x, weight)
+        return torch.nn.functional.linear(x, weight)
+    if OWN_DENSE is True and ops._gemm_ok(x, weight):
+        return ops.linear(x, weight, bias)
+    return torch.nn.functional.linear(x, weight, bias)
+
+
+def select_pending(delta, rows):
+    """``delta`` restricted to the given rows, for either form ``dense_pending`` returns."""
+    if delta is None:
+        return None
+    return delta.index_select(1 if delta.dim() == 3 else 0, rows)
 
 
 class FusedProjections:
@@ -165,10 +190,12 @@ class RMSNorm(nn.Module):
 
     def forward(self, x, delta=None):
         """``delta`` (optional): a residual update that is added to ``x`` IN PLACE before the
-        normalisation (one fused kernel)."""
+        normalisation (one fused kernel); either form that ``dense_pending`` returns."""
         if delta is None:
             return ops.rmsnorm(x, self.weight, self.eps)
         if x.shape[-1] % (16 // x.element_size()) != 0 or x.shape[-1] > 1024 * (16 // x.element_size()):
+            if delta.dim() == 3:    # float32 slices of the projection (``dense_pending``)
+                delta = delta.sum(0).to(x.dtype)
             x.add_(delta)  # row shapes the fused kernel does not take
             return ops.rmsnorm(x, self.weight, self.eps)
         return ops.add_rmsnorm(x, delta, self.weight, self.eps)

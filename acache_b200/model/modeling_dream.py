@@ -18,7 +18,7 @@ from ..utils import get_context
 from .attention import Attention
 from .configuration import DreamConfig
 from . import modeling_common as mc
-from .modeling_common import FusedProjections, RMSNorm, RopeCache, concat_gate_up, dense, gated_mlp_input, project_qkv
+from .modeling_common import FusedProjections, RMSNorm, RopeCache, concat_gate_up, dense_pending, gated_mlp_input, project_qkv, select_pending
 
 
 class DreamMLP(nn.Module):
@@ -41,7 +41,7 @@ class DreamMLP(nn.Module):
             self._gate_up_w = concat_gate_up(self.gate_proj, self.up_proj)
             self._fused.reset(self._params())
         h = gated_mlp_input(x, self._fused, self.gate_proj, self.up_proj, self.act, self._gate_up_w)
-        return dense(h, self.down_proj.weight)
+        return dense_pending(h, self.down_proj.weight)
 
 
 class DreamSdpaAttention(nn.Module):
@@ -88,7 +88,7 @@ class DreamSdpaAttention(nn.Module):
         q, k, v = project_qkv(x, self._qkv_w, self._qkv_b, nh, hkv, D, position_ids, cos, sin, attn, ctx, self._fused)
         o = attn(q, k, v).reshape(n, nh * D)
         attn.kv_already_stored = False
-        return dense(o, self.o_proj.weight)
+        return dense_pending(o, self.o_proj.weight)
 
 
 class DreamDecoderLayer(nn.Module):
@@ -173,7 +173,7 @@ class DreamModel(nn.Module):
         if compute_logits:
             if logits_keep_indices is not None:
                 x = x.index_select(0, logits_keep_indices)
-                delta = delta.index_select(0, logits_keep_indices) if delta is not None else None
+                delta = select_pending(delta, logits_keep_indices)
             x = self.model.norm(x, delta)
             if greedy_stats and mc.OWN_HEAD and ops._gemm_ok(x, self.lm_head.weight):
                 return SimpleNamespace(logits=None, stats=ops.linear_argmax(x, self.lm_head.weight), hidden_states=None)

@@ -21,7 +21,7 @@ from ..utils import get_context
 from .attention import Attention
 from .configuration import LLaDAConfig
 from . import modeling_common as mc
-from .modeling_common import FusedProjections, RMSNorm, RopeCache, concat_gate_up, dense, gated_mlp_input, project_qkv
+from .modeling_common import FusedProjections, RMSNorm, RopeCache, concat_gate_up, dense_pending, gated_mlp_input, project_qkv, select_pending
 
 
 class LLaDALlamaBlock(nn.Module):
@@ -83,9 +83,9 @@ class LLaDALlamaBlock(nn.Module):
         q, k, v = project_qkv(h, self._qkv_w, self._qkv_b, nh, hkv, D, position_ids, cos, sin, attn, ctx, self._fused)
         att = attn(q, k, v).reshape(n, nh * D)
         attn.kv_already_stored = False
-        h = self.ff_norm(x, dense(att, self.attn_out.weight, self.attn_out.bias))
+        h = self.ff_norm(x, dense_pending(att, self.attn_out.weight, self.attn_out.bias))
         h = gated_mlp_input(h, self._fused, self.ff_proj, self.up_proj, cfg.activation_type, self._gate_up_w)
-        return x, dense(h, self.ff_out.weight, self.ff_out.bias)
+        return x, dense_pending(h, self.ff_out.weight, self.ff_out.bias)
 
 
 class LLaDAModel(nn.Module):
@@ -127,7 +127,7 @@ class LLaDAModel(nn.Module):
         if compute_logits:
             if logits_keep_indices is not None:
                 x = x.index_select(0, logits_keep_indices)
-                delta = delta.index_select(0, logits_keep_indices) if delta is not None else None
+                delta = select_pending(delta, logits_keep_indices)
             x = self.transformer["ln_f"](x, delta)
             head = self.transformer["wte"] if self.config.weight_tying else self.transformer["ff_out"]
             if (greedy_stats and mc.OWN_HEAD and getattr(head, "bias", None) is None and not self.config.scale_logits

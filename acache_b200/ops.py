@@ -176,6 +176,27 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     return out
 
 
+def linear_partials_splits(n_rows: int, in_features: int, out_features: int) -> int:
+    """Slices of the ``in_features`` range that ``linear_partials`` would use for this shape; 1 means
+    the projection has enough output tiles to fill the GPU whole (use ``linear``)."""
+    return int(_lib.load().acache_linear_partials_splits(int(n_rows), int(in_features), int(out_features)))
+
+
+def linear_partials(x: torch.Tensor, weight: torch.Tensor, n_splits: int = 0, tile=(0, 0)) -> torch.Tensor:
+    """``x [n, in] @ weight[out, in]^T`` left as fp32 sums over ``n_splits`` slices of the ``in`` range:
+    returns ``[n_splits, n, out]`` float32, to be summed by ``add_rmsnorm`` (which takes it as its
+    update).  For projections with too few output tiles to occupy every SM with whole tiles."""
+    assert _gemm_ok(x, weight), "shape or dtype the projection kernel does not take"
+    n, N = x.shape[0], weight.shape[0]
+    s = int(n_splits) or linear_partials_splits(n, x.shape[1], N)
+    out = torch.empty(s, n, N, dtype=torch.float32, device=x.device)
+    if n:
+        check(_lib.load().acache_linear_partials(ptr(x), x.stride(0), n, x.shape[1], ptr(weight), N, dtype_code(x.dtype),
+                                                 ptr(out), s, tile[0], tile[1], ptr(_lib.err_flag(x.device)),
+                                                 stream_ptr()), "linear_partials")
+    return out
+
+
 def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, act: str = "silu") -> torch.Tensor:
     """``act(x @ Wg^T) * (x @ Wu^T)`` with the two weights interleaved by ``interleave_rows``."""
     assert _gemm_ok(x, weight_gate_up)
@@ -241,8 +262,20 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
 
 def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     """``x += delta`` (in place, rounded to x.dtype) and returns ``rmsnorm(x)``: the residual add of
-    the previous sub-layer fused into the normalisation that follows it."""
+    the previous sub-layer fused into the normalisation that follows it.  ``delta`` may also be the
+    float32 slices ``[n_splits, rows, cols]`` that ``linear_partials`` returns; they are summed in
+    order and rounded to x.dtype first."""
     shape = x.shape
+    if delta.dtype == torch.float32 and x.dtype != torch.float32:
+        # fp32 slices of a projection's K range (``linear_partials``): [n_splits, rows, cols]
+        x2 = x.view(-1, shape[-1])
+        assert delta.dim() == 3 and delta.shape[1:] == x2.shape and delta.stride(2) == 1 and x2.stride(1) == 1
+        y = torch.empty_like(x2)
+        check(_lib.load().acache_add_rmsnorm_partials(ptr(x2), x2.stride(0), ptr(delta), delta.shape[0], delta.stride(0),
+                                                      delta.stride(1), ptr(weight), ptr(y), y.stride(0), x2.shape[0],
+                                                      x2.shape[1], float(eps), dtype_code(x.dtype), stream_ptr()),
+              "add_rmsnorm_partials")
+        return y.view(shape)
     x2, d2 = x.view(-1, shape[-1]), delta.reshape(-1, shape[-1])
     assert x2.stride(1) == 1 and d2.stride(1) == 1 and x2.shape == d2.shape
     y = torch.empty_like(x2)

@@ -354,9 +354,10 @@ def run_ours(args):
         modeling_common.set_own_gemm(args.projections == "own")
         if args.projections not in ("own", "library"):
             on = set(args.projections.split(","))
-            assert on <= {"qkv", "gate_up", "dense", "head"}, on
+            assert on <= {"qkv", "gate_up", "dense", "dense_sliced", "head"}, on
             modeling_common.OWN_QKV, modeling_common.OWN_GATE_UP = "qkv" in on, "gate_up" in on
-            modeling_common.OWN_DENSE, modeling_common.OWN_HEAD = "dense" in on, "head" in on
+            modeling_common.OWN_DENSE = True if "dense" in on else ("sliced" if "dense_sliced" in on else False)
+            modeling_common.OWN_HEAD = "head" in on
 
     wl = dict(WORKLOADS[args.workload])
     if args.batch:
@@ -633,8 +634,9 @@ def main():
     ap.add_argument("--no-subpaths", action="store_true")
     ap.add_argument("--projections", default="default",
                     help="debug only: 'own' / 'library' = every projection on this package's GEMM kernels / on the "
-                         "library GEMM; or a comma list out of qkv,gate_up,dense,head naming the ones on this "
-                         "package's kernels")
+                         "library GEMM; or a comma list out of qkv,gate_up,dense,dense_sliced,head naming the ones "
+                         "on this package's kernels (dense_sliced: the plain projections only where their K range "
+                         "is cut into slices; the default is qkv,gate_up,dense_sliced,head)")
     ap.add_argument("--group-shared-span", type=int, default=-1, choices=[-1, 0, 1],
                     help="block-decode attention serves two requests of a KV head per CTA (-1: the engine's default)")
     ap.add_argument("--mode", default="acache", choices=["acache", "dkv_acache", "dual_cache"],

@@ -127,6 +127,19 @@ ACACHE_API int acache_linear(const void* x, int64_t x_stride, int n_rows, int in
                              int out_features, const void* bias, int dtype, void* out, int64_t out_stride,
                              int tile_mb, int tile_bn, int32_t* err_flag, void* stream);
 
+/* The same projection (no bias) for shapes with so few 256-column output tiles that whole tiles
+ * would leave most CTA pairs idle (the attention-output and feed-forward-output projections of a
+ * block-decode step, modeling_llada.py:738,763; modeling_dream.py:303,354): the in_features range
+ * is cut into n_splits slices, every (tile, slice) runs on a pair of its own and leaves its fp32
+ * sums in partials[slice][n_rows][out_features] (dense).  acache_add_rmsnorm_partials consumes
+ * them.  acache_linear_partials_splits returns the slice count the launch would choose for a shape
+ * (1 = slicing does not pay, use acache_linear); n_splits = 0 asks for that count, and a count
+ * that would leave a slice without a 64-wide k block returns ACACHE_EINVAL. */
+ACACHE_API int acache_linear_partials_splits(int n_rows, int in_features, int out_features);
+ACACHE_API int acache_linear_partials(const void* x, int64_t x_stride, int n_rows, int in_features, const void* weight,
+                                      int out_features, int dtype, float* partials, int n_splits, int tile_mb,
+                                      int tile_bn, int32_t* err_flag, void* stream);
+
 /* acache_linear_swiglu: the gate and up projections and act(gate) * up (modeling_llada.py:757-763,
  * modeling_dream.py:297-303) in one GEMM.  weight_gate_up is [2 * ffn_features, in_features] with the
  * two projections interleaved in groups of 8 rows: rows 16g..16g+7 are gate rows 8g..8g+7, rows
@@ -296,6 +309,14 @@ ACACHE_API int acache_rmsnorm(const void* x, int64_t x_stride, const void* weigh
 ACACHE_API int acache_add_rmsnorm(void* x, int64_t x_stride, const void* delta, int64_t d_stride, const void* weight,
                                   void* y, int64_t y_stride, int n_rows, int n_cols, float eps, int dtype,
                                   void* stream);
+/* The same with the update given as the fp32 K-range slices that acache_linear_partials leaves:
+ * partials[s][row][col], rows p_stride floats apart, slices split_stride floats apart.  The
+ * slices are summed in order and rounded to `dtype` (the projection's output as a GEMM in `dtype`
+ * leaves it) before the add. */
+ACACHE_API int acache_add_rmsnorm_partials(void* x, int64_t x_stride, const float* partials, int n_splits,
+                                           int64_t split_stride, int64_t p_stride, const void* weight, void* y,
+                                           int64_t y_stride, int n_rows, int n_cols, float eps, int dtype,
+                                           void* stream);
 /* y = act(gate) * up, act: 0 = SiLU, 1 = ReLU, 2 = GELU(erf)
  * (nano-vdllm/model/modeling_llada.py:757-763, nano-vdllm/model/modeling_dream.py:297-303). */
 ACACHE_API int acache_act_mul(const void* gate, const void* up, void* y, int64_t n, int act, int dtype, void* stream);

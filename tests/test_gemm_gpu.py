@@ -48,6 +48,72 @@ def test_linear_matches_fp32_reference(n, k, m_out, tile):
     _lib.check_device_errors()
 
 
+@pytest.mark.parametrize("tile", [(0, 0), (1, 256), (2, 256), (1, 112)])
+@pytest.mark.parametrize("n,k,m_out,splits", [(300, 1024, 384, 3), (77, 576, 272, 2), (1, 512, 64, 8), (512, 4096, 4096, 0),
+                                              (512, 12288, 4096, 0), (513, 1152, 2048, 5), (256, 4096, 4096, 0)])
+def test_linear_partials_sum_to_the_projection(n, k, m_out, splits, tile):
+    """The fp32 slices of the K range add up to the fp32 product (tolerance: fp32 summation-order
+    noise, 1e-4 of the largest entry); a slice count of 0 takes the launch's own plan."""
+    _lib, ops = _ops()
+    g = torch.Generator().manual_seed(n + k)
+    x = torch.randn(n, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(m_out, k, generator=g) * k ** -0.5).to(torch.bfloat16)
+    ref = x.float() @ w.float().T
+    parts = ops.linear_partials(x.to(DEV), w.to(DEV), splits, tile)
+    want = splits or ops.linear_partials_splits(n, k, m_out)
+    assert parts.shape == (want, n, m_out) and parts.dtype == torch.float32
+    if splits == 0 and n >= 256:
+        assert want >= 2          # the block-decode shapes are sliced
+    torch.testing.assert_close(parts.sum(0).cpu(), ref, rtol=1e-4, atol=1e-4 * ref.abs().max().item())
+    if want > 1:                  # every slice carries its own part of the K range
+        k_per = -(-(-(-k // 64)) // want) * 64
+        ref0 = x[:, :k_per].float() @ w[:, :k_per].float().T
+        torch.testing.assert_close(parts[0].cpu(), ref0, rtol=1e-4, atol=1e-4 * ref.abs().max().item())
+    _lib.check_device_errors()
+
+
+def test_linear_partials_rejects_an_empty_slice():
+    _lib, ops = _ops()
+    x = torch.zeros(16, 128, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(64, 128, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ValueError):
+        ops.linear_partials(x, w, 3)          # two k blocks cannot feed three slices
+    assert ops.linear_partials(x, w, 2).shape == (2, 16, 64)
+    _lib.check_device_errors()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("n,cols,splits", [(37, 4096, 4), (512, 4096, 2), (5, 1024, 1), (9, 3584, 3)])
+def test_add_rmsnorm_takes_fp32_slices_bit_exactly(n, cols, splits, dtype):
+    """``add_rmsnorm`` on the slices = the slices summed in order in fp32, rounded to the model
+    dtype, then the ordinary fused add + normalisation: same bits in x and in y."""
+    _lib, ops = _ops()
+    g = torch.Generator().manual_seed(n + cols)
+    x = torch.randn(n, cols, generator=g).to(dtype).to(DEV)
+    parts = torch.randn(splits, n, cols, generator=g).to(DEV)
+    wt = (1 + 0.1 * torch.randn(cols, generator=g)).to(dtype).to(DEV)
+    acc = torch.zeros(n, cols, device=DEV)
+    for s in range(splits):
+        acc = acc + parts[s]
+    x_ref = x.clone()
+    y_ref = ops.add_rmsnorm(x_ref, acc.to(dtype), wt, 1e-5)
+    x_got = x.clone()
+    y_got = ops.add_rmsnorm(x_got, parts, wt, 1e-5)
+    assert torch.equal(x_got, x_ref) and torch.equal(y_got, y_ref)
+    # strided slices: rows of a wider buffer
+    wide = torch.randn(splits, n, cols + 64, generator=g).to(DEV)
+    view = wide[:, :, 32:32 + cols]
+    acc = torch.zeros(n, cols, device=DEV)
+    for s in range(splits):
+        acc = acc + view[s]
+    x_ref = x.clone()
+    y_ref = ops.add_rmsnorm(x_ref, acc.to(dtype), wt, 1e-5)
+    x_got = x.clone()
+    y_got = ops.add_rmsnorm(x_got, view, wt, 1e-5)
+    assert torch.equal(x_got, x_ref) and torch.equal(y_got, y_ref)
+    _lib.check_device_errors()
+
+
 def test_linear_takes_strided_rows_and_fp16():
     _lib, ops = _ops()
     g = torch.Generator().manual_seed(3)
