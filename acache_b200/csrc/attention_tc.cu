@@ -92,6 +92,8 @@ __global__ void __launch_bounds__(LOADERS ? NT_LOAD : NT_ALL, 2) attention_tc_ke
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
+  chain_release();
+  chain_wait();
   if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled operand layout needs 1024-byte aligned atoms
     if (threadIdx.x == 0 && err_flag) atomicExch(err_flag, 6);
     return;
@@ -874,11 +876,13 @@ static int launch(const AttnArgs& a, const SplitArgs* split) {
   do {                                                                                                                \
     auto kern = attention_tc_kernel<T, TR, TC, D, KS, SPL, CP, LD>;                                                   \
     ACACHE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));            \
-    kern<<<grid, LD ? NT_LOAD : NT_ALL, smem, a.st>>>(                                                                \
+    ACACHE_CUDA_CHECK(launch_chained(                                                                                 \
+        kern, grid, dim3(LD ? NT_LOAD : NT_ALL), smem, a.st,                                                          \
         (const T*)a.q, a.q_stride, (T*)a.out, a.o_stride, (const T*)a.k_cache, (const T*)a.v_cache, a.num_slots,      \
         a.n_heads, a.n_kv_heads, a.cu_q, a.cu_k, a.slot_map, a.block_tables, a.table_stride, a.block_size,            \
-        a.scale * 1.4426950408889634f, a.shared_prefix_len, a.shared_kv_lens, relocate ? a.affix_shifts : nullptr,    \
-        (const TR*)a.rope_cos, (const TR*)a.rope_sin, a.rope_stride, a.rope_rows, a.err_flag, sp);                    \
+        a.scale * 1.4426950408889634f, a.shared_prefix_len, a.shared_kv_lens,                                         \
+        relocate ? a.affix_shifts : (const int32_t*)nullptr, (const TR*)a.rope_cos, (const TR*)a.rope_sin,            \
+        a.rope_stride, a.rope_rows, a.err_flag, sp));                                                                 \
   } while (0)
   // requests of at most 32 virtual rows (block decode): spread the softmax over the four warps
   // and give the K/V staging to four more warps

@@ -28,6 +28,37 @@ inline int dtype_bytes(int dtype) { return dtype == ACACHE_F32 ? 4 : 2; }
 inline bool dtype_ok(int dtype) { return dtype == ACACHE_F32 || dtype == ACACHE_F16 || dtype == ACACHE_BF16; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// ---- programmatic dependent launch ------------------------------------------------
+// A kernel launched with `launch_chained` may become resident while the kernel before it in the
+// stream is still running (as SMs free up), once every CTA of that kernel has executed
+// `chain_release()`; it must not touch global memory before `chain_wait()`, which returns when
+// the kernel before it has completed and its writes are visible.  Kernels of a decode step
+// release at their first instruction and wait after their on-chip set-up (barriers, TMEM), so
+// launch latency and set-up overlap the tail of the previous kernel; the order of all global
+// memory accesses stays that of plain stream order.  Both are no-ops in a kernel launched the
+// ordinary way.
+#ifdef __CUDACC__
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
+bool chained_launches();     // false when ACACHE_CHAINED_LAUNCHES=0 is set in the environment
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                  Args... args) {
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = grid;
+  lc.blockDim = block;
+  lc.dynamicSmemBytes = smem;
+  lc.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at;
+  lc.numAttrs = chained_launches() ? 1 : 0;
+  return cudaLaunchKernelEx(&lc, kern, static_cast<KArgs>(args)...);
+}
+
 // ---- element conversion ---------------------------------------------------------
 template <typename T> __device__ __forceinline__ float to_f32(T x);
 template <> __device__ __forceinline__ float to_f32<float>(float x) { return x; }

@@ -269,6 +269,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NT, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                  const __grid_constant__ Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
+  chain_release();
   const int BN = p.BN, S = p.stages, AS = p.acc_stages;
   const int G = p.group;                       // stages released together (1 or 2; S is a multiple)
   const int b_bytes = (BN / 2) * BK * 2;
@@ -318,6 +319,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   const uint32_t tmem_base = *tmem_slot;
   if (tid == 0 && (tmem_base & 0xFFFFu) != 0) *abort_flag = 1;   // the pair needs the same columns in both CTAs
   __syncthreads();
+  chain_wait();                // everything above is on-chip set-up; X may still be being written until here
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -562,7 +564,7 @@ static int launch_mb(const CUtensorMap& mx, const CUtensorMap& mw, const Params&
   const int m_tiles = (p.M + 256 * p.MB - 1) / (256 * p.MB), n_tiles = (p.N + p.BN - 1) / p.BN;
   const long total = (long)m_tiles * n_tiles * p.ksplit;
   const int pairs = total < kPairs ? (int)total : kPairs;
-  kern<<<2 * pairs, NT, tile.smem, st>>>(mx, mw, p);
+  ACACHE_CUDA_CHECK(launch_chained(kern, dim3(2 * pairs), dim3(NT), tile.smem, st, mx, mw, p));
   ACACHE_LAUNCH_CHECK();
   return ACACHE_OK;
 }
@@ -600,15 +602,18 @@ static int prepare(const void* x, int64_t ldx, const void* w, int M, int N, int 
 }
 
 // Slices of the K range for a projection whose whole tiles (256 rows x 256 columns per pair) would
-// occupy at most half of the 74 pairs: as many as still run in one wave, at most 4 (measured on B200:
-// 512 x 4096 x 4096 in 23 us with 2 slices against 33 us whole; 256 rows: 19 us with 4 against 33 us;
-// more slices only add fp32 traffic), at least 8 k blocks each.
+// occupy at most half of the 74 pairs: as many as still run in one wave, at most 4.  Measured on
+// B200 (bf16, 4096 output columns): 512 rows, K = 4096: 22 us with 2 slices against 31 us whole;
+// K = 12288: 46 against 73 us; 256 rows, K = 12288: 31 us with 4 slices against 72 us; more slices
+// only add fp32 traffic.  Pipeline fill, the fp32 epilogue and the slices' extra traffic in the
+// consumer cost a sliced launch 6-9 us whatever K, so a slice gets at least 48 k blocks; shorter
+// K ranges are not sliced (return 1) and the caller takes a whole-tile GEMM.
 static int plan_splits(int M, int N, int K) {
   const long tiles = (long)((M + 255) / 256) * ((N + 255) / 256);
   const int k_blocks = (K + BK - 1) / BK;
   long s = kPairs / tiles;
   if (s > 4) s = 4;
-  while (s > 1 && (k_blocks / s < 8 || (s - 1) * ((k_blocks + s - 1) / s) >= k_blocks)) --s;
+  while (s > 1 && (k_blocks / s < 48 || (s - 1) * ((k_blocks + s - 1) / s) >= k_blocks)) --s;
   return s < 2 ? 1 : (int)s;
 }
 

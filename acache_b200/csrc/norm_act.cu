@@ -9,6 +9,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const T* __restrict__ x, i
                                                       const T* __restrict__ w, T* __restrict__ y, int64_t y_stride,
                                                       int n_cols, float eps) {
   constexpr int E = 16 / sizeof(T);
+  chain_release();
+  chain_wait();
   const int row = blockIdx.x;
   const T* xr = x + (int64_t)row * x_stride;
   T* yr = y + (int64_t)row * y_stride;
@@ -69,6 +71,8 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(T* __restrict__ x, int
                                                           const float* __restrict__ partials, int n_splits,
                                                           int64_t split_stride) {
   constexpr int E = 16 / sizeof(T);
+  chain_release();
+  chain_wait();
   const int row = blockIdx.x;
   T* xr = x + (int64_t)row * x_stride;
   const T* dr = PART ? nullptr : delta + (int64_t)row * d_stride;
@@ -260,11 +264,11 @@ extern "C" int acache_rmsnorm(const void* x, int64_t x_stride, const void* weigh
   const int nvec = n_cols / E;
   ACACHE_DISPATCH_DTYPE(dtype, T, {
     if (vec && nvec <= 256) {
-      rmsnorm_kernel<T, 1><<<n_rows, 256, 0, st>>>((const T*)x, x_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps);
+      ACACHE_CUDA_CHECK(launch_chained(rmsnorm_kernel<T, 1>, dim3(n_rows), dim3(256), 0, st, (const T*)x, x_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps));
     } else if (vec && nvec <= 512) {
-      rmsnorm_kernel<T, 2><<<n_rows, 256, 0, st>>>((const T*)x, x_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps);
+      ACACHE_CUDA_CHECK(launch_chained(rmsnorm_kernel<T, 2>, dim3(n_rows), dim3(256), 0, st, (const T*)x, x_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps));
     } else if (vec && nvec <= 1024) {
-      rmsnorm_kernel<T, 4><<<n_rows, 256, 0, st>>>((const T*)x, x_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps);
+      ACACHE_CUDA_CHECK(launch_chained(rmsnorm_kernel<T, 4>, dim3(n_rows), dim3(256), 0, st, (const T*)x, x_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps));
     } else {
       rmsnorm_generic_kernel<T><<<n_rows, 256, 0, st>>>((const T*)x, x_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps);
     }
@@ -306,11 +310,11 @@ extern "C" int acache_add_rmsnorm(void* x, int64_t x_stride, const void* delta, 
   if (!vec || nvec > 1024) return ACACHE_EUNSUPPORTED;
   ACACHE_DISPATCH_DTYPE(dtype, T, {
     if (nvec <= 256) {
-      add_rmsnorm_kernel<T, 1, false><<<n_rows, 256, 0, st>>>((T*)x, x_stride, (const T*)delta, d_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps, nullptr, 0, 0);
+      ACACHE_CUDA_CHECK(launch_chained(add_rmsnorm_kernel<T, 1, false>, dim3(n_rows), dim3(256), 0, st, (T*)x, x_stride, (const T*)delta, d_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps, nullptr, 0, 0));
     } else if (nvec <= 512) {
-      add_rmsnorm_kernel<T, 2, false><<<n_rows, 256, 0, st>>>((T*)x, x_stride, (const T*)delta, d_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps, nullptr, 0, 0);
+      ACACHE_CUDA_CHECK(launch_chained(add_rmsnorm_kernel<T, 2, false>, dim3(n_rows), dim3(256), 0, st, (T*)x, x_stride, (const T*)delta, d_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps, nullptr, 0, 0));
     } else {
-      add_rmsnorm_kernel<T, 4, false><<<n_rows, 256, 0, st>>>((T*)x, x_stride, (const T*)delta, d_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps, nullptr, 0, 0);
+      ACACHE_CUDA_CHECK(launch_chained(add_rmsnorm_kernel<T, 4, false>, dim3(n_rows), dim3(256), 0, st, (T*)x, x_stride, (const T*)delta, d_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps, nullptr, 0, 0));
     }
   });
   ACACHE_LAUNCH_CHECK();
@@ -332,11 +336,11 @@ extern "C" int acache_add_rmsnorm_partials(void* x, int64_t x_stride, const floa
   if (!vec || nvec > 1024) return ACACHE_EUNSUPPORTED;
   ACACHE_DISPATCH_DTYPE(dtype, T, {
     if (nvec <= 256) {
-      add_rmsnorm_kernel<T, 1, true><<<n_rows, 256, 0, st>>>((T*)x, x_stride, nullptr, p_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps, partials, n_splits, split_stride);
+      ACACHE_CUDA_CHECK(launch_chained(add_rmsnorm_kernel<T, 1, true>, dim3(n_rows), dim3(256), 0, st, (T*)x, x_stride, nullptr, p_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps, partials, n_splits, split_stride));
     } else if (nvec <= 512) {
-      add_rmsnorm_kernel<T, 2, true><<<n_rows, 256, 0, st>>>((T*)x, x_stride, nullptr, p_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps, partials, n_splits, split_stride);
+      ACACHE_CUDA_CHECK(launch_chained(add_rmsnorm_kernel<T, 2, true>, dim3(n_rows), dim3(256), 0, st, (T*)x, x_stride, nullptr, p_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps, partials, n_splits, split_stride));
     } else {
-      add_rmsnorm_kernel<T, 4, true><<<n_rows, 256, 0, st>>>((T*)x, x_stride, nullptr, p_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps, partials, n_splits, split_stride);
+      ACACHE_CUDA_CHECK(launch_chained(add_rmsnorm_kernel<T, 4, true>, dim3(n_rows), dim3(256), 0, st, (T*)x, x_stride, nullptr, p_stride, (const T*)weight, (T*)y, y_stride, n_cols, eps, partials, n_splits, split_stride));
     }
   });
   ACACHE_LAUNCH_CHECK();

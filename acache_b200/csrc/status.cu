@@ -1,9 +1,19 @@
 // Status strings and the per-thread CUDA error record.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace acache {
 static thread_local cudaError_t g_last_error = cudaSuccess;
 void set_last_cuda_error(cudaError_t e) { g_last_error = e; }
+
+bool chained_launches() {
+  static const bool on = [] {
+    const char* v = getenv("ACACHE_CHAINED_LAUNCHES");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
 }  // namespace acache
 
 extern "C" const char* acache_status_string(int status) {

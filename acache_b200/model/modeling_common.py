@@ -31,8 +31,12 @@ def build_rope_table(length: int, head_dim: int, theta: float, dtype: torch.dtyp
 # shapes.  With the work fused into their epilogues the QKV, gate/up and output-head projections
 # come out level with or ahead of the library GEMM plus the separate kernels, so they are on.  The
 # two plain projections have 4096 output columns: at block-decode row counts that is 16-32 whole
-# tiles for 74 CTA pairs, so there the K range is cut into slices that run as tiles of their own
-# and the normalisation kernel that follows adds the fp32 slices (``dense_pending``).
+# tiles for 74 CTA pairs, so there the K range can be cut into slices that run as tiles of their
+# own, and the normalisation kernel that follows adds the fp32 slices (``dense_pending``).  A
+# sliced launch costs 6-9 us more than the library GEMM whatever K, so the launch plan
+# (``ops.linear_partials_splits``) only slices long K ranges: the feed-forward output projection
+# (K = 12288: 46 against 41 us) runs here, the attention output projection (K = 4096: 22 against
+# 15 us) stays with the library.
 OWN_QKV = True
 OWN_GATE_UP = True
 OWN_DENSE = "sliced"

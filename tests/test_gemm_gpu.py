@@ -50,7 +50,7 @@ def test_linear_matches_fp32_reference(n, k, m_out, tile):
 
 @pytest.mark.parametrize("tile", [(0, 0), (1, 256), (2, 256), (1, 112)])
 @pytest.mark.parametrize("n,k,m_out,splits", [(300, 1024, 384, 3), (77, 576, 272, 2), (1, 512, 64, 8), (512, 4096, 4096, 0),
-                                              (512, 12288, 4096, 0), (513, 1152, 2048, 5), (256, 4096, 4096, 0)])
+                                              (512, 12288, 4096, 0), (513, 1152, 2048, 5), (256, 4096, 4096, 0), (256, 4096, 4096, 4)])
 def test_linear_partials_sum_to_the_projection(n, k, m_out, splits, tile):
     """The fp32 slices of the K range add up to the fp32 product (tolerance: fp32 summation-order
     noise, 1e-4 of the largest entry); a slice count of 0 takes the launch's own plan."""
@@ -62,8 +62,8 @@ def test_linear_partials_sum_to_the_projection(n, k, m_out, splits, tile):
     parts = ops.linear_partials(x.to(DEV), w.to(DEV), splits, tile)
     want = splits or ops.linear_partials_splits(n, k, m_out)
     assert parts.shape == (want, n, m_out) and parts.dtype == torch.float32
-    if splits == 0 and n >= 256:
-        assert want >= 2          # the block-decode shapes are sliced
+    if splits == 0:               # the launch plan: only long K ranges with few output tiles are sliced
+        assert want == {(512, 4096): 1, (512, 12288): 2, (256, 4096): 1}[(n, k)]
     torch.testing.assert_close(parts.sum(0).cpu(), ref, rtol=1e-4, atol=1e-4 * ref.abs().max().item())
     if want > 1:                  # every slice carries its own part of the K range
         k_per = -(-(-(-k // 64)) // want) * 64
