@@ -52,6 +52,11 @@ _SIGNATURES = {
     "acache_anchor_importance": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                          c_int64, c_int, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_float,
                                          c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+    "acache_anchor_importance_batched_scratch_bytes": (c_int64, [c_int, c_int, c_int, c_int]),
+    "acache_anchor_importance_batched": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                                 c_int, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p,
+                                                 c_int64, c_int, c_int, c_float, c_void_p, c_int64, c_void_p, c_int64,
+                                                 c_void_p, c_void_p]),
     "acache_anchor_importance_static_scratch_bytes": (c_int64, []),
     "acache_anchor_importance_static": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                                 c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_int64, c_int,

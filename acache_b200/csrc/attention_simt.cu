@@ -366,13 +366,16 @@ __global__ void __launch_bounds__(kThreads) importance_partial_kernel(
   }
 }
 
+// blockIdx.y = request of a batched launch: its partial rows follow those of the requests before
+// it, its scores are `importance_stride` floats further on
 __global__ void importance_reduce_kernel(const float* __restrict__ partial, int n_partials, int affix_len,
-                                         float* __restrict__ importance) {
+                                         float* __restrict__ importance, int64_t importance_stride = 0) {
   const int a = blockIdx.x * blockDim.x + threadIdx.x;
   if (a >= affix_len) return;
+  partial += (int64_t)blockIdx.y * n_partials * affix_len;
   float s = 0.f;
   for (int p = 0; p < n_partials; ++p) s += partial[(int64_t)p * affix_len + a];
-  importance[a] += s;
+  importance[(int64_t)blockIdx.y * importance_stride + a] += s;
 }
 
 template <typename T, typename TR> struct PromoteA { using type = float; };
@@ -422,6 +425,12 @@ int importance_tc_dispatch(const void* q, int64_t q_stride, const int32_t* q_row
                            int rope_dtype, float scale, float* partial, int* n_partials, float* ml, int32_t* err_flag,
                            cudaStream_t st);
 int64_t importance_tc_ml_floats(int n_q_rows, int n_heads, int affix_len);
+int importance_tc_batched_dispatch(const void* q, int64_t q_stride, const int32_t* q_rows, const int32_t* req_off,
+                                   int n_requests, int max_q, int n_heads, int n_kv_heads, int head_dim, int dtype,
+                                   const void* affix_k, int64_t k_slot_stride, int affix_len, const int32_t* req_shift,
+                                   const void* rope_cos, const void* rope_sin, int64_t rope_stride, int rope_rows,
+                                   int rope_dtype, float scale, float* partial, int* n_partials, int32_t* err_flag,
+                                   cudaStream_t st);
 
 // implemented in attention_tc.cu: returns ACACHE_EUNSUPPORTED when it declines the shape
 int attention_tc_dispatch(const AttnArgs& a, int dtype, int rope_dtype);
@@ -582,6 +591,43 @@ extern "C" int acache_anchor_importance(const void* q, int64_t q_stride, const i
   });
 #undef IMP
   return ACACHE_EINVAL;
+}
+
+extern "C" int64_t acache_anchor_importance_batched_scratch_bytes(int n_requests, int max_q_rows, int n_heads,
+                                                                  int affix_len) {
+  if (n_requests <= 0 || max_q_rows <= 0 || n_heads <= 0 || affix_len <= 0) return 0;
+  return (int64_t)n_requests * importance_partial_floats(max_q_rows, n_heads, affix_len) * (int64_t)sizeof(float);
+}
+
+extern "C" int acache_anchor_importance_batched(const void* q, int64_t q_stride, const int32_t* q_rows,
+                                                const int32_t* q_row_offsets, int n_requests, int max_q_rows,
+                                                int n_heads, int n_kv_heads, int head_dim, int dtype,
+                                                const void* affix_k, int64_t k_slot_stride, int affix_len,
+                                                const int32_t* affix_shifts, const void* rope_cos,
+                                                const void* rope_sin, int64_t rope_row_stride, int rope_rows,
+                                                int rope_dtype, float scale, float* importance,
+                                                int64_t importance_stride, void* scratch, int64_t scratch_bytes,
+                                                int32_t* err_flag, void* stream) {
+  if (!dtype_ok(dtype) || !dtype_ok(rope_dtype)) return ACACHE_EINVAL;
+  if (n_requests < 0 || max_q_rows < 0 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 ||
+      head_dim <= 0 || affix_len < 0 || importance_stride < affix_len)
+    return ACACHE_EINVAL;
+  if (n_requests == 0 || max_q_rows == 0 || affix_len == 0) return ACACHE_OK;
+  if (!q || !q_rows || !q_row_offsets || !affix_k || !importance || !scratch) return ACACHE_EINVAL;
+  if (affix_shifts != nullptr && (!rope_cos || !rope_sin || rope_rows <= 0)) return ACACHE_EINVAL;
+  if (scratch_bytes < acache_anchor_importance_batched_scratch_bytes(n_requests, max_q_rows, n_heads, affix_len))
+    return ACACHE_EINVAL;
+  cudaStream_t st = (cudaStream_t)stream;
+  int n_partials = 0;
+  const int rc = importance_tc_batched_dispatch(q, q_stride, q_rows, q_row_offsets, n_requests, max_q_rows, n_heads,
+                                                n_kv_heads, head_dim, dtype, affix_k, k_slot_stride, affix_len,
+                                                affix_shifts, rope_cos, rope_sin, rope_row_stride, rope_rows, rope_dtype,
+                                                scale, (float*)scratch, &n_partials, err_flag, st);
+  if (rc != ACACHE_OK) return rc;
+  importance_reduce_kernel<<<dim3((affix_len + 255) / 256, n_requests), 256, 0, st>>>(
+      (const float*)scratch, n_partials, affix_len, importance, importance_stride);
+  ACACHE_LAUNCH_CHECK();
+  return ACACHE_OK;
 }
 
 // ------------------------------------------------------------------------------------

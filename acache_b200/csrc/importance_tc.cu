@@ -35,7 +35,8 @@ __global__ void __launch_bounds__(INT) importance_tc_kernel(
     const T* __restrict__ q, int64_t q_stride, const int32_t* __restrict__ q_rows, int n_q, int n_heads, int n_kv_heads,
     const T* __restrict__ affix_k, int64_t k_slot_stride, int affix_len, int affix_shift,
     const TR* __restrict__ rope_cos, const TR* __restrict__ rope_sin, int64_t rope_stride, float scale_log2,
-    float* __restrict__ partial, int32_t* err_flag, int mode, float* __restrict__ ml) {
+    float* __restrict__ partial, int32_t* err_flag, int mode, float* __restrict__ ml,
+    const int32_t* __restrict__ req_off, const int32_t* __restrict__ req_shift, int rope_rows) {
   constexpr int CH = D * (int)sizeof(T) / 16;
   constexpr int Q_BYTES = IBM * D * (int)sizeof(T);
   constexpr int K_BYTES = IBN * D * (int)sizeof(T);
@@ -52,8 +53,23 @@ __global__ void __launch_bounds__(INT) importance_tc_kernel(
   const int kvh = blockIdx.y;
   const int g = n_heads / n_kv_heads;
   const int m0 = blockIdx.x * IBM;
+  // several requests in one launch (unchunked form only): blockIdx.z is the request, its mask
+  // rows are q_rows[req_off[z] .. req_off[z + 1]), its rotation row req_shift[z]; its partial rows
+  // follow those of the requests before it
+  int req = 0;
+  if (req_off != nullptr) {
+    req = (int)blockIdx.z;
+    const int o = req_off[req];
+    n_q = max(req_off[req + 1] - o, 0);
+    q_rows += o;
+    affix_shift = req_shift != nullptr ? req_shift[req] : 0;
+    if (affix_shift < 0 || affix_shift >= max(rope_rows, 1)) {
+      if (tid == 0 && err_flag) atomicExch(err_flag, 4);
+      affix_shift = 0;
+    }
+  }
   const int vrows = n_q * g;
-  float* my_partial = partial + ((int64_t)blockIdx.y * gridDim.x + blockIdx.x) * affix_len;
+  float* my_partial = partial + (((int64_t)req * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * affix_len;
   if (m0 >= vrows || (smem_u32(smem_raw) & 1023u) != 0) {
     // the first cannot happen with the launch grid, the second would be a launch error: keep the
     // reduce kernel's input defined (every chunk writes the whole row: same zeros) and report
@@ -67,7 +83,7 @@ __global__ void __launch_bounds__(INT) importance_tc_kernel(
   const int tiles_all = (affix_len + IBN - 1) / IBN;
   const int t0 = mode == kBothPasses ? 0 : (int)blockIdx.z * kChunkTiles;
   const int n_tiles = mode == kBothPasses ? tiles_all : min(kChunkTiles, tiles_all - t0);
-  const int n_chunks = (int)gridDim.z;
+  const int n_chunks = req_off != nullptr ? 1 : (int)gridDim.z;
   // (maximum, denominator) of row `tid` for chunk c of this (KV head, row tile)
   float* my_ml = ml + (((int64_t)blockIdx.y * gridDim.x + blockIdx.x) * n_chunks) * (IBM * 2);
 
@@ -251,14 +267,39 @@ static int launch_importance_tc(const void* q, int64_t q_stride, const int32_t* 
   if (chunks <= 1 || ml == nullptr) {
     kern<<<grid, INT, smem, st>>>((const T*)q, q_stride, q_rows, n_q, n_heads, n_kv_heads, (const T*)affix_k,
                                   k_slot_stride, affix_len, affix_shift, (const TR*)rope_cos, (const TR*)rope_sin,
-                                  rope_stride, scale * 1.4426950408889634f, partial, err_flag, kBothPasses, partial);
+                                  rope_stride, scale * 1.4426950408889634f, partial, err_flag, kBothPasses, partial,
+                                  nullptr, nullptr, 0);
   } else {
     dim3 grid3(grid.x, grid.y, chunks);
     for (int mode = kPassOne; mode <= kPassTwo; ++mode)
       kern<<<grid3, INT, smem, st>>>((const T*)q, q_stride, q_rows, n_q, n_heads, n_kv_heads, (const T*)affix_k,
                                      k_slot_stride, affix_len, affix_shift, (const TR*)rope_cos, (const TR*)rope_sin,
-                                     rope_stride, scale * 1.4426950408889634f, partial, err_flag, mode, ml);
+                                     rope_stride, scale * 1.4426950408889634f, partial, err_flag, mode, ml, nullptr, nullptr, 0);
   }
+  ACACHE_LAUNCH_CHECK();
+  *n_partials = (int)(grid.x * grid.y);
+  return ACACHE_OK;
+}
+
+// All requests of a probe batch in one launch: grid.z = request.  `partial` gets n_requests groups
+// of *n_partials rows each.
+template <typename T, typename TR, int D>
+static int launch_importance_tc_batched(const void* q, int64_t q_stride, const int32_t* q_rows, const int32_t* req_off,
+                                        int n_requests, int max_q, int n_heads, int n_kv_heads, const void* affix_k,
+                                        int64_t k_slot_stride, int affix_len, const int32_t* req_shift,
+                                        const void* rope_cos, const void* rope_sin, int64_t rope_stride, int rope_rows,
+                                        float scale, float* partial, int* n_partials, int32_t* err_flag,
+                                        cudaStream_t st) {
+  using TC = typename PromoteI<T, TR>::type;
+  constexpr size_t smem = IBM * D * sizeof(T) + 2 * IBN * D * sizeof(T) + IBN * kPsLd * sizeof(float) + 64;
+  auto kern = importance_tc_kernel<T, TR, TC, D>;
+  ACACHE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int g = n_heads / n_kv_heads;
+  dim3 grid((max_q * g + IBM - 1) / IBM, n_kv_heads, n_requests);
+  kern<<<grid, INT, smem, st>>>((const T*)q, q_stride, q_rows, 0, n_heads, n_kv_heads, (const T*)affix_k, k_slot_stride,
+                                affix_len, 0, (const TR*)rope_cos, (const TR*)rope_sin, rope_stride,
+                                scale * 1.4426950408889634f, partial, err_flag, kBothPasses, partial, req_off, req_shift,
+                                rope_rows);
   ACACHE_LAUNCH_CHECK();
   *n_partials = (int)(grid.x * grid.y);
   return ACACHE_OK;
@@ -307,6 +348,39 @@ int importance_tc_dispatch(const void* q, int64_t q_stride, const int32_t* q_row
   if (rope_dtype == ACACHE_F16) { IMP_TC(__half, __half); }
   IMP_TC(__half, __nv_bfloat16);
 #undef IMP_TC
+}
+
+// The batched form: ACACHE_EUNSUPPORTED also for affixes long enough to be chunked (the caller
+// then loops over the requests).
+int importance_tc_batched_dispatch(const void* q, int64_t q_stride, const int32_t* q_rows, const int32_t* req_off,
+                                   int n_requests, int max_q, int n_heads, int n_kv_heads, int head_dim, int dtype,
+                                   const void* affix_k, int64_t k_slot_stride, int affix_len, const int32_t* req_shift,
+                                   const void* rope_cos, const void* rope_sin, int64_t rope_stride, int rope_rows,
+                                   int rope_dtype, float scale, float* partial, int* n_partials, int32_t* err_flag,
+                                   cudaStream_t st) {
+  if (dtype == ACACHE_F32 || (head_dim != 64 && head_dim != 128) || importance_tc_chunks(affix_len) > 1)
+    return ACACHE_EUNSUPPORTED;
+  if (!aligned16(q) || !aligned16(affix_k) || q_stride % 8 != 0 || k_slot_stride % 8 != 0) return ACACHE_EUNSUPPORTED;
+  if (n_requests > 65535) return ACACHE_EUNSUPPORTED;
+#define IMP_TCB(T, TR)                                                                                                 \
+  return head_dim == 128                                                                                               \
+             ? tc::launch_importance_tc_batched<T, TR, 128>(q, q_stride, q_rows, req_off, n_requests, max_q, n_heads,  \
+                                                            n_kv_heads, affix_k, k_slot_stride, affix_len, req_shift,  \
+                                                            rope_cos, rope_sin, rope_stride, rope_rows, scale, partial, \
+                                                            n_partials, err_flag, st)                                  \
+             : tc::launch_importance_tc_batched<T, TR, 64>(q, q_stride, q_rows, req_off, n_requests, max_q, n_heads,   \
+                                                           n_kv_heads, affix_k, k_slot_stride, affix_len, req_shift,   \
+                                                           rope_cos, rope_sin, rope_stride, rope_rows, scale, partial, \
+                                                           n_partials, err_flag, st)
+  if (dtype == ACACHE_BF16) {
+    if (rope_dtype == ACACHE_F32) { IMP_TCB(__nv_bfloat16, float); }
+    if (rope_dtype == ACACHE_BF16) { IMP_TCB(__nv_bfloat16, __nv_bfloat16); }
+    IMP_TCB(__nv_bfloat16, __half);
+  }
+  if (rope_dtype == ACACHE_F32) { IMP_TCB(__half, float); }
+  if (rope_dtype == ACACHE_F16) { IMP_TCB(__half, __half); }
+  IMP_TCB(__half, __nv_bfloat16);
+#undef IMP_TCB
 }
 
 }  // namespace acache

@@ -50,6 +50,8 @@ class Attention(nn.Module):
         self.kv_already_stored = False
         # set by the engine during the anchor-selection probe: one entry per request of the batch
         self.probe = None
+        # the same probes in the form of the batched score kernel (None: one request, or no mask rows)
+        self.probe_batch = None
 
     def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
         ctx = get_context()
@@ -67,9 +69,14 @@ class Attention(nn.Module):
             # (reference: nano-vdllm/model_runner.py:730-773)
             scale = self.scale if self.scale is not None else self.head_dim ** -0.5
             flat_k = k_cache.view(-1, self.num_kv_heads, self.head_dim)
-            for p in self.probe:
-                ops.anchor_importance(q, p.q_rows, flat_k[: p.affix_len], p.affix_shift, p.rope_cos, p.rope_sin,
-                                      scale, p.importance)
+            pb = self.probe_batch
+            if pb is not None and pb.usable:   # all requests in one launch
+                pb.usable = ops.anchor_importance_batched(q, pb.q_rows, pb.offsets, pb.max_q_rows, flat_k[: pb.affix_len],
+                                                          pb.shifts, pb.rope_cos, pb.rope_sin, scale, pb.importance)
+            if pb is None or not pb.usable:
+                for p in self.probe:
+                    ops.anchor_importance(q, p.q_rows, flat_k[: p.affix_len], p.affix_shift, p.rope_cos, p.rope_sin,
+                                          scale, p.importance)
         if not self.kv_already_stored:
             store_kvcache(k, v, k_cache, v_cache, ctx.slot_mapping)
         if ctx.use_acache:

@@ -243,6 +243,16 @@ class _Probe:
     __slots__ = ("q_rows", "affix_len", "affix_shift", "importance", "rope_cos", "rope_sin")
 
 
+class _ProbeBatch:
+    """The probes of one ragged forward in the form ``ops.anchor_importance_batched`` takes: all
+    mask rows behind one another, per-request offsets into them, rotation rows (None when no
+    request needs one) and the ``[requests, affix_len]`` score matrix.  ``usable`` is cleared by
+    the first layer whose call is declined, so the other layers loop over the requests at once."""
+
+    __slots__ = ("q_rows", "offsets", "max_q_rows", "shifts", "importance", "affix_len", "rope_cos", "rope_sin",
+                 "usable")
+
+
 class ModelRunner(DkvMixin):
     def __init__(self, model, config):
         self.config = config
@@ -443,7 +453,7 @@ class ModelRunner(DkvMixin):
             m.v_cache = self.kv_cache[1, layer_id]
             m.use_reference_attention = config.use_reference_attention
             m.shared_prefix_len = 0
-            m.probe = None
+            m.probe = m.probe_batch = None
         self.block_manager = BlockManager(config.num_kvcache_blocks, bs)
 
     def _flat_kv(self):
@@ -725,16 +735,30 @@ class ModelRunner(DkvMixin):
                 p.importance = importance[b]
                 p.rope_cos, p.rope_sin = a0.relocation_rope_cos, a0.relocation_rope_sin
                 probes.append(p)
+            batch = None
             if any(p.q_rows.size for p in probes):
-                dev_rows = self._staging.ship(**{f"r{i}": p.q_rows for i, p in enumerate(probes)})
+                host = {f"r{i}": p.q_rows for i, p in enumerate(probes)}
+                if len(probes) > 1:   # the same rows once more as one array for the batched score kernel
+                    counts = [int(p.q_rows.size) for p in probes]
+                    host["all"] = np.concatenate([p.q_rows for p in probes]).astype(np.int32)
+                    host["off"] = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+                    host["shift"] = np.asarray([p.affix_shift for p in probes], dtype=np.int32)
+                dev_rows = self._staging.ship(**host)
                 for i, p in enumerate(probes):
                     p.q_rows = dev_rows[f"r{i}"]
+                if len(probes) > 1:
+                    batch = _ProbeBatch()
+                    batch.q_rows, batch.offsets, batch.max_q_rows = dev_rows["all"], dev_rows["off"], max(counts)
+                    batch.shifts = dev_rows["shift"] if any(p.affix_shift for p in probes) else None
+                    batch.importance, batch.affix_len = importance, affix_len
+                    batch.rope_cos, batch.rope_sin = a0.relocation_rope_cos, a0.relocation_rope_sin
+                    batch.usable = True
             else:
                 for p in probes:
                     p.q_rows = torch.empty(0, dtype=torch.int32, device=self.device)
             self._finish_timing(timing, "anchor_selection_prepare", t_prep)
             for m in self._attn_layers:
-                m.probe = probes
+                m.probe, m.probe_batch = probes, batch
             t_fwd = self._start_timing()
             self._forward_model(input_ids, position_ids, compute_logits=False, max_pos=max(len(s) for s in seqs))
             self._finish_timing(timing, "anchor_selection_forward", t_fwd)
@@ -742,7 +766,7 @@ class ModelRunner(DkvMixin):
             self._add_timing_count(timing, "anchor_selection_sequences", len(seqs))
         finally:
             for m in self._attn_layers:
-                m.probe = None
+                m.probe = m.probe_batch = None
             reset_context()
             for seq in reversed(temporarily_allocated):
                 if seq.block_table:

@@ -64,6 +64,41 @@ def anchor_importance(q, q_rows, affix_k, affix_shift: int, rope_cos, rope_sin, 
         ptr(_lib.err_flag(q.device)), stream_ptr()), "anchor_importance", 2)
 
 
+def anchor_importance_batched(q, q_rows, q_row_offsets, max_q_rows: int, affix_k, affix_shifts, rope_cos, rope_sin,
+                              scale: float, importance) -> bool:
+    """``anchor_importance`` for all requests of a probe batch in one launch: request ``r`` owns the
+    mask rows ``q_rows[q_row_offsets[r]:q_row_offsets[r + 1]]`` (both int32 on the device, at most
+    ``max_q_rows`` rows per request), the rotation row ``affix_shifts[r]`` (int32 on the device, or
+    None) and the scores ``importance[r]`` (fp32 ``[n_requests, A]``, accumulated in place with the
+    bits of the per-request call).  Returns False, with nothing launched, for shapes only the
+    per-request call takes (fp32, head sizes other than 64 / 128, affixes beyond 2048 tokens)."""
+    assert q.is_cuda and q.dim() == 3 and q.stride(2) == 1 and q.stride(1) == q.shape[2]
+    assert q_rows.dtype == torch.int32 and q_rows.is_cuda and q_row_offsets.dtype == torch.int32 and q_row_offsets.is_cuda
+    assert affix_shifts is None or (affix_shifts.dtype == torch.int32 and affix_shifts.is_cuda)
+    assert affix_k.dim() == 3 and affix_k.stride(2) == 1 and affix_k.stride(1) == affix_k.shape[2]
+    assert importance.dtype == torch.float32 and importance.dim() == 2 and importance.stride(1) == 1
+    n_req, (nh, D) = q_row_offsets.numel() - 1, q.shape[1:]
+    A, hkv = affix_k.shape[:2]
+    assert importance.shape[0] == n_req and importance.shape[1] == A
+    if n_req <= 0 or max_q_rows <= 0 or A == 0:
+        return True
+    lib = _lib.load()
+    nbytes = lib.acache_anchor_importance_batched_scratch_bytes(n_req, int(max_q_rows), nh, A)
+    scratch = _scratch_for(q.device, nbytes)
+    if affix_shifts is not None:
+        rc, rs, rstride, rrows, rdt = ptr(rope_cos), ptr(rope_sin), rope_cos.stride(0), rope_cos.shape[0], dtype_code(rope_cos.dtype)
+    else:
+        rc, rs, rstride, rrows, rdt = None, None, 0, 0, _lib.F32
+    status = lib.acache_anchor_importance_batched(
+        ptr(q), q.stride(0), ptr(q_rows), ptr(q_row_offsets), n_req, int(max_q_rows), nh, hkv, D, dtype_code(q.dtype),
+        ptr(affix_k), affix_k.stride(0), A, ptr(affix_shifts), rc, rs, rstride, rrows, rdt, float(scale),
+        ptr(importance), importance.stride(0), ptr(scratch), scratch.numel(), ptr(_lib.err_flag(q.device)), stream_ptr())
+    if status == -2:
+        return False
+    check(status, "anchor_importance_batched", 2)
+    return True
+
+
 def anchor_importance_noalloc(q, q_rows, affix_k, affix_shift: int, rope_cos, rope_sin, scale: float, importance):
     """``anchor_importance`` for callers that may not allocate device memory (a host that owns
     the whole GPU through its own arena, a plugin that only gets input and output buffers, a

@@ -204,6 +204,28 @@ ACACHE_API int acache_anchor_importance(const void* q, int64_t q_stride, const i
                              float* importance, void* scratch, int64_t scratch_bytes, int32_t* err_flag,
                              void* stream);
 
+/* One layer's influence scores of ALL requests of a probe batch in one launch (the reference runs
+ * the probe per request, nano-vdllm/model_runner.py:862-907; a batch of newly admitted requests
+ * shares one ragged forward here).  Request r owns the mask rows
+ * q_rows[q_row_offsets[r] .. q_row_offsets[r + 1]) (device int32[n_requests + 1]; at most
+ * max_q_rows of them), the rotation row affix_shifts[r] (device int32[n_requests]; NULL = no
+ * rotation) and the scores importance[r * importance_stride ...].  Every request's result has the
+ * bits of its own acache_anchor_importance call.  Tensor-core shapes only (16-bit dtype, head_dim
+ * 64 or 128, affix_len at most 2048): anything else returns ACACHE_EUNSUPPORTED and the caller
+ * loops over the requests.  An affix_shifts entry outside the table raises err_flag code 4 and is
+ * treated as 0. */
+ACACHE_API int64_t acache_anchor_importance_batched_scratch_bytes(int n_requests, int max_q_rows, int n_heads,
+                                                                  int affix_len);
+ACACHE_API int acache_anchor_importance_batched(const void* q, int64_t q_stride, const int32_t* q_rows,
+                                                const int32_t* q_row_offsets, int n_requests, int max_q_rows,
+                                                int n_heads, int n_kv_heads, int head_dim, int dtype,
+                                                const void* affix_k, int64_t k_slot_stride, int affix_len,
+                                                const int32_t* affix_shifts, const void* rope_cos,
+                                                const void* rope_sin, int64_t rope_row_stride, int rope_rows,
+                                                int rope_dtype, float scale, float* importance,
+                                                int64_t importance_stride, void* scratch, int64_t scratch_bytes,
+                                                int32_t* err_flag, void* stream);
+
 /* The same computation for callers that cannot provide scratch memory and must not cause an
  * allocation: hosts that have given the whole device to their own memory arena, plugins that
  * only ever receive their input and output buffers, and latency-critical loops that cannot

@@ -250,6 +250,55 @@ def test_anchor_importance_vs_oracle(nh, hkv, D, A, nq, shift, dt):
     assert abs(float(got.sum()) - nq * nh) < 1e-2 * nq * nh  # softmax rows sum to one
 
 
+@pytest.mark.parametrize("nh,hkv,D,A,counts,shifts,dt", [
+    (32, 32, 128, 800, [32, 32, 7, 0, 256, 31], None, torch.bfloat16),       # a request without mask rows
+    (8, 2, 128, 300, [70, 5, 129], [13, 0, 40], torch.bfloat16),             # GQA, rotated keys, two row tiles
+    (4, 4, 64, 2048, [3, 9], [5, 5], torch.float16),                         # the longest unchunked affix
+    (28, 4, 128, 600, [32] * 9, [17, 90, 33, 64, 0, 1, 2, 3, 127], torch.bfloat16)])
+def test_anchor_importance_batched_has_the_bits_of_the_per_request_call(nh, hkv, D, A, counts, shifts, dt):
+    """All requests of a probe batch in one launch against one launch per request: same bits,
+    also when the scores accumulate over several calls (layers)."""
+    _lib, ops, aa, att = _ops()
+    g = torch.Generator().manual_seed(16)
+    n = sum(counts) + 23
+    q = torch.randn(n, nh, D, generator=g).to(dt).to(DEV)
+    kc = torch.randn(A + 20, hkv, D, generator=g).to(dt).to(DEV)
+    cos, sin = (t.to(DEV) for t in _rope(128, D))
+    perm = torch.randperm(n, generator=g)[: sum(counts)]
+    rows, off = [], [0]
+    for c in counts:
+        rows.append(perm[off[-1]: off[-1] + c].sort().values.to(torch.int32))
+        off.append(off[-1] + c)
+    ref = torch.zeros(len(counts), A, device=DEV)
+    got = torch.zeros(len(counts), A, device=DEV)
+    all_rows = torch.cat(rows).to(DEV)
+    offsets = torch.tensor(off, dtype=torch.int32, device=DEV)
+    dev_shifts = None if shifts is None else torch.tensor(shifts, dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        for r, rr in enumerate(rows):
+            ops.anchor_importance(q, rr.to(DEV), kc[:A], 0 if shifts is None else shifts[r], cos, sin, D ** -0.5, ref[r])
+        assert ops.anchor_importance_batched(q, all_rows, offsets, max(counts), kc[:A], dev_shifts, cos, sin,
+                                             D ** -0.5, got)
+    assert torch.equal(got, ref)
+    for r, c in enumerate(counts):
+        assert abs(float(got[r].sum()) - 2 * c * nh) <= 1e-2 * max(2 * c * nh, 1)
+    _lib.check_device_errors()
+
+
+def test_anchor_importance_batched_declines_what_only_the_per_request_call_takes():
+    _lib, ops, aa, att = _ops()
+    off = torch.tensor([0, 2, 4], dtype=torch.int32, device=DEV)
+    rows = torch.arange(4, dtype=torch.int32, device=DEV)
+    imp = torch.zeros(2, 2049, device=DEV)
+    q = torch.zeros(4, 4, 64, dtype=torch.bfloat16, device=DEV)
+    kc = torch.zeros(2049, 4, 64, dtype=torch.bfloat16, device=DEV)
+    assert not ops.anchor_importance_batched(q, rows, off, 2, kc, None, None, None, 0.125, imp)   # chunked affix
+    q32, k32 = torch.zeros(4, 4, 64, device=DEV), torch.zeros(100, 4, 64, device=DEV)
+    assert not ops.anchor_importance_batched(q32, rows, off, 2, k32, None, None, None, 0.125, imp[:, :100].contiguous())
+    assert float(imp.abs().sum()) == 0.0
+    _lib.check_device_errors()
+
+
 # ----------------------------------------------------------------------------- attention
 def _tol(dt):
     return {torch.float32: 2e-5, torch.float16: 4e-3, torch.bfloat16: 2e-2}[dt]
