@@ -209,7 +209,8 @@ def case_qkv(n, hidden, nh, hkv, D, fused):
 
 def case_linear(kind, M, K=4096, nh=32, hkv=32, D=128, ffn=12288, vocab=126464):
     """One fused projection of this package at the LLaDA-8B sizes: "qkv" (+ RoPE + cache scatter),
-    "gate_up" (+ gated activation), "head" (+ arg-max statistics), "plain" (K -> 4096)."""
+    "gate_up" (+ gated activation), "head" (+ arg-max statistics), "plain" (K -> 4096), "sliced"
+    (K -> 4096 with the K range cut into the planned number of slices, fp32 partial sums)."""
     x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
     if kind == "qkv":
         N = (nh + 2 * hkv) * D
@@ -229,6 +230,10 @@ def case_linear(kind, M, K=4096, nh=32, hkv=32, D=128, ffn=12288, vocab=126464):
         N = vocab
         w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * K ** -0.5
         fn = lambda: ops.linear_argmax(x, w)
+    elif kind == "sliced":
+        N = 4096
+        w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * K ** -0.5
+        fn = lambda: ops.linear_partials(x, w)
     else:
         N = 4096
         w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * K ** -0.5
@@ -478,6 +483,7 @@ CASES = {
     "linear_gate_up_refresh_llada": (lambda: case_linear("gate_up", 2304), "tensor"),
     "linear_head_decode_llada": (lambda: case_linear("head", 512), "tensor"),
     "linear_plain_decode_llada": (lambda: case_linear("plain", 512), "tensor"),
+    "linear_sliced_ff_out_decode_llada": (lambda: case_linear("sliced", 512, K=12288), "tensor"),
     "act_mul_decode_llada": (lambda: case_act_mul(512, 12288), "hbm"),
     "add_rmsnorm_decode_llada": (lambda: case_add_rmsnorm(512, 4096), "hbm"),
     "topk_cfg1": (lambda: case_topk(4, 512, 103), "latency"),
