@@ -40,3 +40,32 @@ def test_argument_validation_needs_no_gpu():
     assert lib.acache_anchor_topk(None, -1, 4, 4, 1, 1, None, None, None) == -1
     assert lib.acache_anchor_topk(None, 0, 4, 4, 1, 1, None, None, None) == 0
     assert lib.acache_anchor_importance_scratch_bytes(33, 4, 100) == 2 * 4 * 100 * 4
+
+
+def test_launch_plans_and_new_entry_points_validate_without_a_gpu():
+    """Host-side arithmetic of the library: the K-slicing plan of the plain projections and the
+    scratch size / argument checks of the batched influence score."""
+    from acache_b200 import _lib
+
+    lib = _lib.load()
+    plan = lib.acache_linear_partials_splits
+    assert plan(512, 12288, 4096) == 2      # block decode of 16 requests, feed-forward output: 32 tiles x 2 slices
+    assert plan(256, 12288, 4096) == 4      # 8 requests: 16 tiles x 4 slices of 48 k blocks
+    assert plan(512, 4096, 4096) == 1       # K too short for a slice of 48 k blocks
+    assert plan(2304, 12288, 4096) == 1     # a refresh chunk has enough whole tiles
+    assert plan(1024, 18944, 3584) == 1     # Dream block decode: 56 whole tiles
+    assert plan(0, 128, 64) == 1 and plan(16, 128, 64) == 1
+    assert lib.acache_linear_partials(None, 0, 4, 128, None, 64, 2, None, 17, 0, 0, None, None) == -1   # slice count
+    assert lib.acache_linear_partials(None, 0, 0, 128, None, 64, 2, None, 2, 0, 0, None, None) == 0     # no rows
+    assert lib.acache_anchor_importance_batched_scratch_bytes(3, 33, 4, 100) == 3 * 2 * 4 * 100 * 4
+    assert lib.acache_anchor_importance_batched_scratch_bytes(0, 33, 4, 100) == 0
+    args = [None, 0, None, None, 2, 4, 4, 3, 64, 2, None, 0, 10, None, None, None, 0, 0, 0, 0.125, None, 10, None, 0,
+            None, None]
+    assert lib.acache_anchor_importance_batched(*args) == -1          # heads not a multiple of KV heads
+    args[7] = 4
+    args[4] = 0
+    assert lib.acache_anchor_importance_batched(*args) == 0           # no requests: nothing to do
+    args[4] = 2
+    assert lib.acache_anchor_importance_batched(*args) == -1          # null pointers
+    args[21] = 9
+    assert lib.acache_anchor_importance_batched(*args) == -1          # score rows shorter than the affix
